@@ -1,0 +1,275 @@
+/*
+ * skl-b200.h -- public C interface of the B200 (sm_100a) build of SKL's dense linear-algebra path:
+ * the gemm family with its pack and cvt companions.
+ *
+ * Every function keeps the parameter list of the SKL routine it stands in for (cited per group as
+ * path:line inside the SKL source tree); only the ISA field of the name changes to `sm100a`.
+ * skl-b200-compat.h maps SKL's RISC-V names onto these so code written against skl.h compiles
+ * unchanged.
+ *
+ * Conventions kept from SKL (include/skl-common.h:21-47, src/README.md:5-35, src/gemm/README.md:41-71):
+ *   - plain C linkage, every function returns void, the caller owns every buffer;
+ *   - strides are in ELEMENTS; fp8 travels as uint8_t, bf16 as __bf16, fp16 as _Float16;
+ *   - C = alpha*A*B + beta*C; k == 0 gives C = beta*C; zero m or n is a no-op;
+ *   - bytes of an output buffer that the (shape, stride) arguments do not address stay untouched.
+ *
+ * What is new on this target:
+ *   - A pointer may be host memory or device memory (also managed); each argument is classified
+ *     on its own.  Host operands are staged through device memory inside the call.
+ *   - The work is issued on the calling thread's current library stream (default: the CUDA legacy
+ *     default stream) and, unless asynchronous mode was selected, the call returns after it finished.
+ *   - Errors cannot be returned through SKL's void signatures; skl_b200_last_status() reports the
+ *     outcome of the calling thread's most recent library call.  There is no CPU fallback: when no
+ *     usable device exists the call does nothing except record SKL_B200_ERR_CUDA.
+ *   - beta == 0 means C is not read (SKL's scalar reference evaluates 0*C, which differs only when C
+ *     holds NaN/Inf, or in the sign of a zero result).
+ */
+#ifndef SKL_B200_H
+#define SKL_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#if !defined(SKL_FUNC)
+#define SKL_FUNC /* same decorator hook as include/skl-common.h:21-34 */
+#endif
+
+#if !defined(SKL_RESTRICT)
+#if defined(__cplusplus)
+#define SKL_RESTRICT __restrict__
+#else
+#define SKL_RESTRICT restrict
+#endif
+#endif
+
+/* 16-bit float storage types.  Only pointers to them cross the interface, so a build whose
+ * compiler lacks the extension types may define these to uint16_t without changing the ABI. */
+#if !defined(SKL_B200_BF16_T)
+#if defined(__CUDACC__) || defined(SKL_B200_NO_EXT_FLOAT)
+#define SKL_B200_BF16_T uint16_t
+#define SKL_B200_F16_T uint16_t
+#else
+#define SKL_B200_BF16_T __bf16
+#define SKL_B200_F16_T _Float16
+#endif
+#endif
+typedef SKL_B200_BF16_T skl_bf16_t;
+typedef SKL_B200_F16_T skl_f16_t;
+
+#if defined(__cplusplus)
+extern "C" {
+#endif
+
+/* ------------------------------------------------------------------ side channel (not in SKL) */
+
+typedef enum skl_b200_status {
+  SKL_B200_OK = 0,
+  SKL_B200_ERR_INVALID_ARGUMENT = 1, /* null pointer with non-empty shape, overlapping restrict, bad enum */
+  SKL_B200_ERR_CUDA = 2,             /* a CUDA runtime/driver call failed, or no sm_100 device        */
+  SKL_B200_ERR_ALLOC = 3,            /* device workspace could not be allocated                       */
+  SKL_B200_ERR_DEVICE_TIMEOUT = 4,   /* a bounded wait inside a kernel expired; output is undefined   */
+  SKL_B200_ERR_UNSUPPORTED = 5       /* type combination not provided                                 */
+} skl_b200_status_t;
+
+/* Outcome of the calling thread's most recent library call. */
+SKL_FUNC skl_b200_status_t skl_b200_last_status(void);
+SKL_FUNC const char *skl_b200_status_string(skl_b200_status_t s);
+/* Text of the last CUDA error seen by the calling thread ("" if none). */
+SKL_FUNC const char *skl_b200_last_cuda_error(void);
+
+/* Stream (a cudaStream_t passed as void*) used by the calling thread's later calls; NULL = legacy
+ * default stream. */
+SKL_FUNC void skl_b200_set_stream(void *cuda_stream);
+SKL_FUNC void *skl_b200_get_stream(void);
+/* 0 (default): each call returns after its device work completed.  1: calls whose arguments are
+ * all device pointers only enqueue work; skl_b200_synchronize() waits.  Calls with host operands
+ * always complete before returning. */
+SKL_FUNC void skl_b200_set_async(int enabled);
+SKL_FUNC void skl_b200_synchronize(void);
+/* Releases the calling thread's cached device workspaces. */
+SKL_FUNC void skl_b200_release_workspace(void);
+
+/* Which kernel family served the calling thread's last GEMM call (for tests and benchmarks). */
+typedef enum skl_b200_path {
+  SKL_B200_PATH_NONE = 0,
+  SKL_B200_PATH_GENERIC = 1, /* any-stride SIMT kernel                         */
+  SKL_B200_PATH_TCGEN05 = 2, /* TMA + tcgen05 tensor-core kernel               */
+  SKL_B200_PATH_GEMV = 3     /* bandwidth-bound skinny kernel (m <= 16, int8)  */
+} skl_b200_path_t;
+SKL_FUNC skl_b200_path_t skl_b200_last_path(void);
+/* Number of kernels the calling thread's last library call launched. */
+SKL_FUNC int skl_b200_last_launch_count(void);
+/* Restricts GEMM dispatch (debug/testing): 0 = automatic, else force one skl_b200_path_t where legal. */
+SKL_FUNC void skl_b200_force_path(int path);
+
+/* Column range [*start, *start + *count) of an n-column matrix owned by shard `index` of `parts`
+ * when B and C are partitioned by columns across devices (remainder spread over the first shards,
+ * boundaries rounded to `align` columns where possible). */
+SKL_FUNC void skl_b200_shard_columns(size_t n, size_t parts, size_t index, size_t align,
+                                     size_t *start, size_t *count);
+
+/* ------------------------------------------------------------------ GEMM, general element strides
+ * Parameter lists of ref/gemm/gemm_i8rc_i8rc_i32rc.h:45-49, gemm_bf16rc_bf16rc_f32rc.h,
+ * gemm_f16rc_f16rc_f32rc.h, gemm_f8e4m3rc_f8e4m3rc_f32rc.h, gemm_f8e5m2rc_f8e5m2rc_f32rc.h. */
+SKL_FUNC void skl_gemm_i8rc_i8rc_i32rc_sm100a(size_t m, size_t n, size_t k, int32_t alpha,
+                                              const int8_t *a, size_t rsa, size_t csa,
+                                              const int8_t *b, size_t rsb, size_t csb, int32_t beta,
+                                              int32_t *c, size_t rsc, size_t csc);
+SKL_FUNC void skl_gemm_bf16rc_bf16rc_f32rc_sm100a(size_t m, size_t n, size_t k, float alpha,
+                                                  const skl_bf16_t *a, size_t rsa, size_t csa,
+                                                  const skl_bf16_t *b, size_t rsb, size_t csb,
+                                                  float beta, float *c, size_t rsc, size_t csc);
+SKL_FUNC void skl_gemm_f16rc_f16rc_f32rc_sm100a(size_t m, size_t n, size_t k, float alpha,
+                                                const skl_f16_t *a, size_t rsa, size_t csa,
+                                                const skl_f16_t *b, size_t rsb, size_t csb,
+                                                float beta, float *c, size_t rsc, size_t csc);
+SKL_FUNC void skl_gemm_f8e4m3rc_f8e4m3rc_f32rc_sm100a(size_t m, size_t n, size_t k, float alpha,
+                                                      const uint8_t *a, size_t rsa, size_t csa,
+                                                      const uint8_t *b, size_t rsb, size_t csb,
+                                                      float beta, float *c, size_t rsc, size_t csc);
+SKL_FUNC void skl_gemm_f8e5m2rc_f8e5m2rc_f32rc_sm100a(size_t m, size_t n, size_t k, float alpha,
+                                                      const uint8_t *a, size_t rsa, size_t csa,
+                                                      const uint8_t *b, size_t rsb, size_t csb,
+                                                      float beta, float *c, size_t rsc, size_t csc);
+
+/* ------------------------------------------------------------------ GEMM, row-major A, B, C
+ * Parameter lists of src/gemm/gemm_i8_i8_i32_zve32x.h:50-53, gemm_bf16_bf16_f32_zvfbfwma.h:49-52,
+ * gemm_f16_f16_f32_zvfh.h:49-51 (rsa/rsb/rsc are row strides; column strides are 1). */
+SKL_FUNC void skl_gemm_i8_i8_i32_sm100a(size_t m, size_t n, size_t k, int32_t alpha,
+                                        const int8_t *a, size_t rsa, const int8_t *b, size_t rsb,
+                                        int32_t beta, int32_t *c, size_t rsc);
+SKL_FUNC void skl_gemm_bf16_bf16_f32_sm100a(size_t m, size_t n, size_t k, float alpha,
+                                            const skl_bf16_t *a, size_t rsa, const skl_bf16_t *b,
+                                            size_t rsb, float beta, float *c, size_t rsc);
+SKL_FUNC void skl_gemm_f16_f16_f32_sm100a(size_t m, size_t n, size_t k, float alpha,
+                                          const skl_f16_t *a, size_t rsa, const skl_f16_t *b,
+                                          size_t rsb, float beta, float *c, size_t rsc);
+
+/* ------------------------------------------------------------------ GEMM, column-major A, row-major B, C
+ * Parameter lists of src/gemm/gemm_i8c_i8_i32_xsfmm32a8i.h:57-60, gemm_bf16c_bf16_f32_xsfmm32a16f.h:56-60,
+ * gemm_f16c_f16_f32_xsfmm32a16f.h:56-60, gemm_f8e4m3c_f8e4m3_f32_xsfmm32a8f.h:57-61,
+ * gemm_f8e5m2c_f8e5m2_f32_xsfmm32a8f.h:57-61 (csa is the column stride of A; its row stride is 1). */
+SKL_FUNC void skl_gemm_i8c_i8_i32_sm100a(size_t m, size_t n, size_t k, int32_t alpha,
+                                         const int8_t *a, size_t csa, const int8_t *b, size_t rsb,
+                                         int32_t beta, int32_t *c, size_t rsc);
+SKL_FUNC void skl_gemm_bf16c_bf16_f32_sm100a(size_t m, size_t n, size_t k, float alpha,
+                                             const skl_bf16_t *a, size_t csa, const skl_bf16_t *b,
+                                             size_t rsb, float beta, float *c, size_t rsc);
+SKL_FUNC void skl_gemm_f16c_f16_f32_sm100a(size_t m, size_t n, size_t k, float alpha,
+                                           const skl_f16_t *a, size_t csa, const skl_f16_t *b,
+                                           size_t rsb, float beta, float *c, size_t rsc);
+SKL_FUNC void skl_gemm_f8e4m3c_f8e4m3_f32_sm100a(size_t m, size_t n, size_t k, float alpha,
+                                                 const uint8_t *a, size_t csa, const uint8_t *b,
+                                                 size_t rsb, float beta, float *c, size_t rsc);
+SKL_FUNC void skl_gemm_f8e5m2c_f8e5m2_f32_sm100a(size_t m, size_t n, size_t k, float alpha,
+                                                 const uint8_t *a, size_t csa, const uint8_t *b,
+                                                 size_t rsb, float beta, float *c, size_t rsc);
+
+/* ------------------------------------------------------------------ GEMM, packed (blocked 4-D) operands
+ * Parameter lists of ref/gemm/gemm_i8rcprc_i8rcprc_i32rcprc.h:50-55 and the bf16 / f16 / f8e4m3 /
+ * f8e5m2 siblings: m1 x k1 blocks of m0 x k0 for A, k1 x n1 blocks of k0 x n0 for B, m1 x n1 blocks
+ * of m0 x n0 for C; *0 strides inside a block, *1 strides between blocks. */
+SKL_FUNC void skl_gemm_i8rcprc_i8rcprc_i32rcprc_sm100a(
+    size_t m0, size_t n0, size_t k0, size_t m1, size_t n1, size_t k1, int32_t alpha, const int8_t *a,
+    size_t rsa0, size_t csa0, size_t rsa1, size_t csa1, const int8_t *b, size_t rsb0, size_t csb0,
+    size_t rsb1, size_t csb1, int32_t beta, int32_t *c, size_t rsc0, size_t csc0, size_t rsc1,
+    size_t csc1);
+SKL_FUNC void skl_gemm_bf16rcprc_bf16rcprc_f32rcprc_sm100a(
+    size_t m0, size_t n0, size_t k0, size_t m1, size_t n1, size_t k1, float alpha,
+    const skl_bf16_t *a, size_t rsa0, size_t csa0, size_t rsa1, size_t csa1, const skl_bf16_t *b,
+    size_t rsb0, size_t csb0, size_t rsb1, size_t csb1, float beta, float *c, size_t rsc0,
+    size_t csc0, size_t rsc1, size_t csc1);
+SKL_FUNC void skl_gemm_f16rcprc_f16rcprc_f32rcprc_sm100a(
+    size_t m0, size_t n0, size_t k0, size_t m1, size_t n1, size_t k1, float alpha,
+    const skl_f16_t *a, size_t rsa0, size_t csa0, size_t rsa1, size_t csa1, const skl_f16_t *b,
+    size_t rsb0, size_t csb0, size_t rsb1, size_t csb1, float beta, float *c, size_t rsc0,
+    size_t csc0, size_t rsc1, size_t csc1);
+SKL_FUNC void skl_gemm_f8e4m3rcprc_f8e4m3rcprc_f32rcprc_sm100a(
+    size_t m0, size_t n0, size_t k0, size_t m1, size_t n1, size_t k1, float alpha, const uint8_t *a,
+    size_t rsa0, size_t csa0, size_t rsa1, size_t csa1, const uint8_t *b, size_t rsb0, size_t csb0,
+    size_t rsb1, size_t csb1, float beta, float *c, size_t rsc0, size_t csc0, size_t rsc1,
+    size_t csc1);
+SKL_FUNC void skl_gemm_f8e5m2rcprc_f8e5m2rcprc_f32rcprc_sm100a(
+    size_t m0, size_t n0, size_t k0, size_t m1, size_t n1, size_t k1, float alpha, const uint8_t *a,
+    size_t rsa0, size_t csa0, size_t rsa1, size_t csa1, const uint8_t *b, size_t rsb0, size_t csb0,
+    size_t rsb1, size_t csb1, float beta, float *c, size_t rsc0, size_t csc0, size_t rsc1,
+    size_t csc1);
+
+/* ------------------------------------------------------------------ GEMM with the extended epilogue
+ * No SKL counterpart: SKL's outputs are always int32 / fp32 with scalar alpha and beta
+ * (src/gemm/README.md:41-47).  This entry adds per-row and per-column fp32 scale vectors, mixed
+ * operand formats and a narrowed output, all fused into the accumulator read-out:
+ *
+ *     acc   = sum_k A[i,k]*B[k,j]      int32 when ta == tb == SKL_B200_I8, else fp32 accumulation
+ *     v     = alpha * (float)acc
+ *     v     = v * row_scale[i]          when row_scale != NULL   (m entries)
+ *     v     = v * col_scale[j]          when col_scale != NULL   (n entries)
+ *     v     = beta * (float)C[i,j] + v  when beta != 0
+ *     C[i,j]= narrow(v)                 tc: F32 (none), BF16 / F16 (round to nearest even),
+ *                                           F8E4M3 (SKL's saturating encoder, ref/cvt/cvt_ofp8.c:97-134)
+ *
+ * every step one fp32 operation with its own rounding, in that order.
+ * Operand pairs: I8 x I8; any two of {F8E4M3, F8E5M2}; BF16 x BF16; F16 x F16; and BF16 x F8E4M3 /
+ * BF16 x F8E5M2 (the fp8 operand is widened exactly to bf16 first, as skl_cvt_f8e4m3_bf16 does). */
+typedef enum skl_b200_dtype {
+  SKL_B200_I8 = 0,
+  SKL_B200_BF16 = 1,
+  SKL_B200_F16 = 2,
+  SKL_B200_F8E4M3 = 3,
+  SKL_B200_F8E5M2 = 4,
+  SKL_B200_F32 = 5,
+  SKL_B200_I32 = 6
+} skl_b200_dtype_t;
+
+SKL_FUNC void skl_gemm_ex_sm100a(size_t m, size_t n, size_t k, skl_b200_dtype_t ta, const void *a,
+                                 size_t rsa, size_t csa, skl_b200_dtype_t tb, const void *b,
+                                 size_t rsb, size_t csb, float alpha, const float *row_scale,
+                                 const float *col_scale, float beta, skl_b200_dtype_t tc, void *c,
+                                 size_t rsc, size_t csc);
+
+/* ------------------------------------------------------------------ cvt
+ * Parameter lists of ref/cvt/cvt_ofp8.h:59-158 (src/cvt/cvt_f32_f8_zvfofp8min.h:61-112,
+ * cvt_bf16_f8_zvfofp8min_zvfbfmin.h:67-122, cvt_f8_bf16_zvfofp8min.h:39-53) and
+ * ref/cvt/cvt_ofp4.h (src/cvt/cvt_f4_f8_zvfofp4min.c:15-41): dst[i] = narrow(src[i] * scaling_factor). */
+SKL_FUNC void skl_cvt_f32_f8e4m3_sm100a(uint8_t *pDst, const float *pSrc, float scaling_factor, size_t n);
+SKL_FUNC void skl_cvt_sat_f32_f8e4m3_sm100a(uint8_t *pDst, const float *pSrc, float scaling_factor, size_t n);
+SKL_FUNC void skl_cvt_f32_f8e5m2_sm100a(uint8_t *pDst, const float *pSrc, float scaling_factor, size_t n);
+SKL_FUNC void skl_cvt_sat_f32_f8e5m2_sm100a(uint8_t *pDst, const float *pSrc, float scaling_factor, size_t n);
+SKL_FUNC void skl_cvt_bf16_f8e4m3_sm100a(uint8_t *pDst, const skl_bf16_t *pSrc, float scaling_factor, size_t n);
+SKL_FUNC void skl_cvt_sat_bf16_f8e4m3_sm100a(uint8_t *pDst, const skl_bf16_t *pSrc, float scaling_factor, size_t n);
+SKL_FUNC void skl_cvt_bf16_f8e5m2_sm100a(uint8_t *pDst, const skl_bf16_t *pSrc, float scaling_factor, size_t n);
+SKL_FUNC void skl_cvt_sat_bf16_f8e5m2_sm100a(uint8_t *pDst, const skl_bf16_t *pSrc, float scaling_factor, size_t n);
+SKL_FUNC void skl_cvt_f8e4m3_bf16_sm100a(skl_bf16_t *pDst, const uint8_t *pSrc, size_t n);
+SKL_FUNC void skl_cvt_f8e5m2_bf16_sm100a(skl_bf16_t *pDst, const uint8_t *pSrc, size_t n);
+SKL_FUNC void skl_cvt_f4e2m1_f8e4m3_sm100a(uint8_t *pDst, const uint8_t *pSrc, size_t n);
+
+/* ------------------------------------------------------------------ pack / unpack / transpose
+ * Parameter lists of src/pack/pack_e8_zve32x.h:49-113 (ref/pack/pack_e8rc_e8rcprc.h,
+ * unpack_e8rcprc_e8rc.h, transpose_e8.h) and the e16 / e32 siblings. */
+SKL_FUNC void skl_pack_e8rc_e8rcprc_sm100a(size_t m, size_t n, const uint8_t *SKL_RESTRICT src,
+                                           size_t rs, size_t cs, size_t m0, size_t n0,
+                                           uint8_t *SKL_RESTRICT dst, size_t rs0, size_t cs0,
+                                           size_t rs1, size_t cs1, uint8_t pad);
+SKL_FUNC void skl_pack_e16rc_e16rcprc_sm100a(size_t m, size_t n, const uint16_t *SKL_RESTRICT src,
+                                             size_t rs, size_t cs, size_t m0, size_t n0,
+                                             uint16_t *SKL_RESTRICT dst, size_t rs0, size_t cs0,
+                                             size_t rs1, size_t cs1, uint16_t pad);
+SKL_FUNC void skl_pack_e32rc_e32rcprc_sm100a(size_t m, size_t n, const uint32_t *SKL_RESTRICT src,
+                                             size_t rs, size_t cs, size_t m0, size_t n0,
+                                             uint32_t *SKL_RESTRICT dst, size_t rs0, size_t cs0,
+                                             size_t rs1, size_t cs1, uint32_t pad);
+SKL_FUNC void skl_unpack_e8rcprc_e8rc_sm100a(size_t m0, size_t n0, const uint8_t *SKL_RESTRICT src,
+                                             size_t rs0, size_t cs0, size_t rs1, size_t cs1,
+                                             size_t m, size_t n, uint8_t *SKL_RESTRICT dst,
+                                             size_t rs, size_t cs);
+SKL_FUNC void skl_transpose_e8_sm100a(size_t m, size_t n, const uint8_t *SKL_RESTRICT a, size_t rsa,
+                                      uint8_t *SKL_RESTRICT at, size_t rsat);
+SKL_FUNC void skl_transpose_e16_sm100a(size_t m, size_t n, const uint16_t *SKL_RESTRICT a,
+                                       size_t rsa, uint16_t *SKL_RESTRICT at, size_t rsat);
+SKL_FUNC void skl_transpose_e32_sm100a(size_t m, size_t n, const uint32_t *SKL_RESTRICT a,
+                                       size_t rsa, uint32_t *SKL_RESTRICT at, size_t rsat);
+
+#if defined(__cplusplus)
+} /* extern "C" */
+#endif
+#endif /* SKL_B200_H */

@@ -1,0 +1,476 @@
+/*
+ * skl_oracle.c -- CPU restatement of the SKL gemm / pack / cvt semantics.
+ *
+ * TEST INFRASTRUCTURE ONLY (see skl_oracle.h).  Plain C, single-threaded, written for clarity;
+ * the callers thread it over disjoint row slabs when they need speed.
+ *
+ * The fp8 encoders are stated with integer arithmetic on the fp32 bit pattern (round to nearest
+ * even on the discarded bits) instead of the reference's log2f / powf / nearbyintf formulation
+ * (ref/cvt/cvt_ofp8.c:97-172); the two agree on every one of the 2^32 fp32 inputs for both formats
+ * and both overflow flavours (checked exhaustively by oracle/check_cvt_exhaustive.c against the
+ * compiled reference).
+ */
+#include "skl_oracle.h"
+
+#include <string.h>
+
+/* ------------------------------------------------------------------ bit casts */
+static inline uint32_t f32_bits(float x) {
+  uint32_t u;
+  memcpy(&u, &x, sizeof u);
+  return u;
+}
+static inline float bits_f32(uint32_t u) {
+  float x;
+  memcpy(&x, &u, sizeof x);
+  return x;
+}
+
+/* Shift right by s >= 1 bits rounding to nearest, ties to even.  s may exceed 31. */
+static inline uint32_t shr_rne(uint32_t v, int s) {
+  if (s > 31) {
+    return 0; /* v < 2^31 always here, so v / 2^s < 1/2 */
+  }
+  uint32_t q = v >> s;
+  uint32_t rem = v & ((1u << s) - 1u);
+  uint32_t half = 1u << (s - 1);
+  if (rem > half || (rem == half && (q & 1u))) {
+    q += 1u;
+  }
+  return q;
+}
+
+/* ------------------------------------------------------------------ fp8 -> fp32 */
+/* ref/cvt/cvt_ofp8.c:18-52.  S.EEEE.MMM, bias 7, no infinity, one NaN magnitude (0x7F) which
+ * the reference maps to the positive quiet NaN 0x7FC00000 whatever the sign bit says. */
+float orc_f8e4m3_to_f32(uint8_t code) {
+  uint32_t sign = (uint32_t)(code & 0x80u) << 24;
+  uint32_t e = (code >> 3) & 0xFu;
+  uint32_t m = code & 0x7u;
+  if (e == 0xFu && m == 0x7u) {
+    return bits_f32(0x7FC00000u);
+  }
+  if (e == 0) {
+    /* m * 2^-9: exact in fp32; built as an integer-to-float conversion times a power of two */
+    float mag = (float)m * bits_f32((uint32_t)(127 - 9) << 23);
+    return bits_f32(f32_bits(mag) | sign);
+  }
+  return bits_f32(sign | ((e + 120u) << 23) | (m << 20));
+}
+
+/* ref/cvt/cvt_ofp8.c:54-95.  S.EEEEE.MM, bias 15, IEEE-style Inf (mantissa 0) and NaN; every NaN
+ * code becomes +qNaN, infinities keep their sign. */
+float orc_f8e5m2_to_f32(uint8_t code) {
+  uint32_t sign = (uint32_t)(code & 0x80u) << 24;
+  uint32_t e = (code >> 2) & 0x1Fu;
+  uint32_t m = code & 0x3u;
+  if (e == 0x1Fu) {
+    return bits_f32(m == 0 ? (sign | 0x7F800000u) : 0x7FC00000u);
+  }
+  if (e == 0) {
+    float mag = (float)m * bits_f32((uint32_t)(127 - 16) << 23); /* m * 2^-16 */
+    return bits_f32(f32_bits(mag) | sign);
+  }
+  return bits_f32(sign | ((e + 112u) << 23) | (m << 21));
+}
+
+/* ------------------------------------------------------------------ fp32 -> fp8 */
+/* Shared encoder.  mbits: mantissa bits (3 / 2); bias (7 / 15); max_code: largest finite magnitude
+ * code (0x7E / 0x7B); over: code returned (sign already applied by the caller's choice) when the
+ * rounded magnitude exceeds max_code or the input is infinite. */
+static uint8_t encode_f8(float x, int mbits, int bias, uint32_t max_code, uint8_t over) {
+  uint32_t u = f32_bits(x);
+  uint8_t sign = (uint8_t)((u >> 24) & 0x80u);
+  uint32_t au = u & 0x7FFFFFFFu;
+  if (au > 0x7F800000u) {
+    return 0x7Fu; /* NaN in: the reference always answers 0x7F (cvt_ofp8.c:113-115,151-153) */
+  }
+  if (au == 0x7F800000u) {
+    return over;
+  }
+  uint32_t be = au >> 23; /* biased fp32 exponent */
+  if (be == 0) {
+    return sign; /* zero and fp32 subnormals are far below half the smallest fp8 subnormal */
+  }
+  int e = (int)be - 127;
+  uint32_t sig = (au & 0x7FFFFFu) | 0x800000u; /* 1.f as a 24-bit integer, value = sig * 2^(e-23) */
+  int emin = 1 - bias;
+  if (e < emin) {
+    /* target subnormal: code = RNE(|x| * 2^(mbits - emin)); a carry to 2^mbits is the smallest normal */
+    uint32_t q = shr_rne(sig, 23 - mbits + (emin - e));
+    return (uint8_t)(sign | q);
+  }
+  uint32_t q = shr_rne(sig & 0x7FFFFFu, 23 - mbits); /* 0 .. 2^mbits, carry propagates into the exponent */
+  uint32_t mag = ((uint32_t)(e + bias) << mbits) + q;
+  if (e + bias > 0x7F >> mbits || mag > max_code) {
+    return over;
+  }
+  return (uint8_t)(sign | mag);
+}
+
+/* ref/cvt/cvt_ofp8.c:97-134.  Overflow and +-Inf: saturating flavour gives sign|0x7E, the other one
+ * gives the NaN code 0x7F with the sign dropped. */
+uint8_t orc_f32_to_f8e4m3(float x, int saturate) {
+  uint8_t sign = (uint8_t)((f32_bits(x) >> 24) & 0x80u);
+  return encode_f8(x, 3, 7, 0x7Eu, saturate ? (uint8_t)(sign | 0x7Eu) : (uint8_t)0x7Fu);
+}
+
+/* ref/cvt/cvt_ofp8.c:136-172.  Overflow and +-Inf: saturating gives sign|0x7B, else sign|0x7C (Inf). */
+uint8_t orc_f32_to_f8e5m2(float x, int saturate) {
+  uint8_t sign = (uint8_t)((f32_bits(x) >> 24) & 0x80u);
+  return encode_f8(x, 2, 15, 0x7Bu, (uint8_t)(sign | (saturate ? 0x7Bu : 0x7Cu)));
+}
+
+/* ------------------------------------------------------------------ 16-bit floats */
+float orc_bf16_to_f32(uint16_t bits) { return bits_f32((uint32_t)bits << 16); }
+
+/* Round to nearest even on the low 16 bits; NaN keeps sign and top payload bits and is quieted,
+ * which is what gcc's (__bf16) cast does on x86-64. */
+uint16_t orc_f32_to_bf16(float x) {
+  uint32_t u = f32_bits(x);
+  if ((u & 0x7FFFFFFFu) > 0x7F800000u) {
+    return (uint16_t)((u >> 16) | 0x0040u);
+  }
+  u += 0x7FFFu + ((u >> 16) & 1u);
+  return (uint16_t)(u >> 16);
+}
+
+float orc_f16_to_f32(uint16_t bits) {
+  uint32_t sign = (uint32_t)(bits & 0x8000u) << 16;
+  uint32_t e = (bits >> 10) & 0x1Fu;
+  uint32_t m = bits & 0x3FFu;
+  if (e == 0x1Fu) {
+    return bits_f32(sign | 0x7F800000u | (m << 13));
+  }
+  if (e == 0) {
+    float mag = (float)m * bits_f32((uint32_t)(127 - 24) << 23); /* m * 2^-24, exact */
+    return bits_f32(f32_bits(mag) | sign);
+  }
+  return bits_f32(sign | ((e + 112u) << 23) | (m << 13));
+}
+
+uint16_t orc_f32_to_f16(float x) {
+  uint32_t u = f32_bits(x);
+  uint16_t sign = (uint16_t)((u >> 16) & 0x8000u);
+  uint32_t au = u & 0x7FFFFFFFu;
+  if (au > 0x7F800000u) {
+    return (uint16_t)(sign | 0x7E00u | ((au >> 13) & 0x3FFu));
+  }
+  if (au >= 0x47800000u) { /* >= 65536: Inf in, or overflow after rounding handled below */
+    return (uint16_t)(sign | 0x7C00u);
+  }
+  int e = (int)(au >> 23) - 127;
+  if (e < -25) {
+    return sign;
+  }
+  uint32_t sig = (au & 0x7FFFFFu) | 0x800000u;
+  if (e < -14) {
+    return (uint16_t)(sign | shr_rne(sig, 13 + (-14 - e)));
+  }
+  uint32_t mag = ((uint32_t)(e + 15) << 10) + shr_rne(sig & 0x7FFFFFu, 13);
+  return (uint16_t)(sign | (mag > 0x7C00u ? 0x7C00u : mag));
+}
+
+/* ref/cvt/cvt_ofp4.c:18-60: E2M1 nibble -> fp32 -> non-saturating E4M3 (every E2M1 value is exact). */
+uint8_t orc_f4e2m1_to_f8e4m3(uint8_t nibble) {
+  static const float mags[8] = {0.0f, 0.5f, 1.0f, 1.5f, 2.0f, 3.0f, 4.0f, 6.0f};
+  float v = mags[nibble & 7u];
+  if (nibble & 8u) {
+    v = -v;
+  }
+  return orc_f32_to_f8e4m3(v, 0);
+}
+
+/* ------------------------------------------------------------------ array conversions */
+/* ref/cvt/cvt_ofp8.c:174-200: dst[i] = encode(src[i] * scale), the product rounded to fp32 first. */
+void orc_cvt_f32_f8(uint8_t *dst, const float *src, float scale, size_t n, int fmt, int saturate) {
+  for (size_t i = 0; i < n; ++i) {
+    volatile float scaled = src[i] * scale; /* volatile: one fp32 rounding, never fused or widened */
+    dst[i] = (fmt == ORC_F8E4M3) ? orc_f32_to_f8e4m3(scaled, saturate)
+                                 : orc_f32_to_f8e5m2(scaled, saturate);
+  }
+}
+
+/* ref/cvt/cvt_ofp8.c:202-228: the bf16 source is widened to fp32 before the multiply. */
+void orc_cvt_bf16_f8(uint8_t *dst, const uint16_t *src, float scale, size_t n, int fmt,
+                     int saturate) {
+  for (size_t i = 0; i < n; ++i) {
+    volatile float scaled = orc_bf16_to_f32(src[i]) * scale;
+    dst[i] = (fmt == ORC_F8E4M3) ? orc_f32_to_f8e4m3(scaled, saturate)
+                                 : orc_f32_to_f8e5m2(scaled, saturate);
+  }
+}
+
+/* ref/cvt/cvt_ofp8.c:230-242: decode then narrow to bf16 (exact for every non-NaN code). */
+void orc_cvt_f8_bf16(uint16_t *dst, const uint8_t *src, size_t n, int fmt) {
+  for (size_t i = 0; i < n; ++i) {
+    float v = (fmt == ORC_F8E4M3) ? orc_f8e4m3_to_f32(src[i]) : orc_f8e5m2_to_f32(src[i]);
+    dst[i] = orc_f32_to_bf16(v);
+  }
+}
+
+/* ref/cvt/cvt_ofp4.c:62-72: two nibbles per source byte, low nibble first; odd n uses the low
+ * nibble of the last byte only. */
+void orc_cvt_f4e2m1_f8e4m3(uint8_t *dst, const uint8_t *src, size_t n) {
+  for (size_t i = 0; i < n; ++i) {
+    uint8_t byte = src[i / 2];
+    dst[i] = orc_f4e2m1_to_f8e4m3((i & 1u) ? (uint8_t)(byte >> 4) : (uint8_t)(byte & 0xFu));
+  }
+}
+
+/* ------------------------------------------------------------------ operand decode */
+static inline float load_fp(int t, const void *p, size_t idx) {
+  switch (t) {
+  case ORC_BF16:
+    return orc_bf16_to_f32(((const uint16_t *)p)[idx]);
+  case ORC_F16:
+    return orc_f16_to_f32(((const uint16_t *)p)[idx]);
+  case ORC_F8E4M3:
+    return orc_f8e4m3_to_f32(((const uint8_t *)p)[idx]);
+  case ORC_F8E5M2:
+    return orc_f8e5m2_to_f32(((const uint8_t *)p)[idx]);
+  default:
+    return ((const float *)p)[idx];
+  }
+}
+
+/* ------------------------------------------------------------------ GEMM, plain strides */
+/* ref/gemm/gemm_i8rc_i8rc_i32rc.c:10-26.  Unsigned arithmetic gives the two's-complement
+ * wrap-around the reference gets from its int32 expression on every supported target. */
+void orc_gemm_i8_i32(size_t m, size_t n, size_t k, int32_t alpha, const int8_t *a, size_t rsa,
+                     size_t csa, const int8_t *b, size_t rsb, size_t csb, int32_t beta, int32_t *c,
+                     size_t rsc, size_t csc) {
+  for (size_t i = 0; i < m; ++i) {
+    for (size_t j = 0; j < n; ++j) {
+      uint32_t acc = 0;
+      const int8_t *ap = a + i * rsa;
+      const int8_t *bp = b + j * csb;
+      for (size_t p = 0; p < k; ++p) {
+        acc += (uint32_t)((int32_t)ap[p * csa] * (int32_t)bp[p * rsb]);
+      }
+      int32_t *cp = c + i * rsc + j * csc;
+      *cp = (int32_t)((uint32_t)beta * (uint32_t)*cp + (uint32_t)alpha * acc);
+    }
+  }
+}
+
+/* ref/gemm/gemm_bf16rc_bf16rc_f32rc.c:9-24 and siblings: fp32 product, one fp32 accumulator,
+ * k ascending, then beta*c + alpha*acc with a rounding after each operation. */
+void orc_gemm_fp_f32(size_t m, size_t n, size_t k, float alpha, int ta, const void *a, size_t rsa,
+                     size_t csa, int tb, const void *b, size_t rsb, size_t csb, float beta, float *c,
+                     size_t rsc, size_t csc) {
+  for (size_t i = 0; i < m; ++i) {
+    for (size_t j = 0; j < n; ++j) {
+      float acc = 0.0f;
+      for (size_t p = 0; p < k; ++p) {
+        float prod = load_fp(ta, a, i * rsa + p * csa) * load_fp(tb, b, p * rsb + j * csb);
+        acc = acc + prod;
+      }
+      float *cp = c + i * rsc + j * csc;
+      float left = beta * *cp;
+      float right = alpha * acc;
+      *cp = left + right;
+    }
+  }
+}
+
+/* ------------------------------------------------------------------ GEMM, packed operands */
+/* ref/gemm/gemm_i8rcprc_i8rcprc_i32rcprc.c:10-37: blocks (ii1, jj1) of m0 x n0 outputs; the
+ * contraction walks k1 blocks of k0 elements, i.e. k ascending as in the plain routine. */
+void orc_gemm_packed_i8_i32(size_t m0, size_t n0, size_t k0, size_t m1, size_t n1, size_t k1,
+                            int32_t alpha, const int8_t *a, size_t rsa0, size_t csa0, size_t rsa1,
+                            size_t csa1, const int8_t *b, size_t rsb0, size_t csb0, size_t rsb1,
+                            size_t csb1, int32_t beta, int32_t *c, size_t rsc0, size_t csc0,
+                            size_t rsc1, size_t csc1) {
+  for (size_t bi = 0; bi < m1; ++bi) {
+    for (size_t bj = 0; bj < n1; ++bj) {
+      for (size_t i = 0; i < m0; ++i) {
+        for (size_t j = 0; j < n0; ++j) {
+          uint32_t acc = 0;
+          for (size_t bp = 0; bp < k1; ++bp) {
+            const int8_t *ap = a + bi * rsa1 + bp * csa1 + i * rsa0;
+            const int8_t *bq = b + bp * rsb1 + bj * csb1 + j * csb0;
+            for (size_t p = 0; p < k0; ++p) {
+              acc += (uint32_t)((int32_t)ap[p * csa0] * (int32_t)bq[p * rsb0]);
+            }
+          }
+          int32_t *cp = c + bi * rsc1 + bj * csc1 + i * rsc0 + j * csc0;
+          *cp = (int32_t)((uint32_t)beta * (uint32_t)*cp + (uint32_t)alpha * acc);
+        }
+      }
+    }
+  }
+}
+
+/* ref/gemm/gemm_bf16rcprc_bf16rcprc_f32rcprc.c:9-36 and the f16 / f8e4m3 / f8e5m2 siblings. */
+void orc_gemm_packed_fp_f32(size_t m0, size_t n0, size_t k0, size_t m1, size_t n1, size_t k1,
+                            float alpha, int ta, const void *a, size_t rsa0, size_t csa0,
+                            size_t rsa1, size_t csa1, int tb, const void *b, size_t rsb0,
+                            size_t csb0, size_t rsb1, size_t csb1, float beta, float *c,
+                            size_t rsc0, size_t csc0, size_t rsc1, size_t csc1) {
+  for (size_t bi = 0; bi < m1; ++bi) {
+    for (size_t bj = 0; bj < n1; ++bj) {
+      for (size_t i = 0; i < m0; ++i) {
+        for (size_t j = 0; j < n0; ++j) {
+          float acc = 0.0f;
+          for (size_t bp = 0; bp < k1; ++bp) {
+            size_t abase = bi * rsa1 + bp * csa1 + i * rsa0;
+            size_t bbase = bp * rsb1 + bj * csb1 + j * csb0;
+            for (size_t p = 0; p < k0; ++p) {
+              float prod = load_fp(ta, a, abase + p * csa0) * load_fp(tb, b, bbase + p * rsb0);
+              acc = acc + prod;
+            }
+          }
+          float *cp = c + bi * rsc1 + bj * csc1 + i * rsc0 + j * csc0;
+          float left = beta * *cp;
+          float right = alpha * acc;
+          *cp = left + right;
+        }
+      }
+    }
+  }
+}
+
+/* ------------------------------------------------------------------ extended epilogue */
+static inline float load_c(int tc, const void *c, size_t idx) {
+  if (tc == ORC_F8E4M3) {
+    return orc_f8e4m3_to_f32(((const uint8_t *)c)[idx]);
+  }
+  return load_fp(tc, c, idx);
+}
+
+static inline void store_c(int tc, void *c, size_t idx, float v) {
+  switch (tc) {
+  case ORC_BF16:
+    ((uint16_t *)c)[idx] = orc_f32_to_bf16(v);
+    break;
+  case ORC_F16:
+    ((uint16_t *)c)[idx] = orc_f32_to_f16(v);
+    break;
+  case ORC_F8E4M3:
+    ((uint8_t *)c)[idx] = orc_f32_to_f8e4m3(v, 1);
+    break;
+  default:
+    ((float *)c)[idx] = v;
+    break;
+  }
+}
+
+void orc_gemm_ex(size_t m, size_t n, size_t k, int ta, const void *a, size_t rsa, size_t csa, int tb,
+                 const void *b, size_t rsb, size_t csb, float alpha, const float *row_scale,
+                 const float *col_scale, float beta, int tc, void *c, size_t rsc, size_t csc) {
+  for (size_t i = 0; i < m; ++i) {
+    for (size_t j = 0; j < n; ++j) {
+      float v;
+      if (ta == ORC_I8) {
+        uint32_t acc = 0;
+        const int8_t *ap = (const int8_t *)a + i * rsa;
+        const int8_t *bp = (const int8_t *)b + j * csb;
+        for (size_t p = 0; p < k; ++p) {
+          acc += (uint32_t)((int32_t)ap[p * csa] * (int32_t)bp[p * rsb]);
+        }
+        v = (float)(int32_t)acc;
+      } else {
+        float acc = 0.0f;
+        for (size_t p = 0; p < k; ++p) {
+          float prod = load_fp(ta, a, i * rsa + p * csa) * load_fp(tb, b, p * rsb + j * csb);
+          acc = acc + prod;
+        }
+        v = acc;
+      }
+      v = alpha * v;
+      if (row_scale) {
+        v = v * row_scale[i];
+      }
+      if (col_scale) {
+        v = v * col_scale[j];
+      }
+      size_t idx = i * rsc + j * csc;
+      if (beta != 0.0f) {
+        float left = beta * load_c(tc, c, idx);
+        v = left + v;
+      }
+      store_c(tc, c, idx, v);
+    }
+  }
+}
+
+/* ------------------------------------------------------------------ pack / unpack / transpose */
+static inline void copy_elem(size_t esize, void *dst, size_t di, const void *src, size_t si) {
+  switch (esize) {
+  case 1:
+    ((uint8_t *)dst)[di] = ((const uint8_t *)src)[si];
+    break;
+  case 2:
+    ((uint16_t *)dst)[di] = ((const uint16_t *)src)[si];
+    break;
+  default:
+    ((uint32_t *)dst)[di] = ((const uint32_t *)src)[si];
+    break;
+  }
+}
+
+static inline void set_elem(size_t esize, void *dst, size_t di, uint32_t v) {
+  switch (esize) {
+  case 1:
+    ((uint8_t *)dst)[di] = (uint8_t)v;
+    break;
+  case 2:
+    ((uint16_t *)dst)[di] = (uint16_t)v;
+    break;
+  default:
+    ((uint32_t *)dst)[di] = v;
+    break;
+  }
+}
+
+/* ref/pack/pack_e8rc_e8rcprc.c:10-35: every element of every (m0 x n0) block of the
+ * ceil(m/m0) x ceil(n/n0) grid is written: the source value when it exists, else `pad`. */
+void orc_pack(size_t esize, size_t m, size_t n, const void *src, size_t rs, size_t cs, size_t m0,
+              size_t n0, void *dst, size_t rs0, size_t cs0, size_t rs1, size_t cs1, uint32_t pad) {
+  if (m0 == 0 || n0 == 0) {
+    return; /* the reference would divide by zero; the product treats it as a no-op */
+  }
+  size_t m1 = (m + m0 - 1) / m0;
+  size_t n1 = (n + n0 - 1) / n0;
+  for (size_t bi = 0; bi < m1; ++bi) {
+    for (size_t bj = 0; bj < n1; ++bj) {
+      for (size_t i0 = 0; i0 < m0; ++i0) {
+        for (size_t j0 = 0; j0 < n0; ++j0) {
+          size_t i = bi * m0 + i0;
+          size_t j = bj * n0 + j0;
+          size_t di = bi * rs1 + bj * cs1 + i0 * rs0 + j0 * cs0;
+          if (i < m && j < n) {
+            copy_elem(esize, dst, di, src, i * rs + j * cs);
+          } else {
+            set_elem(esize, dst, di, pad);
+          }
+        }
+      }
+    }
+  }
+}
+
+/* ref/pack/unpack_e8rcprc_e8rc.c:10-37: inverse of pack; padding elements are dropped. */
+void orc_unpack(size_t esize, size_t m0, size_t n0, const void *src, size_t rs0, size_t cs0,
+                size_t rs1, size_t cs1, size_t m, size_t n, void *dst, size_t rs, size_t cs) {
+  if (m0 == 0 || n0 == 0) {
+    return;
+  }
+  for (size_t i = 0; i < m; ++i) {
+    for (size_t j = 0; j < n; ++j) {
+      size_t si = (i / m0) * rs1 + (j / n0) * cs1 + (i % m0) * rs0 + (j % n0) * cs0;
+      copy_elem(esize, dst, i * rs + j * cs, src, si);
+    }
+  }
+}
+
+/* ref/pack/transpose_e8.c:11-19: at[j*rsat + i] = a[i*rsa + j]. */
+void orc_transpose(size_t esize, size_t m, size_t n, const void *a, size_t rsa, void *at,
+                   size_t rsat) {
+  for (size_t i = 0; i < m; ++i) {
+    for (size_t j = 0; j < n; ++j) {
+      copy_elem(esize, at, j * rsat + i, a, i * rsa + j);
+    }
+  }
+}

@@ -1,0 +1,104 @@
+/*
+ * abi.h -- the thin C ABI between the C99 host layer and the CUDA translation units.
+ *
+ * Everything here takes DEVICE pointers, element counts, element strides and a cudaStream_t passed
+ * as void*; no C++ or CUDA type appears, so the host layer compiles as plain C99.  Each launcher
+ * enqueues its kernel(s) on `stream` and returns the cudaError_t of the launch as an int (0 = ok);
+ * none of them synchronises, allocates or frees.
+ */
+#ifndef SKL_B200_ABI_H
+#define SKL_B200_ABI_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* element type codes (same numbering as skl_b200_dtype_t) */
+enum {
+  SKL_DT_I8 = 0,
+  SKL_DT_BF16 = 1,
+  SKL_DT_F16 = 2,
+  SKL_DT_F8E4M3 = 3,
+  SKL_DT_F8E5M2 = 4,
+  SKL_DT_F32 = 5,
+  SKL_DT_I32 = 6
+};
+
+/* How the accumulator becomes C. */
+enum {
+  /* C = beta*C + alpha*acc in int32 two's-complement arithmetic (ref/gemm/gemm_i8rc_i8rc_i32rc.c:23) */
+  SKL_EPI_INT = 0,
+  /* v = alpha*(float)acc; *row_scale[i]; *col_scale[j]; (+ beta*C when beta != 0); narrow to tc */
+  SKL_EPI_FLOAT = 1
+};
+
+/* One GEMM problem.  Plain matrices use m1 = n1 = k1 = 1 and *1 strides of 0. */
+typedef struct skl_b200_gemm_args {
+  uint64_t m0, n0, k0; /* block extents (plain matrix: the matrix extents) */
+  uint64_t m1, n1, k1; /* block counts                                      */
+  int32_t ta, tb, tc;  /* SKL_DT_*                                          */
+  int32_t epilogue;    /* SKL_EPI_*                                         */
+  const void *a;
+  const void *b;
+  void *c;
+  int64_t rsa0, csa0, rsa1, csa1;
+  int64_t rsb0, csb0, rsb1, csb1;
+  int64_t rsc0, csc0, rsc1, csc1;
+  int32_t alpha_i, beta_i; /* SKL_EPI_INT   */
+  float alpha_f, beta_f;   /* SKL_EPI_FLOAT */
+  const float *row_scale;  /* m entries or NULL (SKL_EPI_FLOAT) */
+  const float *col_scale;  /* n entries or NULL (SKL_EPI_FLOAT) */
+} skl_b200_gemm_args;
+
+/* Device status word written by kernels whose bounded waits expire: 0 = ok, else a stage code. */
+#define SKL_B200_DEVSTATUS_WORDS 4
+
+/* Any-stride SIMT GEMM: every type pair, blocked operands, k == 0.  One accumulator per output,
+ * k ascending, so float results reproduce the scalar reference's summation order. */
+int skl_b200_launch_gemm_generic(const skl_b200_gemm_args *args, void *stream);
+
+/* Tensor-core GEMM (TMA + tcgen05 + TMEM).  Plain (unblocked) operands only.
+ * skl_b200_gemm_tc_supported returns 1 when the problem meets the kernel's layout rules:
+ * each of A and B has one unit stride, 16-byte aligned base and leading stride, supported pair. */
+int skl_b200_gemm_tc_supported(const skl_b200_gemm_args *args);
+int skl_b200_launch_gemm_tc(const skl_b200_gemm_args *args, uint32_t *dev_status, void *stream);
+
+/* Skinny int8 kernel: m <= 16, A rows and B columns contiguous in k (csa == 1, rsb == 1),
+ * 16-byte aligned rows, k % 16 == 0, m*k bytes of A fit in shared memory. */
+int skl_b200_gemv_i8_supported(const skl_b200_gemm_args *args);
+int skl_b200_launch_gemv_i8(const skl_b200_gemm_args *args, void *stream);
+
+/* cvt: src_type in {F32, BF16}, dst_fmt in {F8E4M3, F8E5M2}. */
+int skl_b200_launch_cvt_to_f8(void *dst, const void *src, int src_type, int dst_fmt, int saturate,
+                              float scale, size_t n, void *stream);
+int skl_b200_launch_cvt_f8_to_bf16(void *dst, const void *src, int src_fmt, size_t n, void *stream);
+/* Strided widening used by the bf16 x fp8 GEMM: dst is a dense rows x cols bf16 matrix with the same
+ * orientation as the source (unit stride kept), leading dimension ld_dst. */
+int skl_b200_launch_cvt_f8_to_bf16_2d(void *dst, size_t ld_dst, const void *src, size_t ld_src,
+                                      int src_fmt, size_t rows, size_t cols, void *stream);
+int skl_b200_launch_cvt_f4_to_f8e4m3(void *dst, const void *src, size_t n, void *stream);
+/* Device-side self check: counts inputs in [first, first+count) (fp32 bit patterns) for which the
+ * hardware-assisted encoder and the integer encoder disagree; *mismatches is a device uint64. */
+int skl_b200_launch_cvt_selfcheck(int dst_fmt, int saturate, uint64_t first, uint64_t count,
+                                  unsigned long long *mismatches, void *stream);
+
+/* pack / unpack / transpose; esize in {1, 2, 4}. */
+int skl_b200_launch_pack(size_t esize, size_t m, size_t n, const void *src, size_t rs, size_t cs,
+                         size_t m0, size_t n0, void *dst, size_t rs0, size_t cs0, size_t rs1,
+                         size_t cs1, uint32_t pad, void *stream);
+int skl_b200_launch_unpack(size_t esize, size_t m0, size_t n0, const void *src, size_t rs0,
+                           size_t cs0, size_t rs1, size_t cs1, size_t m, size_t n, void *dst,
+                           size_t rs, size_t cs, void *stream);
+int skl_b200_launch_transpose(size_t esize, size_t m, size_t n, const void *a, size_t rsa, void *at,
+                              size_t rsat, void *stream);
+
+/* Number of kernel launches issued by this thread's launchers since the last reset. */
+int skl_b200_launch_counter(int reset);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SKL_B200_ABI_H */

@@ -1,0 +1,185 @@
+// gemm_generic.cu -- any-stride SIMT GEMM.
+//
+// Serves every problem the tensor-core and skinny kernels decline: arbitrary element strides on all
+// three matrices, blocked (packed) operands with their twelve strides, k == 0, tiny shapes,
+// unaligned bases.  Semantics are those of the scalar definitions in
+// ref/gemm/gemm_i8rc_i8rc_i32rc.c:10-26 / gemm_i8rcprc_i8rcprc_i32rcprc.c:10-37 and the float
+// siblings: one accumulator per output element, k ascending, products and sums each rounded once
+// to fp32 -- so for float operands this kernel reproduces the reference's summation order exactly.
+//
+// Layout: 64 x 64 output tile per CTA, 16 x 16 threads, 4 x 4 outputs per thread spaced 16 apart,
+// K staged 16 at a time through shared memory as already-decoded 32-bit values.  HBM traffic is
+// operand bytes x (number of tiles sharing them) -- this is the compatibility path, not the fast one.
+#include "numerics.cuh"
+
+namespace sklb {
+
+int &launch_counter_ref() {
+  static thread_local int counter = 0;
+  return counter;
+}
+
+namespace {
+
+constexpr int TM = 64, TN = 64, TK = 16;
+
+struct GenericParams {
+  skl_b200_gemm_args g;
+  int64_t M, N, K;
+};
+
+template <bool BLOCKED>
+__device__ __forceinline__ int64_t offs(int64_t r, int64_t c, int64_t r0, int64_t c0, int64_t rs0,
+                                        int64_t cs0, int64_t rs1, int64_t cs1) {
+  if (!BLOCKED) return r * rs0 + c * cs0;
+  return (r / r0) * rs1 + (r % r0) * rs0 + (c / c0) * cs1 + (c % c0) * cs0;
+}
+
+template <bool IS_INT, bool BLOCKED>
+__global__ void __launch_bounds__(256) gemm_generic_kernel(const GenericParams p) {
+  using acc_t = typename std::conditional<IS_INT, int32_t, float>::type;
+  __shared__ acc_t As[TK][TM + 1];
+  __shared__ acc_t Bs[TK][TN + 1];
+
+  const skl_b200_gemm_args &g = p.g;
+  const int tid = threadIdx.x;
+  const int tx = tid & 15, ty = tid >> 4;
+  const int64_t row0 = (int64_t)blockIdx.y * TM;
+  const int64_t col0 = (int64_t)blockIdx.x * TN;
+
+  acc_t acc[4][4];
+#pragma unroll
+  for (int r = 0; r < 4; ++r)
+#pragma unroll
+    for (int c = 0; c < 4; ++c) acc[r][c] = 0;
+
+  // Pick the staging order whose fastest-moving thread index follows the operand's unit stride.
+  const bool a_k_fast = (g.csa0 == 1);
+  const bool b_k_fast = (g.rsb0 == 1);
+
+  for (int64_t kt = 0; kt < p.K; kt += TK) {
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      int e = tid + q * 256;
+      int kk, rr;
+      if (a_k_fast) {
+        kk = e & 15;
+        rr = e >> 4;
+      } else {
+        rr = e & 63;
+        kk = e >> 6;
+      }
+      int64_t i = row0 + rr, kidx = kt + kk;
+      acc_t v = 0;
+      if (i < p.M && kidx < p.K) {
+        int64_t o = offs<BLOCKED>(i, kidx, g.m0, g.k0, g.rsa0, g.csa0, g.rsa1, g.csa1);
+        if (IS_INT)
+          v = (acc_t)((const int8_t *)g.a)[o];
+        else
+          v = (acc_t)load_as_f32(g.ta, g.a, o);
+      }
+      As[kk][rr] = v;
+    }
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      int e = tid + q * 256;
+      int kk, cc;
+      if (b_k_fast) {
+        kk = e & 15;
+        cc = e >> 4;
+      } else {
+        cc = e & 63;
+        kk = e >> 6;
+      }
+      int64_t j = col0 + cc, kidx = kt + kk;
+      acc_t v = 0;
+      if (j < p.N && kidx < p.K) {
+        int64_t o = offs<BLOCKED>(kidx, j, g.k0, g.n0, g.rsb0, g.csb0, g.rsb1, g.csb1);
+        if (IS_INT)
+          v = (acc_t)((const int8_t *)g.b)[o];
+        else
+          v = (acc_t)load_as_f32(g.tb, g.b, o);
+      }
+      Bs[kk][cc] = v;
+    }
+    __syncthreads();
+    const int klim = (int)((p.K - kt) < TK ? (p.K - kt) : TK);  // no padded terms enter the sum
+    for (int kk = 0; kk < klim; ++kk) {
+      acc_t av[4], bv[4];
+#pragma unroll
+      for (int r = 0; r < 4; ++r) av[r] = As[kk][ty + 16 * r];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) bv[c] = Bs[kk][tx + 16 * c];
+#pragma unroll
+      for (int r = 0; r < 4; ++r)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          if (IS_INT)
+            acc[r][c] = (acc_t)((uint32_t)acc[r][c] + (uint32_t)((int32_t)av[r] * (int32_t)bv[c]));
+          else
+            acc[r][c] = (acc_t)__fadd_rn((float)acc[r][c], __fmul_rn((float)av[r], (float)bv[c]));
+        }
+    }
+    __syncthreads();
+  }
+
+#pragma unroll
+  for (int r = 0; r < 4; ++r) {
+    int64_t i = row0 + ty + 16 * r;
+    if (i >= p.M) continue;
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      int64_t j = col0 + tx + 16 * c;
+      if (j >= p.N) continue;
+      int64_t o = offs<BLOCKED>(i, j, g.m0, g.n0, g.rsc0, g.csc0, g.rsc1, g.csc1);
+      if (g.epilogue == SKL_EPI_INT) {
+        int32_t *cp = (int32_t *)g.c + o;
+        uint32_t prod = (uint32_t)g.alpha_i * (uint32_t)(int32_t)acc[r][c];
+        uint32_t old = (g.beta_i != 0) ? (uint32_t)g.beta_i * (uint32_t)*cp : 0u;
+        *cp = (int32_t)(old + prod);
+      } else {
+        float v = epilogue_value((float)acc[r][c], g.alpha_f, g.row_scale, g.col_scale, i, j);
+        if (g.beta_f != 0.0f) v = __fadd_rn(__fmul_rn(g.beta_f, load_c_f32(g.tc, g.c, o)), v);
+        store_c_f32(g.tc, g.c, o, v);
+      }
+    }
+  }
+}
+
+}  // namespace
+}  // namespace sklb
+
+extern "C" int skl_b200_launch_counter(int reset) {
+  int &c = sklb::launch_counter_ref();
+  int v = c;
+  if (reset) c = 0;
+  return v;
+}
+
+extern "C" int skl_b200_launch_gemm_generic(const skl_b200_gemm_args *args, void *stream) {
+  using namespace sklb;
+  GenericParams p;
+  p.g = *args;
+  p.M = (int64_t)(args->m0 * args->m1);
+  p.N = (int64_t)(args->n0 * args->n1);
+  p.K = (int64_t)(args->k0 * args->k1);
+  if (p.M == 0 || p.N == 0) return 0;
+  const bool blocked = !(args->m1 == 1 && args->n1 == 1 && args->k1 == 1);
+  const bool is_int = (args->ta == SKL_DT_I8);
+  dim3 grid((unsigned)((p.N + TN - 1) / TN), (unsigned)((p.M + TM - 1) / TM));
+  if (grid.y > 65535u) return (int)cudaErrorInvalidConfiguration;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (is_int) {
+    if (blocked)
+      gemm_generic_kernel<true, true><<<grid, 256, 0, s>>>(p);
+    else
+      gemm_generic_kernel<true, false><<<grid, 256, 0, s>>>(p);
+  } else {
+    if (blocked)
+      gemm_generic_kernel<false, true><<<grid, 256, 0, s>>>(p);
+    else
+      gemm_generic_kernel<false, false><<<grid, 256, 0, s>>>(p);
+  }
+  SKLB_COUNT_LAUNCH();
+  return (int)cudaGetLastError();
+}

@@ -1,0 +1,662 @@
+// gemm_tc.cu -- the tensor-core GEMM for sm_100a: TMA-staged operands, tcgen05.mma, TMEM accumulators.
+//
+// Stands in for SKL's matrix-engine kernels (src/gemm/gemm_i8c_i8_i32_xsfmm32a8i.c:2466-2555 and the
+// bf16 / f16 / fp8 siblings): there the accumulator tile lives in matrix-tile registers for the whole
+// K loop and a fused alpha/beta kernel runs on it before the store (:603-641); here it lives in TMEM
+// and the epilogue warps apply alpha/beta, scale vectors and the output narrowing on the way out.
+//
+// One CTA = one 128 x BN output tile at a time, persistent over a static tile schedule
+// (tile = blockIdx.x + i*gridDim.x).  192 threads in three roles:
+//   warp 0      TMA producer: one lane issues cp.async.bulk.tensor loads of the A and B k-slabs
+//               (128 bytes of K per slab, 128-byte swizzle) into a ring of shared-memory stages;
+//   warp 1      MMA issuer: allocates TMEM, and one lane issues 4 tcgen05.mma (K = 32 bytes each) per
+//               stage, then tcgen05.commit to hand the stage back / to publish the finished tile;
+//   warps 2..5  epilogue: tcgen05.ld 32 columns at a time from the finished accumulator
+//               (two accumulators in TMEM, so tile i+1's MMAs overlap tile i's epilogue), apply the
+//               epilogue and store C with 16-byte stores where alignment allows.
+// Operands may be K-major (k contiguous) or MN-major (m or n contiguous) in global memory; the
+// shared-memory matrix descriptors and the instruction descriptor carry the difference, no
+// transposing pre-pass is needed.  Edges in M, N and K rely on TMA zero fill.
+//
+// Every mbarrier wait is bounded (about two seconds of wall time); on expiry the thread records a
+// code in the status words, raises a CTA-wide abort flag and all roles fall through to the common
+// exit, which frees TMEM.  The kernel never spins unboundedly.
+//
+// Roofline: tensor pipe.  Work per launch = 2*M*N*K operations.  HBM traffic is at least
+// (M*K + K*N)*esize + M*N*csize; operand re-reads between tiles are served by the 126 MB L2.
+#include <cuda.h>
+
+#include <cstdio>
+#include <type_traits>
+
+#include "numerics.cuh"
+
+namespace sklb {
+namespace {
+
+constexpr int BM = 128;
+constexpr int SLAB_BYTES = 128;  // bytes of K per stage row = one swizzle atom
+constexpr int NUM_THREADS = 192;
+constexpr int KIND_F16 = 0, KIND_F8 = 1, KIND_I8 = 2;
+
+constexpr uint32_t ERR_WAIT_EMPTY = 0x101, ERR_WAIT_FULL = 0x102, ERR_WAIT_TMEM_EMPTY = 0x103,
+                   ERR_WAIT_TMEM_FULL = 0x104;
+
+struct TcParams {
+  int M, N, K;
+  int tiles_m, tiles_n, num_kb;
+  int a_mn, b_mn;  // 1: operand is MN-major in global/shared memory
+  uint32_t idesc;
+  void *c;
+  int64_t rsc, csc;
+  int tc, epilogue;
+  int c_vec_ok;  // csc == 1 and rows 16-byte aligned
+  int32_t alpha_i, beta_i;
+  float alpha_f, beta_f;
+  const float *row_scale, *col_scale;
+  uint32_t *status;
+};
+
+// ------------------------------------------------------------------ PTX wrappers
+__device__ __forceinline__ uint32_t smem_u32(const void *p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ uint64_t globaltimer_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
+// Bounded wait.  Returns false when the wait expired or another thread of the CTA already gave up.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t *abort_flag,
+                                          uint32_t *status, uint32_t code) {
+  if (mbar_try(bar, parity)) return true;
+  uint64_t t0 = 0;
+  for (uint32_t spins = 1;; ++spins) {
+    if (mbar_try(bar, parity)) return true;
+    if ((spins & 63u) == 0u) {
+      if (*abort_flag) return false;
+      uint64_t now = globaltimer_ns();
+      if (t0 == 0) t0 = now;
+      if (now - t0 > 2000000000ull) {
+        *abort_flag = 1u;
+        atomicCAS(status, 0u, code);
+        return false;
+      }
+    }
+  }
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *tm, uint32_t bar, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(tm), "r"(bar), "r"(x), "r"(y)
+      : "memory");
+}
+
+template <int KIND>
+__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                     uint32_t accumulate) {
+  if (KIND == KIND_F16) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+  } else if (KIND == KIND_F8) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+  }
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
+               : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() {
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after() {
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]),
+        "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]),
+        "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]),
+        "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Shared-memory matrix descriptor (tcgen05): start address, leading / stride byte offsets in 16-byte
+// units, descriptor version 1 at bit 46, 128-byte swizzle (value 2) at bits 61..63.
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr >> 4) & 0x3FFFu);
+  d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16;
+  d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32;
+  d |= 1ull << 46;
+  d |= 2ull << 61;
+  return d;
+}
+
+template <int BN>
+struct TcConfig {
+  static constexpr int A_BYTES = BM * SLAB_BYTES;
+  static constexpr int B_BYTES = BN * SLAB_BYTES;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int STAGES_RAW = (220 * 1024) / STAGE_BYTES;
+  static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
+  static constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+};
+
+// ------------------------------------------------------------------ epilogue for 32 accumulator columns
+template <bool ACC_INT>
+__device__ __forceinline__ void epilogue_chunk(const TcParams &p, const uint32_t (&r)[32], int row,
+                                               int col0) {
+  const int ncols = (p.N - col0) < 32 ? (p.N - col0) : 32;
+  if (p.epilogue == SKL_EPI_INT) {
+    int32_t *crow = (int32_t *)p.c + (int64_t)row * p.rsc + (int64_t)col0 * p.csc;
+    if (p.c_vec_ok && ncols == 32) {
+      uint4 *dst = reinterpret_cast<uint4 *>(crow);
+#pragma unroll
+      for (int v = 0; v < 8; ++v) {
+        uint32_t o[4];
+        uint4 old = make_uint4(0, 0, 0, 0);
+        if (p.beta_i != 0) old = dst[v];
+        const uint32_t oldv[4] = {old.x, old.y, old.z, old.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+          o[e] = (uint32_t)p.beta_i * oldv[e] + (uint32_t)p.alpha_i * r[v * 4 + e];
+        dst[v] = make_uint4(o[0], o[1], o[2], o[3]);
+      }
+    } else {
+#pragma unroll
+      for (int e = 0; e < 32; ++e) {
+        if (e < ncols) {
+          int32_t *cp = crow + (int64_t)e * p.csc;
+          uint32_t old = p.beta_i != 0 ? (uint32_t)p.beta_i * (uint32_t)*cp : 0u;
+          *cp = (int32_t)(old + (uint32_t)p.alpha_i * r[e]);
+        }
+      }
+    }
+    return;
+  }
+  // float epilogue
+  float v[32];
+  const float rs = p.row_scale ? p.row_scale[row] : 1.0f;
+#pragma unroll
+  for (int e = 0; e < 32; ++e) {
+    float acc = ACC_INT ? (float)(int32_t)r[e] : __uint_as_float(r[e]);
+    float x = __fmul_rn(p.alpha_f, acc);
+    if (p.row_scale) x = __fmul_rn(x, rs);
+    if (p.col_scale && e < ncols) x = __fmul_rn(x, __ldg(p.col_scale + col0 + e));
+    v[e] = x;
+  }
+  const int64_t base = (int64_t)row * p.rsc + (int64_t)col0 * p.csc;
+  if (p.beta_f != 0.0f) {
+#pragma unroll
+    for (int e = 0; e < 32; ++e)
+      if (e < ncols)
+        v[e] = __fadd_rn(__fmul_rn(p.beta_f, load_c_f32(p.tc, p.c, base + (int64_t)e * p.csc)), v[e]);
+  }
+  if (p.c_vec_ok && ncols == 32) {
+    if (p.tc == SKL_DT_F32) {
+      uint4 *dst = reinterpret_cast<uint4 *>((float *)p.c + base);
+#pragma unroll
+      for (int q = 0; q < 8; ++q)
+        dst[q] = make_uint4(__float_as_uint(v[4 * q]), __float_as_uint(v[4 * q + 1]),
+                            __float_as_uint(v[4 * q + 2]), __float_as_uint(v[4 * q + 3]));
+    } else if (p.tc == SKL_DT_BF16 || p.tc == SKL_DT_F16) {
+      uint32_t w[16];
+#pragma unroll
+      for (int q = 0; q < 16; ++q) {
+        uint32_t lo = p.tc == SKL_DT_BF16 ? enc_bf16(v[2 * q]) : enc_f16(v[2 * q]);
+        uint32_t hi = p.tc == SKL_DT_BF16 ? enc_bf16(v[2 * q + 1]) : enc_f16(v[2 * q + 1]);
+        w[q] = lo | (hi << 16);
+      }
+      uint4 *dst = reinterpret_cast<uint4 *>((uint16_t *)p.c + base);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) dst[q] = make_uint4(w[4 * q], w[4 * q + 1], w[4 * q + 2], w[4 * q + 3]);
+    } else {  // F8E4M3, saturating
+      uint32_t w[8];
+#pragma unroll
+      for (int q = 0; q < 8; ++q)
+        w[q] = enc_e4m3x2(v[4 * q], v[4 * q + 1], true) | (enc_e4m3x2(v[4 * q + 2], v[4 * q + 3], true) << 16);
+      uint4 *dst = reinterpret_cast<uint4 *>((uint8_t *)p.c + base);
+      dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
+      dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
+    }
+  } else {
+#pragma unroll
+    for (int e = 0; e < 32; ++e)
+      if (e < ncols) store_c_f32(p.tc, p.c, base + (int64_t)e * p.csc, v[e]);
+  }
+}
+
+// ------------------------------------------------------------------ the kernel
+template <int BN, int KIND>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+    gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                   const TcParams p) {
+  using Cfg = TcConfig<BN>;
+  constexpr int ES = (KIND == KIND_F16) ? 2 : 1;   // operand element size
+  constexpr int BKE = SLAB_BYTES / ES;             // k elements per stage
+  constexpr int UMMA_KE = 32 / ES;                 // k elements per tcgen05.mma
+  constexpr int MN_PER_ATOM = SLAB_BYTES / ES;     // MN elements across one 128-byte swizzle row
+  constexpr int ATOM_BYTES = BKE * SLAB_BYTES;     // one MN-major box: BKE rows of 128 bytes
+  constexpr int A_ATOMS = BM / MN_PER_ATOM;        // MN-major boxes per A stage
+  constexpr int B_ATOMS = (BN / MN_PER_ATOM) > 0 ? (BN / MN_PER_ATOM) : 1;
+  static_assert(BN % MN_PER_ATOM == 0 || BN < MN_PER_ATOM, "BN must cover whole swizzle atoms");
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t tiles = (raw + 1023u) & ~1023u;   // stage ring, 1024-byte aligned
+  const uint32_t bars = tiles + Cfg::STAGES * Cfg::STAGE_BYTES;
+  // barrier block: full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2], then tmem base + abort flag
+  const uint32_t full_bar = bars, empty_bar = bars + 8 * Cfg::STAGES;
+  const uint32_t tfull_bar = bars + 16 * Cfg::STAGES, tempty_bar = tfull_bar + 16;
+  uint8_t *bar_gen = smem_raw + (bars - raw);
+  volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(bar_gen + 16 * Cfg::STAGES + 32);
+  volatile uint32_t *abort_flag = tmem_slot + 1;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < Cfg::STAGES; ++s) {
+      mbar_init(full_bar + 8 * s, 1);
+      mbar_init(empty_bar + 8 * s, 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(tfull_bar + 8 * b, 1);
+      mbar_init(tempty_bar + 8 * b, 128);
+    }
+    *abort_flag = 0u;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                     smem_u32((const void *)tmem_slot)),
+                 "r"((uint32_t)Cfg::TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int num_tiles = p.tiles_m * p.tiles_n;
+
+  if (warp == 0) {
+    // ---------------------------------------------------------------- TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; ok && t < num_tiles; t += gridDim.x) {
+        const int m0 = (t % p.tiles_m) * BM, n0 = (t / p.tiles_m) * BN;
+        for (int kb = 0; kb < p.num_kb; ++kb) {
+          if (!mbar_wait(empty_bar + 8 * stage, phase ^ 1u, abort_flag, p.status, ERR_WAIT_EMPTY)) {
+            ok = false;
+            break;
+          }
+          const uint32_t fb = full_bar + 8 * stage;
+          const uint32_t sa = tiles + stage * Cfg::STAGE_BYTES, sb = sa + Cfg::A_BYTES;
+          mbar_expect_tx(fb, Cfg::STAGE_BYTES);
+          const int k0 = kb * BKE;
+          if (!p.a_mn) {
+            tma_load_2d(sa, &tmA, fb, k0, m0);
+          } else {
+#pragma unroll
+            for (int i = 0; i < A_ATOMS; ++i)
+              tma_load_2d(sa + i * ATOM_BYTES, &tmA, fb, m0 + i * MN_PER_ATOM, k0);
+          }
+          if (!p.b_mn) {
+            tma_load_2d(sb, &tmB, fb, k0, n0);
+          } else {
+#pragma unroll
+            for (int i = 0; i < B_ATOMS; ++i)
+              tma_load_2d(sb + i * ATOM_BYTES, &tmB, fb, n0 + i * MN_PER_ATOM, k0);
+          }
+          if (++stage == Cfg::STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0, acc = 0, acc_phase = 0;
+      bool ok = true;
+      // descriptor geometry per operand
+      const uint32_t a_lbo = p.a_mn ? ATOM_BYTES : 16, b_lbo = p.b_mn ? ATOM_BYTES : 16;
+      const uint32_t a_adv = p.a_mn ? (UMMA_KE * SLAB_BYTES) >> 4 : 32 >> 4;
+      const uint32_t b_adv = p.b_mn ? (UMMA_KE * SLAB_BYTES) >> 4 : 32 >> 4;
+      for (int t = blockIdx.x; ok && t < num_tiles; t += gridDim.x) {
+        if (!mbar_wait(tempty_bar + 8 * acc, acc_phase ^ 1u, abort_flag, p.status, ERR_WAIT_TMEM_EMPTY))
+          break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < p.num_kb; ++kb) {
+          if (!mbar_wait(full_bar + 8 * stage, phase, abort_flag, p.status, ERR_WAIT_FULL)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sa = tiles + stage * Cfg::STAGE_BYTES, sb = sa + Cfg::A_BYTES;
+          const uint64_t da = make_smem_desc(sa, a_lbo, 1024), db = make_smem_desc(sb, b_lbo, 1024);
+#pragma unroll
+          for (int k = 0; k < SLAB_BYTES / 32; ++k)
+            umma<KIND>(d_tmem, da + (uint64_t)(k * a_adv), db + (uint64_t)(k * b_adv), p.idesc,
+                       (uint32_t)((kb | k) != 0));
+          umma_commit(empty_bar + 8 * stage);
+          if (++stage == Cfg::STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (!ok) break;
+        umma_commit(tfull_bar + 8 * acc);
+        acc ^= 1u;
+        if (acc == 0) acc_phase ^= 1u;
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- epilogue warps
+    const int quad = warp & 3;
+    uint32_t acc = 0, acc_phase = 0;
+    for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
+      const int m0 = (t % p.tiles_m) * BM, n0 = (t / p.tiles_m) * BN;
+      if (!mbar_wait(tfull_bar + 8 * acc, acc_phase, abort_flag, p.status, ERR_WAIT_TMEM_FULL)) break;
+      tc_fence_after();
+      const int row = m0 + quad * 32 + lane;
+      const uint32_t taddr = tmem_base + acc * BN + ((uint32_t)(quad * 32) << 16);
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        if (n0 + c0 >= p.N) break;  // uniform across the warp
+        uint32_t r[32];
+        tmem_ld32(taddr + c0, r);
+        if (row < p.M) epilogue_chunk<KIND == KIND_I8>(p, r, row, n0 + c0);
+      }
+      tc_fence_before();
+      mbar_arrive(tempty_bar + 8 * acc);
+      acc ^= 1u;
+      if (acc == 0) acc_phase ^= 1u;
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                 "r"((uint32_t)Cfg::TMEM_COLS)
+                 : "memory");
+  }
+}
+
+// ------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void *sym = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)sym;
+  }
+  return fn;
+}
+
+struct OperandView {
+  int mn_major;     // 1: unit stride runs along m (A) / n (B)
+  int64_t ld;       // leading stride in elements
+  bool ok;
+};
+
+// extent_mn x K operand with strides (s_mn, s_k) in elements.
+OperandView classify(const void *base, int64_t extent_mn, int64_t K, int64_t s_mn, int64_t s_k, int es) {
+  OperandView v{0, 0, false};
+  if ((reinterpret_cast<uintptr_t>(base) & 15u) != 0) return v;
+  auto ld_ok = [&](int64_t ld, int64_t inner, int64_t outer) {
+    if (outer <= 1) return true;
+    return ld >= inner && ((ld * es) & 15) == 0;
+  };
+  if (s_k == 1 && ld_ok(s_mn, K, extent_mn)) {  // K-major
+    v.mn_major = 0;
+    v.ld = s_mn;
+    v.ok = true;
+  } else if (s_mn == 1 && ld_ok(s_k, extent_mn, K)) {  // MN-major
+    v.mn_major = 1;
+    v.ld = s_k;
+    v.ok = true;
+  }
+  return v;
+}
+
+int kind_of(int ta, int tb) {
+  if (ta == SKL_DT_I8 && tb == SKL_DT_I8) return KIND_I8;
+  if ((ta == SKL_DT_BF16 && tb == SKL_DT_BF16) || (ta == SKL_DT_F16 && tb == SKL_DT_F16)) return KIND_F16;
+  const bool fa = (ta == SKL_DT_F8E4M3 || ta == SKL_DT_F8E5M2), fb = (tb == SKL_DT_F8E4M3 || tb == SKL_DT_F8E5M2);
+  if (fa && fb) return KIND_F8;
+  return -1;
+}
+
+bool make_map(CUtensorMap *tm, int kind, int dt, const void *base, const OperandView &v, int64_t extent_mn,
+              int64_t K, int box_mn) {
+  EncodeTiledFn enc = encode_fn();
+  if (!enc) return false;
+  const int es = kind == KIND_F16 ? 2 : 1;
+  CUtensorMapDataType cdt = kind == KIND_F16 ? (dt == SKL_DT_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                                                  : CU_TENSOR_MAP_DATA_TYPE_FLOAT16)
+                                             : CU_TENSOR_MAP_DATA_TYPE_UINT8;
+  cuuint64_t dims[2], strides[1];
+  cuuint32_t box[2], estr[2] = {1, 1};
+  const int per_row = SLAB_BYTES / es;  // elements across 128 bytes
+  if (!v.mn_major) {
+    dims[0] = (cuuint64_t)K;
+    dims[1] = (cuuint64_t)extent_mn;
+    box[0] = (cuuint32_t)per_row;
+    box[1] = (cuuint32_t)box_mn;
+  } else {
+    dims[0] = (cuuint64_t)extent_mn;
+    dims[1] = (cuuint64_t)K;
+    box[0] = (cuuint32_t)per_row;
+    box[1] = (cuuint32_t)per_row;  // BKE rows
+  }
+  int64_t ld = v.ld;
+  if (dims[1] <= 1) ld = (int64_t)((dims[0] * es + 15) / 16 * 16) / es;  // stride unused; keep it legal
+  strides[0] = (cuuint64_t)ld * es;
+  CUresult r = enc(tm, cdt, 2, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
+uint32_t fmt_code(int kind, int dt) {
+  if (kind == KIND_F16) return dt == SKL_DT_BF16 ? 1u : 0u;
+  if (kind == KIND_I8) return 1u;  // signed 8-bit
+  return dt == SKL_DT_F8E5M2 ? 1u : 0u;
+}
+
+int sm_count() {
+  static int sms = 0;
+  if (sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (sms <= 0) sms = 148;
+  }
+  return sms;
+}
+
+int pick_bn(int64_t M, int64_t N, int kind) {
+  const int64_t tm = (M + BM - 1) / BM;
+  const int sms = sm_count();
+  const int cand[3] = {256, 128, 64};
+  const double eff[3] = {1.0, 0.8, 0.55};
+  int best = 256;
+  double best_cost = 1e300;
+  for (int i = 0; i < 3; ++i) {
+    const int bn = cand[i];
+    if (kind != KIND_F16 && bn < 128) continue;  // 8-bit MN-major boxes span 128 columns
+    const int64_t tiles = tm * ((N + bn - 1) / bn);
+    const int64_t waves = (tiles + sms - 1) / sms;
+    const double cost = (double)waves * (bn / eff[i] + 24.0);
+    if (cost < best_cost) {
+      best_cost = cost;
+      best = bn;
+    }
+  }
+  return best;
+}
+
+template <int BN, int KIND>
+int launch_cfg(const CUtensorMap &ta, const CUtensorMap &tb, const TcParams &p, cudaStream_t s) {
+  using Cfg = TcConfig<BN>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, KIND>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         Cfg::SMEM_BYTES);
+    if (e != cudaSuccess) return (int)e;
+    attr_set = true;
+  }
+  int grid = p.tiles_m * p.tiles_n;
+  if (grid > sm_count()) grid = sm_count();
+  gemm_tc_kernel<BN, KIND><<<grid, NUM_THREADS, Cfg::SMEM_BYTES, s>>>(ta, tb, p);
+  SKLB_COUNT_LAUNCH();
+  return (int)cudaGetLastError();
+}
+
+}  // namespace
+}  // namespace sklb
+
+using namespace sklb;
+
+extern "C" int skl_b200_gemm_tc_supported(const skl_b200_gemm_args *g) {
+  if (g->m1 != 1 || g->n1 != 1 || g->k1 != 1) return 0;
+  const int kind = kind_of(g->ta, g->tb);
+  if (kind < 0) return 0;
+  const int64_t M = (int64_t)g->m0, N = (int64_t)g->n0, K = (int64_t)g->k0;
+  if (M < 1 || N < 1 || K < 1) return 0;
+  if (M >= (1ll << 31) - 256 || N >= (1ll << 31) - 256 || K >= (1ll << 31) - 256) return 0;
+  if (kind == KIND_I8 && K > 65536) return 0;  // keeps |acc| < 2^31 so no wrap-around question arises
+  const int es = kind == KIND_F16 ? 2 : 1;
+  if (!classify(g->a, M, K, g->rsa0, g->csa0, es).ok) return 0;
+  if (!classify(g->b, N, K, g->csb0, g->rsb0, es).ok) return 0;
+  if (g->epilogue == SKL_EPI_INT) {
+    if (kind != KIND_I8 || g->tc != SKL_DT_I32) return 0;
+  } else {
+    if (!(g->tc == SKL_DT_F32 || g->tc == SKL_DT_BF16 || g->tc == SKL_DT_F16 || g->tc == SKL_DT_F8E4M3)) return 0;
+  }
+  if (encode_fn() == nullptr) return 0;
+  return 1;
+}
+
+extern "C" int skl_b200_launch_gemm_tc(const skl_b200_gemm_args *g, uint32_t *dev_status, void *stream) {
+  const int kind = kind_of(g->ta, g->tb);
+  const int64_t M = (int64_t)g->m0, N = (int64_t)g->n0, K = (int64_t)g->k0;
+  const int es = kind == KIND_F16 ? 2 : 1;
+  const OperandView va = classify(g->a, M, K, g->rsa0, g->csa0, es);
+  const OperandView vb = classify(g->b, N, K, g->csb0, g->rsb0, es);
+  if (kind < 0 || !va.ok || !vb.ok) return (int)cudaErrorInvalidValue;
+  const int bn = pick_bn(M, N, kind);
+
+  CUtensorMap tmA, tmB;
+  if (!make_map(&tmA, kind, g->ta, g->a, va, M, K, BM)) return (int)cudaErrorInvalidValue;
+  if (!make_map(&tmB, kind, g->tb, g->b, vb, N, K, bn)) return (int)cudaErrorInvalidValue;
+
+  TcParams p;
+  p.M = (int)M;
+  p.N = (int)N;
+  p.K = (int)K;
+  p.tiles_m = (int)((M + BM - 1) / BM);
+  p.tiles_n = (int)((N + bn - 1) / bn);
+  const int bke = SLAB_BYTES / es;
+  p.num_kb = (int)((K + bke - 1) / bke);
+  p.a_mn = va.mn_major;
+  p.b_mn = vb.mn_major;
+  const uint32_t cfmt = kind == KIND_I8 ? 2u : 1u;  // S32 : F32 accumulator
+  p.idesc = (cfmt << 4) | (fmt_code(kind, g->ta) << 7) | (fmt_code(kind, g->tb) << 10) |
+            ((uint32_t)va.mn_major << 15) | ((uint32_t)vb.mn_major << 16) | ((uint32_t)(bn >> 3) << 17) |
+            ((uint32_t)(BM >> 4) << 24);
+  p.c = g->c;
+  p.rsc = g->rsc0;
+  p.csc = g->csc0;
+  p.tc = g->tc;
+  p.epilogue = g->epilogue;
+  const int cs = dtype_size(g->tc);
+  p.c_vec_ok = (g->csc0 == 1 && (reinterpret_cast<uintptr_t>(g->c) & 15u) == 0 &&
+                (M <= 1 || ((g->rsc0 * cs) & 15) == 0))
+                   ? 1
+                   : 0;
+  p.alpha_i = g->alpha_i;
+  p.beta_i = g->beta_i;
+  p.alpha_f = g->alpha_f;
+  p.beta_f = g->beta_f;
+  p.row_scale = g->row_scale;
+  p.col_scale = g->col_scale;
+  p.status = dev_status;
+  cudaStream_t s = (cudaStream_t)stream;
+
+#define TC_DISPATCH(BNV)                                                      \
+  switch (kind) {                                                             \
+    case KIND_F16: return launch_cfg<BNV, KIND_F16>(tmA, tmB, p, s);          \
+    case KIND_F8: return launch_cfg<BNV, KIND_F8>(tmA, tmB, p, s);            \
+    default: return launch_cfg<BNV, KIND_I8>(tmA, tmB, p, s);                 \
+  }
+  if (bn == 256) {
+    TC_DISPATCH(256)
+  } else if (bn == 128) {
+    TC_DISPATCH(128)
+  } else {
+    return launch_cfg<64, KIND_F16>(tmA, tmB, p, s);
+  }
+#undef TC_DISPATCH
+}

@@ -1,0 +1,687 @@
+/*
+ * skl_b200_host.c -- the C99 host layer of libskl_b200.
+ *
+ * Implements every entry point declared in include/skl-b200.h on top of the launch ABI in ../abi.h:
+ * argument checks, host/device pointer classification, staging of host operands through cached
+ * device workspaces, kernel-family dispatch, and the per-thread status side channel that SKL's
+ * void signatures have no room for.  No arithmetic on matrix data happens on the CPU: when the
+ * device path cannot run, the call records an error and returns.
+ *
+ * Plain C (gnu99); the CUDA runtime is used only through its C API.
+ */
+#include "../../../include/skl-b200.h"
+#include "../abi.h"
+
+#include <cuda_runtime_api.h>
+#include <stdio.h>
+#include <string.h>
+
+/* ------------------------------------------------------------------ per-thread context */
+
+enum { WS_A = 0, WS_B, WS_C, WS_ROW, WS_COL, WS_WIDEN, WS_COUNT };
+
+typedef struct {
+  void *ptr;
+  size_t cap;
+} workspace_t;
+
+typedef struct {
+  void *stream;
+  int async;
+  skl_b200_status_t status;
+  char cuda_err[192];
+  skl_b200_path_t last_path;
+  int last_launches;
+  int force_path;
+  int device;           /* device the cached resources belong to, -1 = none */
+  uint32_t *dev_status; /* mapped pinned host words written by kernels on a bounded-wait expiry */
+  workspace_t ws[WS_COUNT];
+} ctx_t;
+
+static __thread ctx_t g_ctx = {0, 0, SKL_B200_OK, {0}, SKL_B200_PATH_NONE, 0, 0, -1, 0, {{0, 0}}};
+
+static void set_err(skl_b200_status_t s) {
+  if (g_ctx.status == SKL_B200_OK) g_ctx.status = s;
+}
+
+static int cuda_ok(cudaError_t e) {
+  if (e == cudaSuccess) return 1;
+  if (g_ctx.status == SKL_B200_OK) {
+    g_ctx.status = SKL_B200_ERR_CUDA;
+    snprintf(g_ctx.cuda_err, sizeof g_ctx.cuda_err, "%s: %s", cudaGetErrorName(e), cudaGetErrorString(e));
+  }
+  (void)cudaGetLastError();
+  return 0;
+}
+
+static void release_resources(void) {
+  for (int i = 0; i < WS_COUNT; ++i) {
+    if (g_ctx.ws[i].ptr) (void)cudaFree(g_ctx.ws[i].ptr);
+    g_ctx.ws[i].ptr = 0;
+    g_ctx.ws[i].cap = 0;
+  }
+  if (g_ctx.dev_status) (void)cudaFreeHost(g_ctx.dev_status);
+  g_ctx.dev_status = 0;
+  g_ctx.device = -1;
+}
+
+/* Start of every public call: clears the status, binds the cached resources to the current device. */
+static int begin_call(void) {
+  g_ctx.status = SKL_B200_OK;
+  g_ctx.cuda_err[0] = 0;
+  g_ctx.last_launches = 0;
+  (void)skl_b200_launch_counter(1);
+  int dev = -1;
+  if (!cuda_ok(cudaGetDevice(&dev))) return 0;
+  if (dev != g_ctx.device) {
+    if (g_ctx.device >= 0) {
+      int cur = dev;
+      (void)cudaSetDevice(g_ctx.device);
+      release_resources();
+      (void)cudaSetDevice(cur);
+    }
+    int major = 0;
+    if (!cuda_ok(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev))) return 0;
+    if (major != 10) {
+      g_ctx.status = SKL_B200_ERR_CUDA;
+      snprintf(g_ctx.cuda_err, sizeof g_ctx.cuda_err, "device %d is not compute capability 10.x", dev);
+      return 0;
+    }
+    g_ctx.device = dev;
+  }
+  return 1;
+}
+
+static void end_call(void) { g_ctx.last_launches = skl_b200_launch_counter(0); }
+
+static uint32_t *device_status_words(void) {
+  if (!g_ctx.dev_status) {
+    void *p = 0;
+    if (!cuda_ok(cudaHostAlloc(&p, SKL_B200_DEVSTATUS_WORDS * sizeof(uint32_t), cudaHostAllocMapped))) return 0;
+    memset(p, 0, SKL_B200_DEVSTATUS_WORDS * sizeof(uint32_t));
+    g_ctx.dev_status = (uint32_t *)p;
+  }
+  return g_ctx.dev_status;
+}
+
+static void *workspace(int slot, size_t bytes) {
+  workspace_t *w = &g_ctx.ws[slot];
+  if (bytes == 0) bytes = 16;
+  if (w->cap < bytes) {
+    if (w->ptr) {
+      /* the previous call's work on this buffer has completed or is ordered before the free */
+      (void)cudaStreamSynchronize((cudaStream_t)g_ctx.stream);
+      (void)cudaFree(w->ptr);
+      w->ptr = 0;
+      w->cap = 0;
+    }
+    size_t want = bytes + bytes / 8 + 256;
+    void *p = 0;
+    cudaError_t e = cudaMalloc(&p, want);
+    if (e != cudaSuccess) {
+      (void)cudaGetLastError();
+      set_err(SKL_B200_ERR_ALLOC);
+      return 0;
+    }
+    w->ptr = p;
+    w->cap = want;
+  }
+  return w->ptr;
+}
+
+static int on_device(const void *p) {
+  struct cudaPointerAttributes at;
+  if (p == 0) return 1;
+  if (cudaPointerGetAttributes(&at, p) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return 0;
+  }
+  return at.type == cudaMemoryTypeDevice || at.type == cudaMemoryTypeManaged;
+}
+
+static void finish(int had_host_operand) {
+  if (g_ctx.status != SKL_B200_OK) {
+    (void)cudaStreamSynchronize((cudaStream_t)g_ctx.stream);
+    return;
+  }
+  if (had_host_operand || !g_ctx.async) {
+    cuda_ok(cudaStreamSynchronize((cudaStream_t)g_ctx.stream));
+    if (g_ctx.dev_status && g_ctx.dev_status[0] != 0) {
+      g_ctx.status = SKL_B200_ERR_DEVICE_TIMEOUT;
+      snprintf(g_ctx.cuda_err, sizeof g_ctx.cuda_err, "bounded device wait expired, stage code 0x%x",
+               g_ctx.dev_status[0]);
+      g_ctx.dev_status[0] = 0;
+    }
+  }
+}
+
+/* ------------------------------------------------------------------ side channel */
+
+skl_b200_status_t skl_b200_last_status(void) { return g_ctx.status; }
+
+const char *skl_b200_status_string(skl_b200_status_t s) {
+  switch (s) {
+  case SKL_B200_OK: return "ok";
+  case SKL_B200_ERR_INVALID_ARGUMENT: return "invalid argument";
+  case SKL_B200_ERR_CUDA: return "CUDA error";
+  case SKL_B200_ERR_ALLOC: return "device workspace allocation failed";
+  case SKL_B200_ERR_DEVICE_TIMEOUT: return "bounded device wait expired";
+  case SKL_B200_ERR_UNSUPPORTED: return "unsupported type combination";
+  default: return "unknown status";
+  }
+}
+
+const char *skl_b200_last_cuda_error(void) { return g_ctx.cuda_err; }
+void skl_b200_set_stream(void *cuda_stream) { g_ctx.stream = cuda_stream; }
+void *skl_b200_get_stream(void) { return g_ctx.stream; }
+void skl_b200_set_async(int enabled) { g_ctx.async = enabled != 0; }
+skl_b200_path_t skl_b200_last_path(void) { return g_ctx.last_path; }
+int skl_b200_last_launch_count(void) { return g_ctx.last_launches; }
+void skl_b200_force_path(int path) { g_ctx.force_path = path; }
+
+void skl_b200_synchronize(void) {
+  g_ctx.status = SKL_B200_OK;
+  g_ctx.cuda_err[0] = 0;
+  cuda_ok(cudaStreamSynchronize((cudaStream_t)g_ctx.stream));
+  if (g_ctx.dev_status && g_ctx.dev_status[0] != 0) {
+    set_err(SKL_B200_ERR_DEVICE_TIMEOUT);
+    g_ctx.dev_status[0] = 0;
+  }
+}
+
+void skl_b200_release_workspace(void) {
+  (void)cudaStreamSynchronize((cudaStream_t)g_ctx.stream);
+  release_resources();
+}
+
+void skl_b200_shard_columns(size_t n, size_t parts, size_t index, size_t align, size_t *start,
+                            size_t *count) {
+  size_t s = 0, c = 0;
+  if (parts != 0 && index < parts) {
+    if (align == 0) align = 1;
+    size_t units = (n + align - 1) / align; /* whole `align`-column units, the last may be short */
+    size_t base = units / parts, extra = units % parts;
+    size_t u0 = index * base + (index < extra ? index : extra);
+    size_t u1 = u0 + base + (index < extra ? 1 : 0);
+    s = u0 * align;
+    size_t e = u1 * align;
+    if (s > n) s = n;
+    if (e > n) e = n;
+    c = e - s;
+  }
+  if (start) *start = s;
+  if (count) *count = c;
+}
+
+/* ------------------------------------------------------------------ staging helpers */
+
+static size_t dt_size(int dt) {
+  return (dt == SKL_DT_F32 || dt == SKL_DT_I32) ? 4 : ((dt == SKL_DT_BF16 || dt == SKL_DT_F16) ? 2 : 1);
+}
+
+/* Elements spanned by a blocked matrix: last addressed offset + 1 (0 when empty). */
+static size_t span4(uint64_t r0, uint64_t c0, uint64_t r1, uint64_t c1, int64_t rs0, int64_t cs0,
+                    int64_t rs1, int64_t cs1) {
+  if (r0 == 0 || c0 == 0 || r1 == 0 || c1 == 0) return 0;
+  return (size_t)((r0 - 1) * (uint64_t)rs0 + (c0 - 1) * (uint64_t)cs0 + (r1 - 1) * (uint64_t)rs1 +
+                  (c1 - 1) * (uint64_t)cs1 + 1);
+}
+
+static const void *stage_in(int slot, const void *host, size_t bytes) {
+  void *d = workspace(slot, bytes);
+  if (!d) return 0;
+  if (bytes && !cuda_ok(cudaMemcpyAsync(d, host, bytes, cudaMemcpyHostToDevice, (cudaStream_t)g_ctx.stream)))
+    return 0;
+  return d;
+}
+
+/* A host-resident output matrix staged on the device with the caller's own strides. */
+typedef struct {
+  void *host;
+  void *dev;
+  size_t span_bytes;
+  /* 2-D form: `height` runs of `width` bytes every `pitch` bytes; width == 0 means "whole span" */
+  size_t width, height, pitch;
+} out_stage_t;
+
+static int stage_out_begin(out_stage_t *o, void *host, size_t span_bytes, size_t width, size_t height,
+                           size_t pitch, int need_old) {
+  o->host = host;
+  o->span_bytes = span_bytes;
+  o->width = width;
+  o->height = height;
+  o->pitch = pitch;
+  o->dev = workspace(WS_C, span_bytes);
+  if (!o->dev) return 0;
+  cudaStream_t s = (cudaStream_t)g_ctx.stream;
+  if (width == 0) {
+    /* irregular addressing: bring the whole span over so untouched bytes survive the round trip */
+    return cuda_ok(cudaMemcpyAsync(o->dev, host, span_bytes, cudaMemcpyHostToDevice, s));
+  }
+  if (need_old)
+    return cuda_ok(cudaMemcpy2DAsync(o->dev, pitch, host, pitch, width, height, cudaMemcpyHostToDevice, s));
+  return 1;
+}
+
+static int stage_out_end(const out_stage_t *o) {
+  cudaStream_t s = (cudaStream_t)g_ctx.stream;
+  if (o->width == 0) return cuda_ok(cudaMemcpyAsync(o->host, o->dev, o->span_bytes, cudaMemcpyDeviceToHost, s));
+  return cuda_ok(
+      cudaMemcpy2DAsync(o->host, o->pitch, o->dev, o->pitch, o->width, o->height, cudaMemcpyDeviceToHost, s));
+}
+
+/* ------------------------------------------------------------------ GEMM driver */
+
+static void run_gemm(skl_b200_gemm_args *g) {
+  if (!begin_call()) return;
+  g_ctx.last_path = SKL_B200_PATH_NONE;
+  const uint64_t M = g->m0 * g->m1, N = g->n0 * g->n1, K = g->k0 * g->k1;
+  if (M == 0 || N == 0) {
+    end_call();
+    return;
+  }
+  if (!g->c || (K != 0 && (!g->a || !g->b))) {
+    set_err(SKL_B200_ERR_INVALID_ARGUMENT);
+    return;
+  }
+  const size_t ea = dt_size(g->ta), eb = dt_size(g->tb), ec = dt_size(g->tc);
+  int host_any = 0;
+
+  /* operands */
+  if (K != 0 && !on_device(g->a)) {
+    host_any = 1;
+    size_t bytes = span4(g->m0, g->k0, g->m1, g->k1, g->rsa0, g->csa0, g->rsa1, g->csa1) * ea;
+    g->a = stage_in(WS_A, g->a, bytes);
+    if (!g->a) return;
+  }
+  if (K != 0 && !on_device(g->b)) {
+    host_any = 1;
+    size_t bytes = span4(g->k0, g->n0, g->k1, g->n1, g->rsb0, g->csb0, g->rsb1, g->csb1) * eb;
+    g->b = stage_in(WS_B, g->b, bytes);
+    if (!g->b) return;
+  }
+  if (g->row_scale && !on_device(g->row_scale)) {
+    host_any = 1;
+    g->row_scale = (const float *)stage_in(WS_ROW, g->row_scale, (size_t)M * sizeof(float));
+    if (!g->row_scale) return;
+  }
+  if (g->col_scale && !on_device(g->col_scale)) {
+    host_any = 1;
+    g->col_scale = (const float *)stage_in(WS_COL, g->col_scale, (size_t)N * sizeof(float));
+    if (!g->col_scale) return;
+  }
+
+  /* output */
+  out_stage_t out;
+  int c_host = !on_device(g->c);
+  if (c_host) {
+    host_any = 1;
+    size_t span = span4(g->m0, g->n0, g->m1, g->n1, g->rsc0, g->csc0, g->rsc1, g->csc1) * ec;
+    int need_old = (g->epilogue == SKL_EPI_INT) ? (g->beta_i != 0) : (g->beta_f != 0.0f);
+    size_t width = 0, height = 0, pitch = 0;
+    if (g->m1 == 1 && g->n1 == 1) {
+      if (g->csc0 == 1 && (uint64_t)g->rsc0 >= g->n0) {
+        width = (size_t)g->n0 * ec;
+        height = (size_t)g->m0;
+        pitch = (size_t)g->rsc0 * ec;
+      } else if (g->rsc0 == 1 && (uint64_t)g->csc0 >= g->m0) {
+        width = (size_t)g->m0 * ec;
+        height = (size_t)g->n0;
+        pitch = (size_t)g->csc0 * ec;
+      }
+      if (height == 1) pitch = width; /* a single run: any pitch >= width is legal for the 2-D copy */
+    }
+    if (!stage_out_begin(&out, g->c, span, width, height, pitch, need_old)) return;
+    g->c = out.dev;
+  }
+
+  /* bf16 x fp8: widen the fp8 operand exactly to bf16 when that makes the tensor-core path usable */
+  if (g->ta == SKL_DT_BF16 && (g->tb == SKL_DT_F8E4M3 || g->tb == SKL_DT_F8E5M2) && g->k1 == 1 &&
+      g->n1 == 1 && g->m1 == 1 && K != 0 && g_ctx.force_path != SKL_B200_PATH_GENERIC) {
+    size_t rows = 0, cols = 0, ld_src = 0;
+    int k_major = 0;
+    if (g->rsb0 == 1 && (g->n0 == 1 || (uint64_t)g->csb0 >= g->k0)) {
+      rows = (size_t)g->n0; cols = (size_t)g->k0; ld_src = (size_t)g->csb0; k_major = 1;
+    } else if (g->csb0 == 1 && (g->k0 == 1 || (uint64_t)g->rsb0 >= g->n0)) {
+      rows = (size_t)g->k0; cols = (size_t)g->n0; ld_src = (size_t)g->rsb0;
+    }
+    if (rows != 0) {
+      size_t ld_dst = (cols + 7) & ~(size_t)7; /* 16-byte aligned rows */
+      void *wide = workspace(WS_WIDEN, rows * ld_dst * 2);
+      if (!wide) return;
+      if (!cuda_ok((cudaError_t)skl_b200_launch_cvt_f8_to_bf16_2d(wide, ld_dst, g->b, ld_src, g->tb, rows, cols,
+                                                                 g_ctx.stream)))
+        return;
+      g->b = wide;
+      g->tb = SKL_DT_BF16;
+      if (k_major) {
+        g->rsb0 = 1;
+        g->csb0 = (int64_t)ld_dst;
+      } else {
+        g->rsb0 = (int64_t)ld_dst;
+        g->csb0 = 1;
+      }
+    }
+  }
+
+  /* dispatch */
+  int path = SKL_B200_PATH_GENERIC;
+  const int gemv_ok = K != 0 && skl_b200_gemv_i8_supported(g);
+  const int tc_ok = K != 0 && skl_b200_gemm_tc_supported(g);
+  if (g_ctx.force_path == SKL_B200_PATH_GEMV && gemv_ok) {
+    path = SKL_B200_PATH_GEMV;
+  } else if (g_ctx.force_path == SKL_B200_PATH_TCGEN05 && tc_ok) {
+    path = SKL_B200_PATH_TCGEN05;
+  } else if (g_ctx.force_path == 0) {
+    if (gemv_ok)
+      path = SKL_B200_PATH_GEMV;
+    else if (tc_ok && (double)M * (double)N * (double)K >= 32768.0)
+      path = SKL_B200_PATH_TCGEN05;
+  }
+  int rc = 0;
+  if (path == SKL_B200_PATH_GEMV) {
+    rc = skl_b200_launch_gemv_i8(g, g_ctx.stream);
+  } else if (path == SKL_B200_PATH_TCGEN05) {
+    uint32_t *st = device_status_words();
+    if (!st) return;
+    rc = skl_b200_launch_gemm_tc(g, st, g_ctx.stream);
+  } else {
+    rc = skl_b200_launch_gemm_generic(g, g_ctx.stream);
+  }
+  g_ctx.last_path = (skl_b200_path_t)path;
+  if (!cuda_ok((cudaError_t)rc)) return;
+
+  if (c_host && !stage_out_end(&out)) return;
+  finish(host_any);
+  end_call();
+}
+
+static void gemm_plain(int ta, int tb, int tc, int epi, size_t m, size_t n, size_t k, const void *a,
+                       size_t rsa, size_t csa, const void *b, size_t rsb, size_t csb, void *c,
+                       size_t rsc, size_t csc, int32_t alpha_i, int32_t beta_i, float alpha_f,
+                       float beta_f, const float *row_scale, const float *col_scale) {
+  skl_b200_gemm_args g;
+  memset(&g, 0, sizeof g);
+  g.m0 = m; g.n0 = n; g.k0 = k;
+  g.m1 = 1; g.n1 = 1; g.k1 = 1;
+  g.ta = ta; g.tb = tb; g.tc = tc;
+  g.epilogue = epi;
+  g.a = a; g.b = b; g.c = c;
+  g.rsa0 = (int64_t)rsa; g.csa0 = (int64_t)csa;
+  g.rsb0 = (int64_t)rsb; g.csb0 = (int64_t)csb;
+  g.rsc0 = (int64_t)rsc; g.csc0 = (int64_t)csc;
+  g.alpha_i = alpha_i; g.beta_i = beta_i;
+  g.alpha_f = alpha_f; g.beta_f = beta_f;
+  g.row_scale = row_scale; g.col_scale = col_scale;
+  run_gemm(&g);
+}
+
+static void gemm_packed(int t, int tc, int epi, size_t m0, size_t n0, size_t k0, size_t m1, size_t n1,
+                        size_t k1, const void *a, size_t rsa0, size_t csa0, size_t rsa1, size_t csa1,
+                        const void *b, size_t rsb0, size_t csb0, size_t rsb1, size_t csb1, void *c,
+                        size_t rsc0, size_t csc0, size_t rsc1, size_t csc1, int32_t alpha_i,
+                        int32_t beta_i, float alpha_f, float beta_f) {
+  skl_b200_gemm_args g;
+  memset(&g, 0, sizeof g);
+  g.m0 = m0; g.n0 = n0; g.k0 = k0;
+  g.m1 = m1; g.n1 = n1; g.k1 = k1;
+  g.ta = t; g.tb = t; g.tc = tc;
+  g.epilogue = epi;
+  g.a = a; g.b = b; g.c = c;
+  g.rsa0 = (int64_t)rsa0; g.csa0 = (int64_t)csa0; g.rsa1 = (int64_t)rsa1; g.csa1 = (int64_t)csa1;
+  g.rsb0 = (int64_t)rsb0; g.csb0 = (int64_t)csb0; g.rsb1 = (int64_t)rsb1; g.csb1 = (int64_t)csb1;
+  g.rsc0 = (int64_t)rsc0; g.csc0 = (int64_t)csc0; g.rsc1 = (int64_t)rsc1; g.csc1 = (int64_t)csc1;
+  g.alpha_i = alpha_i; g.beta_i = beta_i;
+  g.alpha_f = alpha_f; g.beta_f = beta_f;
+  /* a blocked description with a single block per dimension is a plain matrix */
+  run_gemm(&g);
+}
+
+/* ------------------------------------------------------------------ GEMM entry points */
+
+void skl_gemm_i8rc_i8rc_i32rc_sm100a(size_t m, size_t n, size_t k, int32_t alpha, const int8_t *a,
+                                     size_t rsa, size_t csa, const int8_t *b, size_t rsb, size_t csb,
+                                     int32_t beta, int32_t *c, size_t rsc, size_t csc) {
+  gemm_plain(SKL_DT_I8, SKL_DT_I8, SKL_DT_I32, SKL_EPI_INT, m, n, k, a, rsa, csa, b, rsb, csb, c, rsc, csc,
+             alpha, beta, 0.0f, 0.0f, 0, 0);
+}
+
+#define SKL_B200_DEF_GEMM_RC_F32(NAME, TYPE, DT)                                                      \
+  void NAME(size_t m, size_t n, size_t k, float alpha, const TYPE *a, size_t rsa, size_t csa,         \
+            const TYPE *b, size_t rsb, size_t csb, float beta, float *c, size_t rsc, size_t csc) {    \
+    gemm_plain(DT, DT, SKL_DT_F32, SKL_EPI_FLOAT, m, n, k, a, rsa, csa, b, rsb, csb, c, rsc, csc, 0, 0, \
+               alpha, beta, 0, 0);                                                                    \
+  }
+SKL_B200_DEF_GEMM_RC_F32(skl_gemm_bf16rc_bf16rc_f32rc_sm100a, skl_bf16_t, SKL_DT_BF16)
+SKL_B200_DEF_GEMM_RC_F32(skl_gemm_f16rc_f16rc_f32rc_sm100a, skl_f16_t, SKL_DT_F16)
+SKL_B200_DEF_GEMM_RC_F32(skl_gemm_f8e4m3rc_f8e4m3rc_f32rc_sm100a, uint8_t, SKL_DT_F8E4M3)
+SKL_B200_DEF_GEMM_RC_F32(skl_gemm_f8e5m2rc_f8e5m2rc_f32rc_sm100a, uint8_t, SKL_DT_F8E5M2)
+
+/* row-major A, B, C: column strides are 1 */
+void skl_gemm_i8_i8_i32_sm100a(size_t m, size_t n, size_t k, int32_t alpha, const int8_t *a, size_t rsa,
+                               const int8_t *b, size_t rsb, int32_t beta, int32_t *c, size_t rsc) {
+  skl_gemm_i8rc_i8rc_i32rc_sm100a(m, n, k, alpha, a, rsa, 1, b, rsb, 1, beta, c, rsc, 1);
+}
+void skl_gemm_bf16_bf16_f32_sm100a(size_t m, size_t n, size_t k, float alpha, const skl_bf16_t *a,
+                                   size_t rsa, const skl_bf16_t *b, size_t rsb, float beta, float *c,
+                                   size_t rsc) {
+  skl_gemm_bf16rc_bf16rc_f32rc_sm100a(m, n, k, alpha, a, rsa, 1, b, rsb, 1, beta, c, rsc, 1);
+}
+void skl_gemm_f16_f16_f32_sm100a(size_t m, size_t n, size_t k, float alpha, const skl_f16_t *a,
+                                 size_t rsa, const skl_f16_t *b, size_t rsb, float beta, float *c,
+                                 size_t rsc) {
+  skl_gemm_f16rc_f16rc_f32rc_sm100a(m, n, k, alpha, a, rsa, 1, b, rsb, 1, beta, c, rsc, 1);
+}
+
+/* column-major A (row stride 1), row-major B and C */
+void skl_gemm_i8c_i8_i32_sm100a(size_t m, size_t n, size_t k, int32_t alpha, const int8_t *a, size_t csa,
+                                const int8_t *b, size_t rsb, int32_t beta, int32_t *c, size_t rsc) {
+  skl_gemm_i8rc_i8rc_i32rc_sm100a(m, n, k, alpha, a, 1, csa, b, rsb, 1, beta, c, rsc, 1);
+}
+#define SKL_B200_DEF_GEMM_C_F32(NAME, GENERAL, TYPE)                                                  \
+  void NAME(size_t m, size_t n, size_t k, float alpha, const TYPE *a, size_t csa, const TYPE *b,      \
+            size_t rsb, float beta, float *c, size_t rsc) {                                           \
+    GENERAL(m, n, k, alpha, a, 1, csa, b, rsb, 1, beta, c, rsc, 1);                                   \
+  }
+SKL_B200_DEF_GEMM_C_F32(skl_gemm_bf16c_bf16_f32_sm100a, skl_gemm_bf16rc_bf16rc_f32rc_sm100a, skl_bf16_t)
+SKL_B200_DEF_GEMM_C_F32(skl_gemm_f16c_f16_f32_sm100a, skl_gemm_f16rc_f16rc_f32rc_sm100a, skl_f16_t)
+SKL_B200_DEF_GEMM_C_F32(skl_gemm_f8e4m3c_f8e4m3_f32_sm100a, skl_gemm_f8e4m3rc_f8e4m3rc_f32rc_sm100a, uint8_t)
+SKL_B200_DEF_GEMM_C_F32(skl_gemm_f8e5m2c_f8e5m2_f32_sm100a, skl_gemm_f8e5m2rc_f8e5m2rc_f32rc_sm100a, uint8_t)
+
+/* packed operands */
+void skl_gemm_i8rcprc_i8rcprc_i32rcprc_sm100a(size_t m0, size_t n0, size_t k0, size_t m1, size_t n1,
+                                              size_t k1, int32_t alpha, const int8_t *a, size_t rsa0,
+                                              size_t csa0, size_t rsa1, size_t csa1, const int8_t *b,
+                                              size_t rsb0, size_t csb0, size_t rsb1, size_t csb1,
+                                              int32_t beta, int32_t *c, size_t rsc0, size_t csc0,
+                                              size_t rsc1, size_t csc1) {
+  gemm_packed(SKL_DT_I8, SKL_DT_I32, SKL_EPI_INT, m0, n0, k0, m1, n1, k1, a, rsa0, csa0, rsa1, csa1, b, rsb0,
+              csb0, rsb1, csb1, c, rsc0, csc0, rsc1, csc1, alpha, beta, 0.0f, 0.0f);
+}
+#define SKL_B200_DEF_GEMM_PACKED_F32(NAME, TYPE, DT)                                                  \
+  void NAME(size_t m0, size_t n0, size_t k0, size_t m1, size_t n1, size_t k1, float alpha,            \
+            const TYPE *a, size_t rsa0, size_t csa0, size_t rsa1, size_t csa1, const TYPE *b,         \
+            size_t rsb0, size_t csb0, size_t rsb1, size_t csb1, float beta, float *c, size_t rsc0,    \
+            size_t csc0, size_t rsc1, size_t csc1) {                                                  \
+    gemm_packed(DT, SKL_DT_F32, SKL_EPI_FLOAT, m0, n0, k0, m1, n1, k1, a, rsa0, csa0, rsa1, csa1, b,  \
+                rsb0, csb0, rsb1, csb1, c, rsc0, csc0, rsc1, csc1, 0, 0, alpha, beta);                \
+  }
+SKL_B200_DEF_GEMM_PACKED_F32(skl_gemm_bf16rcprc_bf16rcprc_f32rcprc_sm100a, skl_bf16_t, SKL_DT_BF16)
+SKL_B200_DEF_GEMM_PACKED_F32(skl_gemm_f16rcprc_f16rcprc_f32rcprc_sm100a, skl_f16_t, SKL_DT_F16)
+SKL_B200_DEF_GEMM_PACKED_F32(skl_gemm_f8e4m3rcprc_f8e4m3rcprc_f32rcprc_sm100a, uint8_t, SKL_DT_F8E4M3)
+SKL_B200_DEF_GEMM_PACKED_F32(skl_gemm_f8e5m2rcprc_f8e5m2rcprc_f32rcprc_sm100a, uint8_t, SKL_DT_F8E5M2)
+
+/* extended epilogue */
+static int is_f8(int t) { return t == SKL_DT_F8E4M3 || t == SKL_DT_F8E5M2; }
+
+void skl_gemm_ex_sm100a(size_t m, size_t n, size_t k, skl_b200_dtype_t ta, const void *a, size_t rsa,
+                        size_t csa, skl_b200_dtype_t tb, const void *b, size_t rsb, size_t csb,
+                        float alpha, const float *row_scale, const float *col_scale, float beta,
+                        skl_b200_dtype_t tc, void *c, size_t rsc, size_t csc) {
+  int pair_ok = (ta == SKL_B200_I8 && tb == SKL_B200_I8) || (is_f8(ta) && is_f8(tb)) ||
+                (ta == SKL_B200_BF16 && tb == SKL_B200_BF16) || (ta == SKL_B200_F16 && tb == SKL_B200_F16) ||
+                (ta == SKL_B200_BF16 && is_f8(tb));
+  int out_ok = tc == SKL_B200_F32 || tc == SKL_B200_BF16 || tc == SKL_B200_F16 || tc == SKL_B200_F8E4M3;
+  if (!pair_ok || !out_ok) {
+    g_ctx.status = SKL_B200_ERR_UNSUPPORTED;
+    g_ctx.cuda_err[0] = 0;
+    return;
+  }
+  gemm_plain((int)ta, (int)tb, (int)tc, SKL_EPI_FLOAT, m, n, k, a, rsa, csa, b, rsb, csb, c, rsc, csc, 0, 0,
+             alpha, beta, row_scale, col_scale);
+}
+
+/* ------------------------------------------------------------------ cvt */
+
+static void run_cvt_to_f8(void *dst, const void *src, int src_type, int fmt, int sat, float scale, size_t n) {
+  if (!begin_call()) return;
+  if (n == 0) { end_call(); return; }
+  if (!dst || !src) { set_err(SKL_B200_ERR_INVALID_ARGUMENT); return; }
+  int host_any = 0;
+  const void *dsrc = src;
+  void *ddst = dst;
+  if (!on_device(src)) {
+    host_any = 1;
+    dsrc = stage_in(WS_A, src, n * dt_size(src_type));
+    if (!dsrc) return;
+  }
+  int dst_host = !on_device(dst);
+  if (dst_host) {
+    host_any = 1;
+    ddst = workspace(WS_C, n);
+    if (!ddst) return;
+  }
+  if (!cuda_ok((cudaError_t)skl_b200_launch_cvt_to_f8(ddst, dsrc, src_type, fmt, sat, scale, n, g_ctx.stream)))
+    return;
+  if (dst_host &&
+      !cuda_ok(cudaMemcpyAsync(dst, ddst, n, cudaMemcpyDeviceToHost, (cudaStream_t)g_ctx.stream)))
+    return;
+  finish(host_any);
+  end_call();
+}
+
+#define SKL_B200_DEF_CVT_TO_F8(NAME, SRC_T, SRC_DT, FMT, SAT)                           \
+  void NAME(uint8_t *pDst, const SRC_T *pSrc, float scaling_factor, size_t n) {         \
+    run_cvt_to_f8(pDst, pSrc, SRC_DT, FMT, SAT, scaling_factor, n);                     \
+  }
+SKL_B200_DEF_CVT_TO_F8(skl_cvt_f32_f8e4m3_sm100a, float, SKL_DT_F32, SKL_DT_F8E4M3, 0)
+SKL_B200_DEF_CVT_TO_F8(skl_cvt_sat_f32_f8e4m3_sm100a, float, SKL_DT_F32, SKL_DT_F8E4M3, 1)
+SKL_B200_DEF_CVT_TO_F8(skl_cvt_f32_f8e5m2_sm100a, float, SKL_DT_F32, SKL_DT_F8E5M2, 0)
+SKL_B200_DEF_CVT_TO_F8(skl_cvt_sat_f32_f8e5m2_sm100a, float, SKL_DT_F32, SKL_DT_F8E5M2, 1)
+SKL_B200_DEF_CVT_TO_F8(skl_cvt_bf16_f8e4m3_sm100a, skl_bf16_t, SKL_DT_BF16, SKL_DT_F8E4M3, 0)
+SKL_B200_DEF_CVT_TO_F8(skl_cvt_sat_bf16_f8e4m3_sm100a, skl_bf16_t, SKL_DT_BF16, SKL_DT_F8E4M3, 1)
+SKL_B200_DEF_CVT_TO_F8(skl_cvt_bf16_f8e5m2_sm100a, skl_bf16_t, SKL_DT_BF16, SKL_DT_F8E5M2, 0)
+SKL_B200_DEF_CVT_TO_F8(skl_cvt_sat_bf16_f8e5m2_sm100a, skl_bf16_t, SKL_DT_BF16, SKL_DT_F8E5M2, 1)
+
+/* widening directions: mode 0 = fp8 -> bf16 (out 2 bytes/elt, in 1), mode 1 = fp4 -> fp8 (out 1, in 1/2) */
+static void run_cvt_widen(void *dst, const void *src, int mode, int fmt, size_t n) {
+  if (!begin_call()) return;
+  if (n == 0) { end_call(); return; }
+  if (!dst || !src) { set_err(SKL_B200_ERR_INVALID_ARGUMENT); return; }
+  const size_t in_bytes = mode == 0 ? n : (n + 1) / 2, out_bytes = mode == 0 ? 2 * n : n;
+  int host_any = 0;
+  const void *dsrc = src;
+  void *ddst = dst;
+  if (!on_device(src)) {
+    host_any = 1;
+    dsrc = stage_in(WS_A, src, in_bytes);
+    if (!dsrc) return;
+  }
+  int dst_host = !on_device(dst);
+  if (dst_host) {
+    host_any = 1;
+    ddst = workspace(WS_C, out_bytes);
+    if (!ddst) return;
+  }
+  int rc = mode == 0 ? skl_b200_launch_cvt_f8_to_bf16(ddst, dsrc, fmt, n, g_ctx.stream)
+                     : skl_b200_launch_cvt_f4_to_f8e4m3(ddst, dsrc, n, g_ctx.stream);
+  if (!cuda_ok((cudaError_t)rc)) return;
+  if (dst_host &&
+      !cuda_ok(cudaMemcpyAsync(dst, ddst, out_bytes, cudaMemcpyDeviceToHost, (cudaStream_t)g_ctx.stream)))
+    return;
+  finish(host_any);
+  end_call();
+}
+
+void skl_cvt_f8e4m3_bf16_sm100a(skl_bf16_t *pDst, const uint8_t *pSrc, size_t n) {
+  run_cvt_widen(pDst, pSrc, 0, SKL_DT_F8E4M3, n);
+}
+void skl_cvt_f8e5m2_bf16_sm100a(skl_bf16_t *pDst, const uint8_t *pSrc, size_t n) {
+  run_cvt_widen(pDst, pSrc, 0, SKL_DT_F8E5M2, n);
+}
+void skl_cvt_f4e2m1_f8e4m3_sm100a(uint8_t *pDst, const uint8_t *pSrc, size_t n) {
+  run_cvt_widen(pDst, pSrc, 1, 0, n);
+}
+
+/* ------------------------------------------------------------------ pack / unpack / transpose */
+
+/* op: 0 pack, 1 unpack, 2 transpose.  `plain` is the 2-D side, `blk` the blocked side. */
+static void run_relayout(int op, size_t esize, size_t m, size_t n, const void *src, void *dst, size_t rs,
+                         size_t cs, size_t m0, size_t n0, size_t rs0, size_t cs0, size_t rs1, size_t cs1,
+                         uint32_t pad) {
+  if (!begin_call()) return;
+  if (op != 2 && (m0 == 0 || n0 == 0)) { end_call(); return; } /* ref/pack/unpack_e8rcprc_e8rc.c:16-18 */
+  if (m == 0 || n == 0) { end_call(); return; }
+  if (!src || !dst) { set_err(SKL_B200_ERR_INVALID_ARGUMENT); return; }
+  size_t src_span, dst_span;
+  if (op == 0) {
+    size_t m1 = (m + m0 - 1) / m0, n1 = (n + n0 - 1) / n0;
+    src_span = span4(m, n, 1, 1, (int64_t)rs, (int64_t)cs, 0, 0);
+    dst_span = span4(m0, n0, m1, n1, (int64_t)rs0, (int64_t)cs0, (int64_t)rs1, (int64_t)cs1);
+  } else if (op == 1) {
+    size_t m1 = (m + m0 - 1) / m0, n1 = (n + n0 - 1) / n0;
+    src_span = span4(m0, n0, m1, n1, (int64_t)rs0, (int64_t)cs0, (int64_t)rs1, (int64_t)cs1);
+    dst_span = span4(m, n, 1, 1, (int64_t)rs, (int64_t)cs, 0, 0);
+  } else {
+    src_span = span4(m, n, 1, 1, (int64_t)rs, 1, 0, 0);
+    dst_span = span4(n, m, 1, 1, (int64_t)rs0, 1, 0, 0); /* rs0 carries rsat */
+  }
+  int host_any = 0;
+  const void *dsrc = src;
+  void *ddst = dst;
+  if (!on_device(src)) {
+    host_any = 1;
+    dsrc = stage_in(WS_A, src, src_span * esize);
+    if (!dsrc) return;
+  }
+  out_stage_t out;
+  int dst_host = !on_device(dst);
+  if (dst_host) {
+    host_any = 1;
+    /* destinations may have gaps the operation must not disturb: round-trip the whole span */
+    if (!stage_out_begin(&out, dst, dst_span * esize, 0, 0, 0, 1)) return;
+    ddst = out.dev;
+  }
+  int rc;
+  if (op == 0)
+    rc = skl_b200_launch_pack(esize, m, n, dsrc, rs, cs, m0, n0, ddst, rs0, cs0, rs1, cs1, pad, g_ctx.stream);
+  else if (op == 1)
+    rc = skl_b200_launch_unpack(esize, m0, n0, dsrc, rs0, cs0, rs1, cs1, m, n, ddst, rs, cs, g_ctx.stream);
+  else
+    rc = skl_b200_launch_transpose(esize, m, n, dsrc, rs, ddst, rs0, g_ctx.stream);
+  if (!cuda_ok((cudaError_t)rc)) return;
+  if (dst_host && !stage_out_end(&out)) return;
+  finish(host_any);
+  end_call();
+}
+
+#define SKL_B200_DEF_PACK(BITS, TYPE)                                                                  \
+  void skl_pack_e##BITS##rc_e##BITS##rcprc_sm100a(size_t m, size_t n, const TYPE *SKL_RESTRICT src,    \
+                                                  size_t rs, size_t cs, size_t m0, size_t n0,          \
+                                                  TYPE *SKL_RESTRICT dst, size_t rs0, size_t cs0,      \
+                                                  size_t rs1, size_t cs1, TYPE pad) {                  \
+    run_relayout(0, sizeof(TYPE), m, n, src, dst, rs, cs, m0, n0, rs0, cs0, rs1, cs1, (uint32_t)pad);  \
+  }                                                                                                    \
+  void skl_transpose_e##BITS##_sm100a(size_t m, size_t n, const TYPE *SKL_RESTRICT a, size_t rsa,      \
+                                      TYPE *SKL_RESTRICT at, size_t rsat) {                            \
+    run_relayout(2, sizeof(TYPE), m, n, a, at, rsa, 1, 1, 1, rsat, 1, 0, 0, 0);                        \
+  }
+SKL_B200_DEF_PACK(8, uint8_t)
+SKL_B200_DEF_PACK(16, uint16_t)
+SKL_B200_DEF_PACK(32, uint32_t)
+
+void skl_unpack_e8rcprc_e8rc_sm100a(size_t m0, size_t n0, const uint8_t *SKL_RESTRICT src, size_t rs0,
+                                    size_t cs0, size_t rs1, size_t cs1, size_t m, size_t n,
+                                    uint8_t *SKL_RESTRICT dst, size_t rs, size_t cs) {
+  run_relayout(1, 1, m, n, src, dst, rs, cs, m0, n0, rs0, cs0, rs1, cs1, 0);
+}

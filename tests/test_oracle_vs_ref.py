@@ -1,0 +1,105 @@
+"""The oracle port against the compiled reference library on fresh seeded inputs.
+Skipped where oracle/_ref/libskl-ref.so was never built (the golden-vector test still runs)."""
+import numpy as np
+import pytest
+
+import helpers as H
+from oracle import pyoracle as orc
+
+P = orc._p
+pytestmark = pytest.mark.skipif(orc.ref() is None, reason="compiled reference library not present")
+
+SHAPES = [(1, 1, 1), (7, 7, 7), (17, 17, 17), (1, 64, 64), (64, 1, 64), (4, 5, 0), (15, 17, 31), (33, 129, 20),
+          (129, 33, 20), (63, 65, 64)]
+
+
+@pytest.mark.parametrize("t", [H.I8, H.BF16, H.F16, H.F8E4M3, H.F8E5M2])
+@pytest.mark.parametrize("shape", SHAPES)
+def test_gemm_rc(t, shape):
+    m, n, k = shape
+    g = H.rng(hash((t, shape)) & 0xFFFF)
+    for (rsa, csa), (rsb, csb), (rsc, csc) in [((max(k, 1), 1), (n, 1), (n, 1)), ((1, m), (1, max(k, 1)), (1, m)),
+                                               ((max(k, 1) + 2, 1), (n + 3, 1), (2 * n, 2))]:
+        A = H.Strided(t, m, k, rsa, csa, g, all_codes=True)
+        B = H.Strided(t, k, n, rsb, csb, g, all_codes=True)
+        C0 = H.Strided(H.I32 if t == H.I8 else H.F32, m, n, rsc, csc, g)
+        C1 = C0.copy()
+        orc.ref_gemm_rc(t, m, n, k, 2, A.view, rsa, csa, B.view, rsb, csb, 3, C0.view, rsc, csc)
+        orc.port_gemm_rc(t, t, m, n, k, 2, A.view, rsa, csa, B.view, rsb, csb, 3, C1.view, rsc, csc)
+        assert np.array_equal(C0.buf.view(np.uint8), C1.buf.view(np.uint8))
+
+
+def test_gemm_ex_reduces_to_reference_when_plain():
+    """With no scale vectors and fp32 output the extended epilogue is alpha*acc (+ beta*c)."""
+    g = H.rng(77)
+    m, n, k = 9, 11, 37
+    for t in (H.BF16, H.F16, H.F8E4M3, H.F8E5M2):
+        A = H.Strided(t, m, k, k, 1, g, all_codes=True)
+        B = H.Strided(t, k, n, n, 1, g, all_codes=True)
+        C0 = H.Strided(H.F32, m, n, n, 1, g)
+        C1 = C0.copy()
+        orc.ref_gemm_rc(t, m, n, k, 1.5, A.view, k, 1, B.view, n, 1, 0.5, C0.view, n, 1)
+        orc.port_gemm_ex(m, n, k, t, A.view, k, 1, t, B.view, n, 1, 1.5, None, None, 0.5, H.F32, C1.view, n, 1)
+        assert np.array_equal(C0.get(), C1.get())
+
+
+def test_cvt_random_and_boundaries():
+    g = H.rng(5)
+    x = np.concatenate([g.uniform(-512, 512, 20000), g.normal(0, 1e-3, 5000), g.uniform(-1e5, 1e5, 5000)]).astype(np.float32)
+    bits = g.integers(0, 2 ** 32, 50000, dtype=np.uint64).astype(np.uint32)
+    x = np.concatenate([x, bits.view(np.float32)])
+    xb = H.f32_to_bf16_bits(x)
+    ref, port = orc.ref(), orc.port()
+    for fmt, f in (("f8e4m3", H.F8E4M3), ("f8e5m2", H.F8E5M2)):
+        for sat in ("", "sat_"):
+            for scale in (1.0, 1.5, 0.37):
+                a = np.zeros(x.size, np.uint8)
+                b = np.zeros(x.size, np.uint8)
+                getattr(ref, f"skl_cvt_{sat}f32_{fmt}_ref")(P(a), P(x), scale, x.size)
+                port.orc_cvt_f32_f8(P(b), P(x), scale, x.size, f, int(sat != ""))
+                assert np.array_equal(a, b)
+                getattr(ref, f"skl_cvt_{sat}bf16_{fmt}_ref")(P(a), P(xb), scale, x.size)
+                port.orc_cvt_bf16_f8(P(b), P(xb), scale, x.size, f, int(sat != ""))
+                assert np.array_equal(a, b)
+
+
+def test_bf16_narrowing_matches_compiler_cast():
+    """orc_f32_to_bf16 against the reference's (__bf16) cast, reached through skl_cvt_f8*_bf16_ref for
+    the exact cases and through a bf16 GEMM with k = 1 for rounding cases."""
+    port = orc.port()
+    g = H.rng(9)
+    x = g.normal(0, 1, 4096).astype(np.float32)
+    got = np.array([port.orc_f32_to_bf16(float(v)) for v in x], dtype=np.uint16)
+    assert np.array_equal(got, H.f32_to_bf16_bits(x))
+
+
+@pytest.mark.parametrize("e", [8, 16, 32])
+def test_pack_unpack_transpose(e):
+    ref, port = orc.ref(), orc.port()
+    dt = {8: np.uint8, 16: np.uint16, 32: np.uint32}[e]
+    g = H.rng(100 + e)
+    for (m, n, m0, n0) in [(128, 128, 8, 8), (13, 10, 4, 3), (1, 1, 1, 1), (65, 3, 64, 1), (7, 9, 16, 16)]:
+        for src_cm in (0, 1):
+            for blk_cm in (0, 1):
+                src = g.integers(0, 255, size=m * n).astype(dt)
+                rs, cs = (1, m) if src_cm else (n, 1)
+                m1, n1 = -(-m // m0), -(-n // n0)
+                rs0, cs0 = (1, m0) if blk_cm else (n0, 1)
+                rs1, cs1 = n1 * m0 * n0, m0 * n0
+                d0 = np.full(m1 * n1 * m0 * n0, 0x11, dtype=dt)
+                d1 = d0.copy()
+                getattr(ref, f"skl_pack_e{e}rc_e{e}rcprc_ref")(m, n, P(src), rs, cs, m0, n0, P(d0), rs0, cs0, rs1, cs1, 0xFF)
+                port.orc_pack(e // 8, m, n, P(src), rs, cs, m0, n0, P(d1), rs0, cs0, rs1, cs1, 0xFF)
+                assert np.array_equal(d0, d1)
+                if e == 8:
+                    b0 = np.zeros(m * n, dtype=dt)
+                    b1 = np.zeros(m * n, dtype=dt)
+                    ref.skl_unpack_e8rcprc_e8rc_ref(m0, n0, P(d0), rs0, cs0, rs1, cs1, m, n, P(b0), rs, cs)
+                    port.orc_unpack(1, m0, n0, P(d0), rs0, cs0, rs1, cs1, m, n, P(b1), rs, cs)
+                    assert np.array_equal(b0, b1) and np.array_equal(b0, src)
+        a = g.integers(0, 255, size=m * (n + 1)).astype(dt)
+        t0 = np.zeros(n * (m + 2), dtype=dt)
+        t1 = t0.copy()
+        getattr(ref, f"skl_transpose_e{e}_ref")(m, n, P(a), n + 1, P(t0), m + 2)
+        port.orc_transpose(e // 8, m, n, P(a), n + 1, P(t1), m + 2)
+        assert np.array_equal(t0, t1)
