@@ -1,0 +1,136 @@
+"""GEMM parity on the GPU through the C ABI, shape classes after the reference's own suites
+(test/gemm/rvv/skl_gemm_i8_i8_i32_zve32x_x390.c:58-81, test/gemm/xsfmm/skl_gemm_i8c_i8_i32_xsfmm32a8i.c:61-89):
+minimal, odd, skinny, k = 0 with and without beta, tile edge -1/0/+1 (re-centred on this library's
+128 x 256 tile and 64 / 128-element k slabs), wide and tall, alpha = 2 / beta = 3."""
+import numpy as np
+import pytest
+
+import helpers as H
+import skl_b200 as S
+from gpu_common import check_gemm_rc
+
+pytestmark = pytest.mark.gpu
+ALL_T = [H.I8, H.BF16, H.F16, H.F8E4M3, H.F8E5M2]
+
+SMALL = [(1, 1, 0, 1, 0), (1, 1, 1, 1, 0), (7, 7, 7, 1, 0), (17, 17, 17, 1, 0), (1, 33, 31, 1, 0),
+         (33, 1, 31, 1, 0), (33, 33, 0, 1, 0), (16, 16, 0, 1, 1), (16, 16, 16, 1, 0), (15, 17, 31, 1, 0),
+         (33, 129, 32, 1, 0), (129, 33, 32, 1, 0), (32, 32, 32, 1, 1), (65, 65, 0, 2, 3), (65, 65, 33, 2, 3),
+         (0, 5, 3, 1, 0), (5, 0, 3, 1, 0)]
+
+
+@pytest.mark.parametrize("t", ALL_T)
+@pytest.mark.parametrize("m,n,k,alpha,beta", SMALL)
+def test_generic_path_small_shapes_device(skl, t, m, n, k, alpha, beta):
+    for layout in ("rrr", "crr", "rkp"):
+        check_gemm_rc(skl, t, m, n, k, layout, alpha, beta, where="device", path=S.PATH_GENERIC)
+
+
+@pytest.mark.parametrize("t", ALL_T)
+def test_host_pointers_are_staged(skl, t):
+    for (m, n, k, layout, beta) in [(33, 29, 40, "rrr", 0), (33, 29, 40, "rrp", 3), (20, 31, 16, "crc", 1),
+                                    (129, 260, 192, "rkr", 0)]:
+        check_gemm_rc(skl, t, m, n, k, layout, 2, beta, where="host", align=16 if m > 100 else 1)
+
+
+# tile-edge classes for the tensor-core kernel: (m, n, k)
+TC_SHAPES = [(127, 255, 63), (128, 256, 64), (129, 257, 65), (128, 256, 128), (256, 512, 129), (1, 256, 64),
+             (128, 16, 64), (130, 40, 1), (385, 300, 200), (64, 1000, 320), (300, 128, 1024)]
+
+
+@pytest.mark.parametrize("t", ALL_T)
+@pytest.mark.parametrize("layout", ["rkr", "rrr", "ckr", "crr", "rkc", "rrp"])
+def test_tensor_core_path(skl, t, layout):
+    """Every operand-major combination (A k-major / m-major, B k-major / n-major) and C layouts."""
+    for i, (m, n, k) in enumerate(TC_SHAPES):
+        alpha, beta = ((2, 3) if i % 3 == 0 else (1, 0))
+        check_gemm_rc(skl, t, m, n, k, layout, alpha, beta, where="device", path=S.PATH_TCGEN05, align=16,
+                      expect_path=S.PATH_TCGEN05, seed=i)
+
+
+@pytest.mark.parametrize("t", ALL_T)
+def test_tensor_core_matches_generic_bits_for_int8_and_bound_for_float(skl, t):
+    check_gemm_rc(skl, t, 512, 512, 1024, "rrr", 1, 0, where="device", path=0, expect_path=S.PATH_TCGEN05)
+
+
+def test_config1_int8_512x512x1024_bit_exact(skl):
+    """BASELINE config 1: A row-major, B K x N row-major, int32 out, alpha 1, beta 0; both pointer domains."""
+    for where in ("device", "host"):
+        check_gemm_rc(skl, H.I8, 512, 512, 1024, "rrr", 1, 0, where=where, seed=1, expect_path=S.PATH_TCGEN05)
+
+
+def test_unaligned_problem_falls_back_to_generic(skl):
+    used = check_gemm_rc(skl, H.BF16, 130, 70, 77, "rrr", 1, 0, where="device")
+    assert used == S.PATH_GENERIC
+
+
+def test_specialised_entry_points(skl):
+    """Row-major and column-major-A wrappers take SKL's shortened argument lists."""
+    import torch
+    from oracle import pyoracle as orc
+
+    g = H.rng(3)
+    m, n, k = 96, 80, 64
+    a = H.random_operand(H.I8, (m, k), g)
+    b = H.random_operand(H.I8, (k, n), g)
+    want = np.zeros((m, n), np.int32)
+    orc.port_gemm_rc(H.I8, H.I8, m, n, k, 1, a, k, 1, b, n, 1, 0, want, n, 1)
+    c = np.zeros((m, n), np.int32)
+    skl.skl_gemm_i8_i8_i32_sm100a(m, n, k, 1, S.ptr(a), k, S.ptr(b), n, 0, S.ptr(c), n)
+    S.check()
+    assert np.array_equal(c, want)
+    at = np.ascontiguousarray(a.T)  # column-major A: element (i, p) at at[p, i]
+    c2 = np.zeros((m, n), np.int32)
+    skl.skl_gemm_i8c_i8_i32_sm100a(m, n, k, 1, S.ptr(at), m, S.ptr(b), n, 0, S.ptr(c2), n)
+    S.check()
+    assert np.array_equal(c2, want)
+    for name, t in (("bf16", H.BF16), ("f16", H.F16)):
+        af = H.random_operand(t, (m, k), g)
+        bf = H.random_operand(t, (k, n), g)
+        wantf = np.zeros((m, n), np.float32)
+        orc.port_gemm_rc(t, t, m, n, k, 1.0, af, k, 1, bf, n, 1, 0.0, wantf, n, 1)
+        cf = np.zeros((m, n), np.float32)
+        getattr(skl, f"skl_gemm_{name}_{name}_f32_sm100a")(m, n, k, 1.0, S.ptr(af), k, S.ptr(bf), n, 0.0, S.ptr(cf), n)
+        S.check()
+        bound = H.skl_forward_bound(t, af, t, bf, 1.0, 0.0, None, k)
+        assert np.all(np.abs(cf.astype(np.float64) - wantf) <= bound)
+        cf2 = np.zeros((m, n), np.float32)
+        aft = np.ascontiguousarray(af.T)
+        getattr(skl, f"skl_gemm_{name}c_{name}_f32_sm100a")(m, n, k, 1.0, S.ptr(aft), m, S.ptr(bf), n, 0.0, S.ptr(cf2), n)
+        S.check()
+        assert np.all(np.abs(cf2.astype(np.float64) - wantf) <= bound)
+
+
+@pytest.mark.parametrize("t", ALL_T)
+def test_packed_operands(skl, t):
+    """Blocked 4-D operands (all block counts up to 3 x 3, k1 0..3), block-column-major C."""
+    from oracle import pyoracle as orc
+
+    P = orc._p
+    name = {H.I8: "i8", H.BF16: "bf16", H.F16: "f16", H.F8E4M3: "f8e4m3", H.F8E5M2: "f8e5m2"}[t]
+    tc = H.I32 if t == H.I8 else H.F32
+    fn = getattr(skl, f"skl_gemm_{name}rcprc_{name}rcprc_{'i32' if t == H.I8 else 'f32'}rcprc_sm100a")
+    g = H.rng(11)
+    for (m0, n0, k0) in [(4, 3, 2), (8, 8, 4)]:
+        for m1 in (1, 3):
+            for n1 in (1, 2):
+                for k1 in (0, 1, 3):
+                    a = H.random_operand(t, (max(1, m1 * k1 * m0 * k0),), g, True)
+                    b = H.random_operand(t, (max(1, k1 * n1 * k0 * n0),), g, True)
+                    c = H.random_operand(tc, (m1 * n1 * m0 * n0 + 9,), g)
+                    sa = (k0, 1, max(k1, 1) * m0 * k0, m0 * k0)
+                    sb = (1, k0, n1 * k0 * n0, k0 * n0)
+                    sc = (1, m0, m0 * n0, m1 * m0 * n0)  # column-major inside and between blocks
+                    want = c.copy()
+                    if t == H.I8:
+                        orc.port().orc_gemm_packed_i8_i32(m0, n0, k0, m1, n1, k1, 2, P(a), *sa, P(b), *sb, 3, P(want), *sc)
+                    else:
+                        orc.port().orc_gemm_packed_fp_f32(m0, n0, k0, m1, n1, k1, 2.0, t, P(a), *sa, t, P(b), *sb, 3.0,
+                                                         P(want), *sc)
+                    got = c.copy()
+                    fn(m0, n0, k0, m1, n1, k1, 2, S.ptr(a), *sa, S.ptr(b), *sb, 3, S.ptr(got), *sc)
+                    S.check()
+                    if t == H.I8:
+                        assert np.array_equal(got, want)
+                    else:
+                        assert np.allclose(got, want, rtol=1e-5, atol=1e-5)
+                        assert np.array_equal(got[-9:], want[-9:])

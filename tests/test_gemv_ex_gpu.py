@@ -1,0 +1,96 @@
+"""Skinny int8 kernel and the extended epilogue on the GPU, through the C ABI."""
+import numpy as np
+import pytest
+
+import helpers as H
+import skl_b200 as S
+from gpu_common import DeviceBuf, check_gemm_rc
+from oracle import pyoracle as orc
+
+pytestmark = pytest.mark.gpu
+P = orc._p
+
+
+@pytest.mark.parametrize("m", [1, 2, 3, 4, 7, 8, 13, 16])
+def test_gemv_int32_bit_exact(skl, m):
+    """Weights "[N][K]" (layout 'k'), activations row-major; int32 out with alpha/beta."""
+    for (n, k, alpha, beta) in [(14336, 4096, 1, 0), (1000, 512, 2, 3), (5, 16, 1, 0), (257, 4096, 1, 1),
+                                (4099, 1024, 1, 0)]:
+        used = check_gemm_rc(skl, H.I8, m, n, k, "rkr", alpha, beta, where="device", seed=m)
+        assert used == S.PATH_GEMV
+
+
+def ex_case(skl, m, n, k, ta, tb, tc, layout, alpha, beta, use_rs, use_cs, where, seed, force=0, amp=1.0):
+    from gpu_common import layout_strides
+
+    g = H.rng(seed)
+    (rsa, csa), (rsb, csb), (rsc, csc) = layout_strides(layout, m, n, k, 16)
+    A = H.Strided(ta, m, k, rsa, csa, g, all_codes=True)
+    B = H.Strided(tb, k, n, rsb, csb, g, all_codes=True)
+    cvals = None
+    if tc == H.F8E4M3:
+        cvals = H.random_operand(H.F8E4M3, (m, n), g)
+    C = H.Strided(tc, m, n, rsc, csc, g, fill=cvals)
+    rs = (g.uniform(0.5, 1.5, m) * amp).astype(np.float32) if use_rs else None
+    cs = (g.uniform(0.5, 1.5, n) * 1e-2).astype(np.float32) if use_cs else None
+    want = C.copy()
+    orc.port_gemm_ex(m, n, k, ta, A.view, rsa, csa, tb, B.view, rsb, csb, alpha, rs, cs, beta, tc, want.view, rsc, csc)
+    before = C.copy()
+    skl.skl_b200_force_path(force)
+    try:
+        if where == "host":
+            skl.skl_gemm_ex_sm100a(m, n, k, ta, S.ptr(A.view), rsa, csa, tb, S.ptr(B.view), rsb, csb, alpha, S.ptr(rs),
+                                   S.ptr(cs), beta, tc, S.ptr(C.view), rsc, csc)
+            S.check()
+            after = C.buf
+        else:
+            import torch
+
+            da, db, dc = DeviceBuf(A.buf), DeviceBuf(B.buf), DeviceBuf(C.buf)
+            drs = torch.from_numpy(rs).cuda() if use_rs else None
+            dcs = torch.from_numpy(cs).cuda() if use_cs else None
+            skl.skl_gemm_ex_sm100a(m, n, k, ta, da.ptr(A.off), rsa, csa, tb, db.ptr(B.off), rsb, csb, alpha, S.ptr(drs),
+                                   S.ptr(dcs), beta, tc, dc.ptr(C.off), rsc, csc)
+            S.check()
+            torch.cuda.synchronize()
+            after = dc.back()
+    finally:
+        skl.skl_b200_force_path(0)
+    H.assert_untouched_outside(before, after, "C")
+    return A, B, before, want, after[C.idx()], rs, cs
+
+
+@pytest.mark.parametrize("m", [1, 4, 16])
+def test_config4_decode_gemv_dequantised(skl, m):
+    """BASELINE config 4 at full size: int8 weights 14336 x 4096 with per-row scales, int8 activations with
+    per-row scale, fp32 out = ((float)acc * s_x[i]) * s_w[j].  The accumulator is exact, so the result
+    must equal the oracle's bit for bit."""
+    for where in ("device", "host"):
+        _, _, _, want, got, _, _ = ex_case(skl, m, 14336, 4096, H.I8, H.I8, H.F32, "rkr", 1.0, 0.0, True, True, where, 40 + m)
+        assert skl.skl_b200_last_path() == S.PATH_GEMV
+        assert np.array_equal(got.view(np.uint32), want.get().view(np.uint32))
+
+
+@pytest.mark.parametrize("pair", [(H.I8, H.I8), (H.BF16, H.BF16), (H.F16, H.F16), (H.F8E4M3, H.F8E4M3),
+                                  (H.F8E5M2, H.F8E4M3), (H.F8E4M3, H.F8E5M2), (H.BF16, H.F8E4M3), (H.BF16, H.F8E5M2)])
+@pytest.mark.parametrize("tc", [H.F32, H.BF16, H.F16, H.F8E4M3])
+def test_extended_epilogue_all_pairs_and_outputs(skl, pair, tc):
+    ta, tb = pair
+    for (m, n, k, layout, beta, force) in [(130, 260, 192, "rkr", 0.0, 0), (130, 260, 192, "rrr", 0.5, 0),
+                                           (33, 17, 40, "rrp", 0.5, S.PATH_GENERIC), (64, 96, 128, "ckc", 0.0, 0)]:
+        A, B, before, want, got, rs, cs = ex_case(skl, m, n, k, ta, tb, tc, layout, 1.5, beta, True, True, "device",
+                                                  m + k, force, amp=(1.0 if ta == H.I8 else 100.0))
+        ref = H.to_f32(tc, want.get()).astype(np.float64)
+        out = H.to_f32(tc, got).astype(np.float64)
+        if ta == H.I8:
+            assert np.array_equal(got, want.get())  # integer accumulator: the whole chain is exact
+            continue
+        # float pairs: error of the accumulator (reference's bound) scaled through the epilogue, plus
+        # one unit in the last place of the output type
+        scale = np.abs(1.5 * rs[:, None].astype(np.float64) * cs[None, :].astype(np.float64))
+        bound = H.skl_forward_bound(ta, A.get(), tb, B.get(), 1.0, 0.0, None, k) * scale * 2
+        ulp = {H.F32: 2.0 ** -23, H.BF16: 2.0 ** -7, H.F16: 2.0 ** -10, H.F8E4M3: 2.0 ** -3}[tc]
+        tol = bound + ulp * np.maximum(np.abs(ref), 2.0 ** -9 if tc == H.F8E4M3 else 0.0) + 1e-30
+        err = np.where(out == ref, 0.0, np.abs(out - ref))  # equal infinities count as agreement
+        tol = np.where(np.isfinite(tol), tol, np.inf)
+        assert np.all(err <= tol), float(np.nanmax(err - tol))
