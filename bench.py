@@ -1,0 +1,451 @@
+#!/usr/bin/env python
+"""Benchmark of the sm_100a gemm path through the library's C ABI.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--no-also]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
+
+Headline workload ("c5", BASELINE configs[4]): the LLM MLP projection
+    C[16384, 14336] (bf16) = X[16384, 4096] (bf16) . W[4096, 14336] (fp8 E4M3, per-column fp32 scale)
+with W and C partitioned by columns over the N ranks (X replicated, no data-path collective, outputs
+left sharded).  One step = one call of skl_gemm_ex_sm100a per rank: the exact fp8->bf16 widening of the
+rank's W slice followed by the tcgen05 bf16 GEMM with the per-column scale and the bf16 narrowing fused
+into its epilogue.  `value` is whole-job TFLOP/s (2*M*N*K per step over the slowest rank's device time)
+with operands resident in HBM; `e2e` is the same call handed pinned HOST buffers, so the host->device
+copies of X, W, scales and the device->host copy of C are inside the timed region.  The total work is
+fixed as N grows ("strong" scaling).  Inputs are seeded synthetic tensors of the configured
+shapes and distributions; every operand set is larger than the 126 MB L2.
+
+At N = 1 the line also carries, under "also", short measurements of the other BASELINE configs
+(int8 8192^3, bf16/fp16 4096^3, fp8 8192^3, the decode GEMV at M = 1/4/16) and a `cpu_baseline`:
+the reference's scalar routines (oracle/_ref when built, else the oracle port) timed on the host cores
+on a bounded row sample of the same workload.
+
+--impl reference times only that CPU path (rank 0; other ranks exit at once).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+M_C5, K_C5, N_C5 = 16384, 4096, 14336
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as fh:
+            d = json.load(fh)
+        return {"hbm_gbs": d["hbm_gbs"], "bf16_burst": d["bf16_tflops"],
+                "bf16_sustained": d["bf16_tflops_sustained"], "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_burst": 1590.0, "bf16_sustained": 1400.0, "source": "fallback"}
+
+
+# ----------------------------------------------------------------------------- clocks (read-only NVML)
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU from a background thread while a region runs."""
+
+    def __init__(self, index: int, period_s: float = 0.02):
+        self.index, self.period, self.samples, self.reasons = index, period_s, [], set()
+        self.max_mhz = None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def _run(self):
+        nv = self.nv
+        names = {
+            getattr(nv, "nvmlClocksThrottleReasonHwSlowdown", 0x8): "hw_slowdown",
+            getattr(nv, "nvmlClocksThrottleReasonHwThermalSlowdown", 0x40): "hw_thermal_slowdown",
+            getattr(nv, "nvmlClocksThrottleReasonSwThermalSlowdown", 0x20): "sw_thermal_slowdown",
+            getattr(nv, "nvmlClocksThrottleReasonSwPowerCap", 0x4): "sw_power_cap",
+            getattr(nv, "nvmlClocksThrottleReasonHwPowerBrakeSlowdown", 0x80): "hw_power_brake",
+        }
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                for bit, name in names.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            self._stop.wait(self.period)
+
+    def __enter__(self):
+        if self.nv is not None:
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join()
+
+    def summary(self):
+        s = sorted(self.samples)
+        return {"sm_mhz": (s[len(s) // 2] if s else None), "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(s)}
+
+
+# ----------------------------------------------------------------------------- CPU baseline (checker only)
+def cpu_reference_sample(rows_per_thread: int | None, budget_s: float, threads: int):
+    """Times the reference's scalar path on a row sample of the c5 workload.
+
+    The sample is `threads * rows_per_thread` rows of C at full N and K: widening of W with
+    skl_cvt_f8e4m3_bf16_ref, then skl_gemm_bf16rc_bf16rc_f32rc_ref on each thread's row slab (rows are
+    independent, arithmetic unchanged; W is handed over k-contiguous, which is bit-identical and faster
+    for the scalar loop).  Returns (tflops, seconds, rows, kind)."""
+    import numpy as np
+
+    from oracle import pyoracle as orc
+
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import helpers as H
+
+    ref = orc.ref()
+    kind = "reference" if ref is not None else "port"
+    g = H.rng(5)
+    n, k = N_C5, K_C5
+    w8 = H.random_operand(H.F8E4M3, (n, k), g)  # [N][K], k contiguous
+    wide = np.zeros((n, k), np.uint16)
+
+    def widen(i0, rows):
+        if ref is not None:
+            ref.skl_cvt_f8e4m3_bf16_ref(orc._p(wide[i0:]), orc._p(w8[i0:]), rows * k)
+        else:
+            orc.port().orc_cvt_f8_bf16(orc._p(wide[i0:]), orc._p(w8[i0:]), rows * k, H.F8E4M3)
+
+    def run(rows_per_thread):
+        rows = rows_per_thread * threads
+        x = H.random_operand(H.BF16, (rows, k), g)
+        c = np.zeros((rows, n), np.float32)
+
+        def slab(i0, r):
+            if ref is not None:
+                orc.ref_gemm_rc(H.BF16, r, n, k, 1.0, x[i0:], k, 1, wide, 1, k, 0.0, c[i0:], n, 1)
+            else:
+                orc.port_gemm_rc(H.BF16, H.BF16, r, n, k, 1.0, x[i0:], k, 1, wide, 1, k, 0.0, c[i0:], n, 1)
+
+        t0 = time.perf_counter()
+        orc.rows_in_parallel(widen, n, threads)
+        orc.rows_in_parallel(slab, rows, threads)
+        return time.perf_counter() - t0, rows
+
+    if rows_per_thread is None:
+        t1, _ = run(1)  # calibration pass: one row per thread
+        rows_per_thread = max(1, min(64, int(budget_s / max(t1, 1e-3))))
+        if rows_per_thread == 1:
+            return 2.0 * threads * n * k / t1 / 1e12, t1, threads, kind, 1
+    t, rows = run(rows_per_thread)
+    return 2.0 * rows * n * k / t / 1e12, t, rows, kind, rows_per_thread
+
+
+def reference_arm(args, rank: int, world: int) -> None:
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    total_budget = 150.0
+    per_step = max(0.5, min(4.0, total_budget / max(1, args.steps + args.warmup + 1)))
+    tf, t, rows, kind, rpt = cpu_reference_sample(None, per_step, threads)  # calibration + first sample
+    for _ in range(max(0, args.warmup - 1)):
+        cpu_reference_sample(rpt, per_step, threads)
+    times = []
+    for _ in range(args.steps):
+        tf_i, t_i, rows, kind, _ = cpu_reference_sample(rpt, per_step, threads)
+        times.append(t_i)
+    ms = 1e3 * sum(times) / len(times)
+    value = 2.0 * rows * N_C5 * K_C5 / (ms * 1e-3) / 1e12
+    sample = (f"{rows} of {M_C5} rows of C at full N={N_C5}, K={K_C5} per step ({rpt} rows per thread), "
+              "fp8->bf16 widening of W included; rate is independent of the row count")
+    line = {
+        "impl": "reference", "metric": "gemm_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": workload_config(args.gpus),
+        "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": threads, "kind": kind, "sample": sample},
+        "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(n_gpus: int):
+    return {"workload": "c5: bf16 X[16384x4096] . fp8-E4M3 W[4096x14336] with per-column fp32 scales -> bf16 C, "
+                        "W and C column-sharded over the ranks, X replicated",
+            "m": M_C5, "k": K_C5, "n": N_C5, "n_per_gpu": N_C5 // max(1, n_gpus),
+            "l2": "operands larger than L2 (X 128 MiB + W slice + C slice)", "parallelism": f"n-shard x{n_gpus}"}
+
+
+# ----------------------------------------------------------------------------- device helpers
+def time_steps(torch, fn, steps: int, barrier=None):
+    """K back-to-back calls between two events on the current stream, synchronised on both sides."""
+    torch.cuda.synchronize()
+    if barrier:
+        barrier()
+        torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    if barrier:
+        barrier()
+    return e0.elapsed_time(e1)  # ms
+
+
+def also_configs(torch, S, lib, peaks, steps=20, warmup=3):
+    """Short device-resident measurements of the other BASELINE configs (1 GPU)."""
+    import numpy as np
+
+    out = {}
+    dev = "cuda"
+    g = torch.Generator(device=dev)
+    g.manual_seed(1234)
+
+    def gemm_rate(tag, m, n, k, ta, tb, tc, a, b, c, b_kmajor, alpha=1.0):
+        rsb, csb = (1, k) if b_kmajor else (n, 1)
+
+        def call():
+            lib.skl_gemm_ex_sm100a(m, n, k, ta, a.data_ptr(), k, 1, tb, b.data_ptr(), rsb, csb, alpha, None, None, 0.0,
+                                   tc, c.data_ptr(), n, 1)
+
+        for _ in range(warmup):
+            call()
+        S.check()
+        ms = time_steps(torch, call, steps) / steps
+        out[tag] = {"tflops": round(2.0 * m * n * k / (ms * 1e-3) / 1e12, 1), "ms": round(ms, 4)}
+
+    # int8 8192^3 (the perf companion of config 1), int32 out through the SKL entry point
+    m = n = k = 8192
+    a = torch.randint(-128, 128, (m, k), dtype=torch.int8, device=dev, generator=g)
+    b = torch.randint(-128, 128, (k, n), dtype=torch.int8, device=dev, generator=g)
+    c = torch.empty((m, n), dtype=torch.int32, device=dev)
+
+    def call_i8():
+        lib.skl_gemm_i8_i8_i32_sm100a(m, n, k, 1, a.data_ptr(), k, b.data_ptr(), n, 0, c.data_ptr(), n)
+
+    for _ in range(warmup):
+        call_i8()
+    S.check()
+    ms = time_steps(torch, call_i8, steps) / steps
+    out["int8_8192_i32out"] = {"tops": round(2.0 * m * n * k / (ms * 1e-3) / 1e12, 1), "ms": round(ms, 4)}
+    del c
+
+    # fp8 8192^3 -> bf16 (config 3), both operand-format runs, operands reuse the int8 buffers' bytes
+    a8, b8 = a.view(torch.uint8) & 0x77, b.view(torch.uint8) & 0x77  # finite codes only
+    c16 = torch.empty((m, n), dtype=torch.bfloat16, device=dev)
+    gemm_rate("fp8_e4m3xe4m3_8192_bf16out", m, n, k, S.F8E4M3, S.F8E4M3, S.BF16, a8, b8, c16, False, 1e-3)
+    gemm_rate("fp8_e5m2xe4m3_8192_bf16out", m, n, k, S.F8E5M2, S.F8E4M3, S.BF16, a8, b8, c16, False, 1e-6)
+    del a, b, a8, b8, c16
+
+    # bf16 / fp16 4096^3 -> bf16 / fp16 (config 2)
+    m = n = k = 4096
+    for tag, tdt, code in (("bf16", torch.bfloat16, S.BF16), ("fp16", torch.float16, S.F16)):
+        a = (torch.randn((m, k), device=dev, generator=g) / 64.0).to(tdt)
+        b = (torch.randn((k, n), device=dev, generator=g) / 64.0).to(tdt)
+        c = torch.empty((m, n), dtype=tdt, device=dev)
+        gemm_rate(f"{tag}_4096_{tag}out", m, n, k, code, code, code, a, b, c, False)
+    del a, b, c
+
+    # decode GEMV (config 4): rotate over weight copies totalling > 2x L2 so every pass streams from HBM
+    n, k = 14336, 4096
+    copies = 6
+    w = torch.randint(-127, 128, (copies, n, k), dtype=torch.int8, device=dev, generator=g)
+    sw = torch.rand((n,), device=dev, generator=g) * 1e-2 + 5e-3
+    for mm in (1, 4, 16):
+        x = torch.randint(-127, 128, (mm, k), dtype=torch.int8, device=dev, generator=g)
+        sx = torch.rand((mm,), device=dev, generator=g) + 0.5
+        y = torch.empty((mm, n), dtype=torch.float32, device=dev)
+        idx = [0]
+
+        def call():
+            wi = w[idx[0] % copies]
+            idx[0] += 1
+            lib.skl_gemm_ex_sm100a(mm, n, k, S.I8, x.data_ptr(), k, 1, S.I8, wi.data_ptr(), 1, k, 1.0, sx.data_ptr(),
+                                   sw.data_ptr(), 0.0, S.F32, y.data_ptr(), n, 1)
+
+        for _ in range(warmup):
+            call()
+        S.check()
+        reps = 60
+        ms = time_steps(torch, call, reps) / reps
+        nbytes = n * k + mm * k + 4 * (n + mm) + 4 * mm * n
+        gbs = nbytes / (ms * 1e-3) / 1e9
+        out[f"gemv_i8_m{mm}"] = {"gbs": round(gbs, 1), "us": round(ms * 1e3, 2),
+                                 "frac_of_hbm_peak": round(gbs / peaks["hbm_gbs"], 3)}
+    return out
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=30)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-also", action="store_true", help="skip the other configs and the CPU baseline")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+
+    if args.impl == "reference":
+        reference_arm(args, rank, world)
+        return
+
+    import numpy as np
+    import torch
+
+    import skl_b200 as S
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the library has no CPU path")
+    torch.cuda.set_device(local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+
+        dist = dist_mod
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    barrier = (lambda: dist.barrier()) if dist else None
+
+    lib = S.lib()  # raises if the CUDA library is not built: no fallback
+    lib.skl_b200_set_stream(torch.cuda.current_stream().cuda_stream)
+    peaks = measured_peaks()
+
+    # ---------------- inputs (seed 5): X ~ N(0,1) bf16; W ~ N(0, 0.02), per-column scale amax/448, E4M3
+    m, k, n_total = M_C5, K_C5, N_C5
+    col0, ncols = S.shard_columns(n_total, world, rank, 256)
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(5)
+    x = torch.randn((m, k), device="cuda", generator=gen).to(torch.bfloat16)
+    w32_full = torch.randn((k, n_total), device="cuda", generator=gen) * 0.02
+    w32 = w32_full[:, col0:col0 + ncols].contiguous()
+    del w32_full
+    scale = (w32.abs().amax(dim=0) / 448.0).clamp_min(1e-30).contiguous()
+    wq_in = (w32 / scale[None, :]).contiguous()
+    w8 = torch.empty((k, ncols), dtype=torch.uint8, device="cuda")
+    lib.skl_cvt_sat_f32_f8e4m3_sm100a(w8.data_ptr(), wq_in.data_ptr(), 1.0, k * ncols)
+    S.check()
+    del w32, wq_in
+    c = torch.empty((m, ncols), dtype=torch.bfloat16, device="cuda")
+
+    def step():
+        lib.skl_gemm_ex_sm100a(m, ncols, k, S.BF16, x.data_ptr(), k, 1, S.F8E4M3, w8.data_ptr(), ncols, 1, 1.0, None,
+                               scale.data_ptr(), 0.0, S.BF16, c.data_ptr(), ncols, 1)
+
+    lib.skl_b200_set_async(0)
+    step()
+    S.check()
+    assert lib.skl_b200_last_path() == S.PATH_TCGEN05, "workload did not run on the tcgen05 kernel"
+    launches_per_step = lib.skl_b200_last_launch_count()
+    lib.skl_b200_set_async(1)
+    for _ in range(args.warmup):
+        step()
+    lib.skl_b200_synchronize()
+    S.check()
+
+    # ---------------- timed region, device-resident operands
+    lib.skl_b200_profile_begin(args.steps)
+    with ClockSampler(local_rank) as clk:
+        ms_total = time_steps(torch, step, args.steps, barrier)
+    kernel_ms = S.C.c_double(0.0)
+    recorded = lib.skl_b200_profile_end(S.C.byref(kernel_ms))
+    lib.skl_b200_synchronize()
+    S.check()
+    t = torch.tensor([ms_total], device="cuda", dtype=torch.float64)
+    if dist:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_step = float(t.item()) / args.steps
+    flops_step = 2.0 * m * n_total * k
+    value = flops_step / (ms_step * 1e-3) / 1e12
+
+    # ---------------- end to end: pinned host buffers through the same call
+    lib.skl_b200_set_async(0)
+    xh = x.cpu().pin_memory()
+    w8h = w8.cpu().pin_memory()
+    sh = scale.cpu().pin_memory()
+    ch = torch.empty((m, ncols), dtype=torch.bfloat16).pin_memory()
+
+    def step_host():
+        lib.skl_gemm_ex_sm100a(m, ncols, k, S.BF16, xh.data_ptr(), k, 1, S.F8E4M3, w8h.data_ptr(), ncols, 1, 1.0, None,
+                               sh.data_ptr(), 0.0, S.BF16, ch.data_ptr(), ncols, 1)
+
+    e2e_steps = max(3, min(args.steps, 8))
+    for _ in range(2):
+        step_host()
+    S.check()
+    ms_e2e_total = time_steps(torch, step_host, e2e_steps, barrier)
+    S.check()
+    t = torch.tensor([ms_e2e_total], device="cuda", dtype=torch.float64)
+    if dist:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_e2e = float(t.item()) / e2e_steps
+    e2e_value = flops_step / (ms_e2e * 1e-3) / 1e12
+    same = bool(torch.equal(ch.cuda(), c))
+    h2d = xh.numel() * 2 + w8h.numel() + sh.numel() * 4
+    d2h = ch.numel() * 2
+    del xh, w8h, sh, ch
+
+    # ---------------- roofline of the dominant kernel (the tcgen05 GEMM), from the library's event pairs
+    kern_ms = kernel_ms.value / max(1, recorded)
+    achieved = 2.0 * m * ncols * k / (kern_ms * 1e-3) / 1e12 if kern_ms > 0 else None
+    region_s = ms_total * 1e-3
+    peak_kind = "sustained" if region_s >= 2.0 else "burst"
+    peak = peaks["bf16_sustained"] if peak_kind == "sustained" else peaks["bf16_burst"]
+    roofline = {"bound": "tensor", "kernel": "gemm_tc_kernel<256, f16> (bf16 x bf16 -> fp32 in TMEM -> bf16)",
+                "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": (achieved / peak if achieved else None),
+                "peak_kind": f"{peak_kind}, of {peaks['source']}", "kernel_ms": kern_ms,
+                "traffic": None}
+
+    line = {
+        "metric": "gemm_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": workload_config(world),
+        "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                "ms_per_step": ms_e2e, "steps": e2e_steps, "matches_device_run": same},
+        "gpu_launches": launches_per_step * args.steps,
+        "launches_per_step": launches_per_step,
+        "clocks": clk.summary(),
+        "roofline": roofline,
+    }
+
+    if world == 1 and not args.no_also:
+        lib.skl_b200_set_async(1)
+        del x, w8, c
+        torch.cuda.empty_cache()
+        line["also"] = also_configs(torch, S, lib, peaks)
+        lib.skl_b200_synchronize()
+        lib.skl_b200_set_async(0)
+        threads = os.cpu_count() or 1
+        tf, secs, rows, kind, rpt = cpu_reference_sample(None, 3.0, threads)
+        line["cpu_baseline"] = {"value": tf, "unit": "TFLOP/s", "cores": threads, "kind": kind,
+                                "sample": f"{rows} of {M_C5} rows of C at full N and K ({rpt} per thread, {secs:.1f} s), "
+                                          "widening of W included; rate is independent of the row count"}
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if dist:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

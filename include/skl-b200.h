@@ -99,6 +99,12 @@ typedef enum skl_b200_path {
 SKL_FUNC skl_b200_path_t skl_b200_last_path(void);
 /* Number of kernels the calling thread's last library call launched. */
 SKL_FUNC int skl_b200_last_launch_count(void);
+/* Kernel timing for benchmarks: after skl_b200_profile_begin(n) the next n GEMM calls of this thread
+ * bracket their main kernel (not staging copies or the fp8-widening pre-pass) with CUDA events on the
+ * launch stream; skl_b200_profile_end waits for the stream, stores the summed kernel time in
+ * *total_ms and returns how many calls were recorded. */
+SKL_FUNC void skl_b200_profile_begin(int max_calls);
+SKL_FUNC int skl_b200_profile_end(double *total_ms);
 /* Restricts GEMM dispatch (debug/testing): 0 = automatic, else force one skl_b200_path_t where legal. */
 SKL_FUNC void skl_b200_force_path(int path);
 

@@ -43,6 +43,8 @@ SIGNATURES = {
     "skl_b200_last_path": ([], _I),
     "skl_b200_last_launch_count": ([], _I),
     "skl_b200_force_path": ([_I], None),
+    "skl_b200_profile_begin": ([_I], None),
+    "skl_b200_profile_end": ([C.POINTER(C.c_double)], _I),
     "skl_b200_shard_columns": ([_SZ, _SZ, _SZ, _SZ, C.POINTER(_SZ), C.POINTER(_SZ)], None),
     "skl_gemm_i8rc_i8rc_i32rc_sm100a": (_GEMM_RC_I, None),
     "skl_gemm_bf16rc_bf16rc_f32rc_sm100a": (_GEMM_RC_F, None),

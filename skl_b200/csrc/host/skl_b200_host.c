@@ -14,6 +14,7 @@
 
 #include <cuda_runtime_api.h>
 #include <stdio.h>
+#include <stdlib.h>
 #include <string.h>
 
 /* ------------------------------------------------------------------ per-thread context */
@@ -36,9 +37,12 @@ typedef struct {
   int device;           /* device the cached resources belong to, -1 = none */
   uint32_t *dev_status; /* mapped pinned host words written by kernels on a bounded-wait expiry */
   workspace_t ws[WS_COUNT];
+  /* optional timing of the main GEMM kernel of each call: pairs of events on the launch stream */
+  cudaEvent_t *prof_ev;
+  int prof_cap, prof_used;
 } ctx_t;
 
-static __thread ctx_t g_ctx = {0, 0, SKL_B200_OK, {0}, SKL_B200_PATH_NONE, 0, 0, -1, 0, {{0, 0}}};
+static __thread ctx_t g_ctx = {0, 0, SKL_B200_OK, {0}, SKL_B200_PATH_NONE, 0, 0, -1, 0, {{0, 0}}, 0, 0, 0};
 
 static void set_err(skl_b200_status_t s) {
   if (g_ctx.status == SKL_B200_OK) g_ctx.status = s;
@@ -178,6 +182,43 @@ void skl_b200_set_async(int enabled) { g_ctx.async = enabled != 0; }
 skl_b200_path_t skl_b200_last_path(void) { return g_ctx.last_path; }
 int skl_b200_last_launch_count(void) { return g_ctx.last_launches; }
 void skl_b200_force_path(int path) { g_ctx.force_path = path; }
+
+void skl_b200_profile_begin(int max_calls) {
+  if (g_ctx.prof_ev) {
+    for (int i = 0; i < 2 * g_ctx.prof_cap; ++i) (void)cudaEventDestroy(g_ctx.prof_ev[i]);
+    free(g_ctx.prof_ev);
+    g_ctx.prof_ev = 0;
+  }
+  g_ctx.prof_cap = 0;
+  g_ctx.prof_used = 0;
+  if (max_calls <= 0) return;
+  g_ctx.prof_ev = (cudaEvent_t *)calloc((size_t)(2 * max_calls), sizeof(cudaEvent_t));
+  if (!g_ctx.prof_ev) return;
+  for (int i = 0; i < 2 * max_calls; ++i) {
+    if (cudaEventCreate(&g_ctx.prof_ev[i]) != cudaSuccess) {
+      (void)cudaGetLastError();
+      for (int j = 0; j < i; ++j) (void)cudaEventDestroy(g_ctx.prof_ev[j]);
+      free(g_ctx.prof_ev);
+      g_ctx.prof_ev = 0;
+      return;
+    }
+  }
+  g_ctx.prof_cap = max_calls;
+}
+
+int skl_b200_profile_end(double *total_ms) {
+  double sum = 0.0;
+  int n = g_ctx.prof_used;
+  (void)cudaStreamSynchronize((cudaStream_t)g_ctx.stream);
+  for (int i = 0; i < n; ++i) {
+    float ms = 0.0f;
+    if (cudaEventElapsedTime(&ms, g_ctx.prof_ev[2 * i], g_ctx.prof_ev[2 * i + 1]) == cudaSuccess) sum += ms;
+    else (void)cudaGetLastError();
+  }
+  if (total_ms) *total_ms = sum;
+  skl_b200_profile_begin(0);
+  return n;
+}
 
 void skl_b200_synchronize(void) {
   g_ctx.status = SKL_B200_OK;
@@ -379,6 +420,8 @@ static void run_gemm(skl_b200_gemm_args *g) {
       path = SKL_B200_PATH_TCGEN05;
   }
   int rc = 0;
+  const int prof = g_ctx.prof_ev && g_ctx.prof_used < g_ctx.prof_cap;
+  if (prof) (void)cudaEventRecord(g_ctx.prof_ev[2 * g_ctx.prof_used], (cudaStream_t)g_ctx.stream);
   if (path == SKL_B200_PATH_GEMV) {
     rc = skl_b200_launch_gemv_i8(g, g_ctx.stream);
   } else if (path == SKL_B200_PATH_TCGEN05) {
@@ -387,6 +430,10 @@ static void run_gemm(skl_b200_gemm_args *g) {
     rc = skl_b200_launch_gemm_tc(g, st, g_ctx.stream);
   } else {
     rc = skl_b200_launch_gemm_generic(g, g_ctx.stream);
+  }
+  if (prof) {
+    (void)cudaEventRecord(g_ctx.prof_ev[2 * g_ctx.prof_used + 1], (cudaStream_t)g_ctx.stream);
+    g_ctx.prof_used++;
   }
   g_ctx.last_path = (skl_b200_path_t)path;
   if (!cuda_ok((cudaError_t)rc)) return;
