@@ -233,6 +233,32 @@ SKL_FUNC void skl_gemm_ex_sm100a(size_t m, size_t n, size_t k, skl_b200_dtype_t 
                                  const float *col_scale, float beta, skl_b200_dtype_t tc, void *c,
                                  size_t rsc, size_t csc);
 
+/* ------------------------------------------------------------------ GEMM without device allocation
+ * No counterpart in the reference: SKL's kernels never allocate because they never need scratch
+ * memory, whereas the bf16 x fp8 case above widens B into a workspace obtained with cudaMalloc.
+ * Callers that cannot tolerate that -- a latency-bound serving loop (cudaMalloc / cudaFree stall the
+ * whole device), or a process whose free device memory is already owned by another allocator's pool,
+ * where a cudaMalloc from this library would fail -- use this entry instead.  It computes exactly what
+ *     skl_gemm_ex_sm100a(m, n, k, BF16, a, rsa, csa, F8E4M3, b, rsb, csb, alpha, NULL, col_scale, 0, BF16, c, rsc, csc)
+ * computes, with the widened B held in a fixed 32 MiB array inside the library image, and it calls
+ * no allocating routine.  Consequences of that one shared array:
+ *   - every GPU that loads the library carries the 32 MiB until the process exits;
+ *   - the widened B (k*n bf16 elements, rows padded to a multiple of 8) must fit in 32 MiB, otherwise
+ *     the call is refused with return code 1 and a message naming both sizes;
+ *   - the first call on each device resolves the array's device address; make it before any stream
+ *     capture begins;
+ *   - calls whose GPU work overlaps (other streams, other threads) race on the array: serialise them.
+ *     A call returns only after its own work on cuda_stream has finished.
+ * All pointers must be device memory (host pointers would need staging, hence an allocation).
+ * Returns 0 or a skl_b200_status_t value; on failure a sentence saying why is copied to error_text
+ * (error_text_len bytes including the terminator; may be NULL / 0). */
+SKL_FUNC int skl_gemm_bf16_f8e4m3_bf16_noalloc_sm100a(size_t m, size_t n, size_t k, float alpha,
+                                                      const void *a, size_t rsa, size_t csa,
+                                                      const void *b, size_t rsb, size_t csb,
+                                                      const float *col_scale, void *c, size_t rsc,
+                                                      size_t csc, void *cuda_stream, char *error_text,
+                                                      size_t error_text_len);
+
 /* ------------------------------------------------------------------ cvt
  * Parameter lists of ref/cvt/cvt_ofp8.h:59-158 (src/cvt/cvt_f32_f8_zvfofp8min.h:61-112,
  * cvt_bf16_f8_zvfofp8min_zvfbfmin.h:67-122, cvt_f8_bf16_zvfofp8min.h:39-53) and

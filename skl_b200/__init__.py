@@ -66,6 +66,8 @@ SIGNATURES = {
     "skl_gemm_f8e5m2rcprc_f8e5m2rcprc_f32rcprc_sm100a": (_GEMM_P_F, None),
     "skl_gemm_ex_sm100a": ([_SZ, _SZ, _SZ, _I, _VP, _SZ, _SZ, _I, _VP, _SZ, _SZ, _F, _VP, _VP, _F, _I,
                             _VP, _SZ, _SZ], None),
+    "skl_gemm_bf16_f8e4m3_bf16_noalloc_sm100a": ([_SZ, _SZ, _SZ, _F, _VP, _SZ, _SZ, _VP, _SZ, _SZ, _VP, _VP, _SZ,
+                                                  _SZ, _VP, C.c_char_p, _SZ], _I),
     "skl_cvt_f32_f8e4m3_sm100a": ([_VP, _VP, _F, _SZ], None),
     "skl_cvt_sat_f32_f8e4m3_sm100a": ([_VP, _VP, _F, _SZ], None),
     "skl_cvt_f32_f8e5m2_sm100a": ([_VP, _VP, _F, _SZ], None),
