@@ -52,7 +52,7 @@ def measured_peaks():
 class ClockSampler:
     """Samples SM clock and throttle reasons of one GPU from a background thread while a region runs."""
 
-    def __init__(self, index: int, period_s: float = 0.02):
+    def __init__(self, index: int, period_s: float = 0.004):
         self.index, self.period, self.samples, self.reasons = index, period_s, [], set()
         self.max_mhz = None
         self._stop = threading.Event()
@@ -210,86 +210,178 @@ def time_steps(torch, fn, steps: int, barrier=None):
     return e0.elapsed_time(e1)  # ms
 
 
-def also_configs(torch, S, lib, peaks, steps=20, warmup=3):
-    """Short device-resident measurements of the other BASELINE configs (1 GPU)."""
-    import numpy as np
+def make_workloads(torch, S, lib):
+    """Named device-resident workloads besides c5: name -> builder returning (call, work, kind, reps).
 
-    out = {}
+    kind "tflops": work = operations per call; kind "gbs": work = algorithmic bytes per call."""
     dev = "cuda"
     g = torch.Generator(device=dev)
     g.manual_seed(1234)
+    W = {}
 
-    def gemm_rate(tag, m, n, k, ta, tb, tc, a, b, c, b_kmajor, alpha=1.0):
-        rsb, csb = (1, k) if b_kmajor else (n, 1)
+    def gemm_ex(m, n, k, ta, tb, tc, a, b, c, alpha=1.0):
+        def call():
+            lib.skl_gemm_ex_sm100a(m, n, k, ta, a.data_ptr(), k, 1, tb, b.data_ptr(), n, 1, alpha, None, None, 0.0, tc,
+                                   c.data_ptr(), n, 1)
+        return call
+
+    def int8_8192():
+        # the perf companion of config 1 (whose own 0.5 GOP cannot load the machine): SKL entry, int32 out
+        m = n = k = 8192
+        a = torch.randint(-128, 128, (m, k), dtype=torch.int8, device=dev, generator=g)
+        b = torch.randint(-128, 128, (k, n), dtype=torch.int8, device=dev, generator=g)
+        c = torch.empty((m, n), dtype=torch.int32, device=dev)
 
         def call():
-            lib.skl_gemm_ex_sm100a(m, n, k, ta, a.data_ptr(), k, 1, tb, b.data_ptr(), rsb, csb, alpha, None, None, 0.0,
-                                   tc, c.data_ptr(), n, 1)
+            lib.skl_gemm_i8_i8_i32_sm100a(m, n, k, 1, a.data_ptr(), k, b.data_ptr(), n, 0, c.data_ptr(), n)
+        return call, 2.0 * m * n * k, "tflops", 20
 
-        for _ in range(warmup):
-            call()
-        S.check()
-        ms = time_steps(torch, call, steps) / steps
-        out[tag] = {"tflops": round(2.0 * m * n * k / (ms * 1e-3) / 1e12, 1), "ms": round(ms, 4)}
+    def fp8(ta, alpha):
+        def build():
+            m = n = k = 8192  # config 3; finite codes only
+            a = torch.randint(0, 256, (m, k), dtype=torch.uint8, device=dev, generator=g) & 0x77
+            b = torch.randint(0, 256, (k, n), dtype=torch.uint8, device=dev, generator=g) & 0x77
+            c = torch.empty((m, n), dtype=torch.bfloat16, device=dev)
+            return gemm_ex(m, n, k, ta, S.F8E4M3, S.BF16, a, b, c, alpha), 2.0 * m * n * k, "tflops", 20
+        return build
 
-    # int8 8192^3 (the perf companion of config 1), int32 out through the SKL entry point
-    m = n = k = 8192
-    a = torch.randint(-128, 128, (m, k), dtype=torch.int8, device=dev, generator=g)
-    b = torch.randint(-128, 128, (k, n), dtype=torch.int8, device=dev, generator=g)
-    c = torch.empty((m, n), dtype=torch.int32, device=dev)
+    def half(tdt, code):
+        def build():
+            m = n = k = 4096  # config 2
+            a = (torch.randn((m, k), device=dev, generator=g) / 64.0).to(tdt)
+            b = (torch.randn((k, n), device=dev, generator=g) / 64.0).to(tdt)
+            c = torch.empty((m, n), dtype=tdt, device=dev)
+            return gemm_ex(m, n, k, code, code, code, a, b, c), 2.0 * m * n * k, "tflops", 40
+        return build
 
-    def call_i8():
-        lib.skl_gemm_i8_i8_i32_sm100a(m, n, k, 1, a.data_ptr(), k, b.data_ptr(), n, 0, c.data_ptr(), n)
+    def gemv(mm):
+        def build():
+            # config 4; rotate over weight copies totalling > 2x L2 so every pass streams from HBM
+            n, k, copies = 14336, 4096, 6
+            w = torch.randint(-127, 128, (copies, n, k), dtype=torch.int8, device=dev, generator=g)
+            sw = torch.rand((n,), device=dev, generator=g) * 1e-2 + 5e-3
+            x = torch.randint(-127, 128, (mm, k), dtype=torch.int8, device=dev, generator=g)
+            sx = torch.rand((mm,), device=dev, generator=g) + 0.5
+            y = torch.empty((mm, n), dtype=torch.float32, device=dev)
+            idx = [0]
 
+            def call():
+                wi = w[idx[0] % copies]
+                idx[0] += 1
+                lib.skl_gemm_ex_sm100a(mm, n, k, S.I8, x.data_ptr(), k, 1, S.I8, wi.data_ptr(), 1, k, 1.0, sx.data_ptr(),
+                                       sw.data_ptr(), 0.0, S.F32, y.data_ptr(), n, 1)
+            return call, float(n * k + mm * k + 4 * (n + mm) + 4 * mm * n), "gbs", 60
+        return build
+
+    def cvt_f32_e4m3():
+        n = 1 << 27  # 512 MiB in, 128 MiB out: config 3's operand preparation at twice the size
+        src = torch.randn((n,), device=dev, generator=g)
+        dst = torch.empty((n,), dtype=torch.uint8, device=dev)
+
+        def call():
+            lib.skl_cvt_sat_f32_f8e4m3_sm100a(dst.data_ptr(), src.data_ptr(), 0.37, n)
+        return call, 5.0 * n, "gbs", 10
+
+    def cvt_e4m3_bf16():
+        n = 1 << 28
+        src = torch.randint(0, 256, (n,), dtype=torch.uint8, device=dev, generator=g)
+        dst = torch.empty((n,), dtype=torch.bfloat16, device=dev)
+
+        def call():
+            lib.skl_cvt_f8e4m3_bf16_sm100a(dst.data_ptr(), src.data_ptr(), n)
+        return call, 3.0 * n, "gbs", 10
+
+    def transpose_e8():
+        m = n = 16384
+        a = torch.randint(0, 256, (m, n), dtype=torch.uint8, device=dev, generator=g)
+        at = torch.empty((n, m), dtype=torch.uint8, device=dev)
+
+        def call():
+            lib.skl_transpose_e8_sm100a(m, n, a.data_ptr(), n, at.data_ptr(), m)
+        return call, 2.0 * m * n, "gbs", 10
+
+    def pack_e16():
+        m, n, m0, n0 = 16384, 8192, 128, 64  # row-major bf16 matrix into 128 x 64 row-major blocks
+        a = torch.randint(0, 30000, (m, n), dtype=torch.int16, device=dev, generator=g)
+        out = torch.empty((m * n,), dtype=torch.int16, device=dev)
+        n1 = n // n0
+
+        def call():
+            lib.skl_pack_e16rc_e16rcprc_sm100a(m, n, a.data_ptr(), n, 1, m0, n0, out.data_ptr(), n0, 1, n1 * m0 * n0,
+                                               m0 * n0, 0)
+        return call, 4.0 * m * n, "gbs", 10
+
+    W["int8_8192_i32out"] = int8_8192
+    W["fp8_e4m3xe4m3_8192_bf16out"] = fp8(S.F8E4M3, 1e-3)
+    W["fp8_e5m2xe4m3_8192_bf16out"] = fp8(S.F8E5M2, 1e-6)
+    W["bf16_4096_bf16out"] = half(torch.bfloat16, S.BF16)
+    W["fp16_4096_fp16out"] = half(torch.float16, S.F16)
+    W["gemv_i8_m1"], W["gemv_i8_m4"], W["gemv_i8_m16"] = gemv(1), gemv(4), gemv(16)
+    W["cvt_sat_f32_f8e4m3_128M"] = cvt_f32_e4m3
+    W["cvt_f8e4m3_bf16_256M"] = cvt_e4m3_bf16
+    W["transpose_e8_16384"] = transpose_e8
+    W["pack_e16_16384x8192"] = pack_e16
+    return W
+
+
+def time_graph(torch, lib, call, reps, replays=5):
+    """Device time per call with the host out of the picture: `reps` calls captured into one CUDA graph
+    (the library only enqueues when its operands are device memory), the graph replayed between two events."""
+    prev = lib.skl_b200_get_stream()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    graph = torch.cuda.CUDAGraph()
+    lib.skl_b200_set_stream(side.cuda_stream)
+    try:
+        with torch.cuda.graph(graph, stream=side):
+            for _ in range(reps):
+                call()
+    finally:
+        lib.skl_b200_set_stream(prev)
+    torch.cuda.synchronize()
+    graph.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(replays):
+        graph.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / (replays * reps)
+
+
+def run_workload(torch, S, lib, peaks, build, warmup=3, reps=None):
+    call, work, kind, default_reps = build()
+    reps = reps or default_reps
     for _ in range(warmup):
-        call_i8()
+        call()
     S.check()
-    ms = time_steps(torch, call_i8, steps) / steps
-    out["int8_8192_i32out"] = {"tops": round(2.0 * m * n * k / (ms * 1e-3) / 1e12, 1), "ms": round(ms, 4)}
-    del c
+    ms = time_steps(torch, call, reps) / reps
+    lib.skl_b200_synchronize()
+    S.check()
+    if kind == "tflops":
+        return {"tflops": round(work / (ms * 1e-3) / 1e12, 1), "ms": round(ms, 4)}
+    # bandwidth-bound kernels last microseconds: time them inside a CUDA graph so that the figure is the
+    # device's, and keep the back-to-back API figure (host launch cost included) beside it
+    out = {"us_api_back_to_back": round(ms * 1e3, 2)}
+    try:
+        ms = time_graph(torch, lib, call, reps)
+        out["timing"] = "cuda graph replay"
+    except Exception as exc:  # pragma: no cover - capture refused: keep the API timing
+        out["timing"] = f"api calls (graph capture failed: {type(exc).__name__})"
+    lib.skl_b200_synchronize()
+    S.check()
+    gbs = work / (ms * 1e-3) / 1e9
+    out.update({"gbs": round(gbs, 1), "us": round(ms * 1e3, 2), "frac_of_hbm_peak": round(gbs / peaks["hbm_gbs"], 3)})
+    return out
 
-    # fp8 8192^3 -> bf16 (config 3), both operand-format runs, operands reuse the int8 buffers' bytes
-    a8, b8 = a.view(torch.uint8) & 0x77, b.view(torch.uint8) & 0x77  # finite codes only
-    c16 = torch.empty((m, n), dtype=torch.bfloat16, device=dev)
-    gemm_rate("fp8_e4m3xe4m3_8192_bf16out", m, n, k, S.F8E4M3, S.F8E4M3, S.BF16, a8, b8, c16, False, 1e-3)
-    gemm_rate("fp8_e5m2xe4m3_8192_bf16out", m, n, k, S.F8E5M2, S.F8E4M3, S.BF16, a8, b8, c16, False, 1e-6)
-    del a, b, a8, b8, c16
 
-    # bf16 / fp16 4096^3 -> bf16 / fp16 (config 2)
-    m = n = k = 4096
-    for tag, tdt, code in (("bf16", torch.bfloat16, S.BF16), ("fp16", torch.float16, S.F16)):
-        a = (torch.randn((m, k), device=dev, generator=g) / 64.0).to(tdt)
-        b = (torch.randn((k, n), device=dev, generator=g) / 64.0).to(tdt)
-        c = torch.empty((m, n), dtype=tdt, device=dev)
-        gemm_rate(f"{tag}_4096_{tag}out", m, n, k, code, code, code, a, b, c, False)
-    del a, b, c
-
-    # decode GEMV (config 4): rotate over weight copies totalling > 2x L2 so every pass streams from HBM
-    n, k = 14336, 4096
-    copies = 6
-    w = torch.randint(-127, 128, (copies, n, k), dtype=torch.int8, device=dev, generator=g)
-    sw = torch.rand((n,), device=dev, generator=g) * 1e-2 + 5e-3
-    for mm in (1, 4, 16):
-        x = torch.randint(-127, 128, (mm, k), dtype=torch.int8, device=dev, generator=g)
-        sx = torch.rand((mm,), device=dev, generator=g) + 0.5
-        y = torch.empty((mm, n), dtype=torch.float32, device=dev)
-        idx = [0]
-
-        def call():
-            wi = w[idx[0] % copies]
-            idx[0] += 1
-            lib.skl_gemm_ex_sm100a(mm, n, k, S.I8, x.data_ptr(), k, 1, S.I8, wi.data_ptr(), 1, k, 1.0, sx.data_ptr(),
-                                   sw.data_ptr(), 0.0, S.F32, y.data_ptr(), n, 1)
-
-        for _ in range(warmup):
-            call()
-        S.check()
-        reps = 60
-        ms = time_steps(torch, call, reps) / reps
-        nbytes = n * k + mm * k + 4 * (n + mm) + 4 * mm * n
-        gbs = nbytes / (ms * 1e-3) / 1e9
-        out[f"gemv_i8_m{mm}"] = {"gbs": round(gbs, 1), "us": round(ms * 1e3, 2),
-                                 "frac_of_hbm_peak": round(gbs / peaks["hbm_gbs"], 3)}
+def also_configs(torch, S, lib, peaks):
+    """Short device-resident measurements of the other BASELINE configs and companions (1 GPU)."""
+    out = {}
+    for name, build in make_workloads(torch, S, lib).items():
+        out[name] = run_workload(torch, S, lib, peaks, build)
+        torch.cuda.empty_cache()
     return out
 
 
@@ -300,6 +392,8 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-also", action="store_true", help="skip the other configs and the CPU baseline")
+    ap.add_argument("--only", default=None, help="run one named side workload (see make_workloads) and print "
+                                                 "its own small JSON line; used for profiler captures")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
@@ -330,6 +424,13 @@ def main() -> None:
     lib = S.lib()  # raises if the CUDA library is not built: no fallback
     lib.skl_b200_set_stream(torch.cuda.current_stream().cuda_stream)
     peaks = measured_peaks()
+
+    if args.only:
+        lib.skl_b200_set_async(1)
+        res = run_workload(torch, S, lib, peaks, make_workloads(torch, S, lib)[args.only], warmup=args.warmup,
+                           reps=args.steps)
+        print(json.dumps({"workload": args.only, **res, "steps": args.steps, "warmup": args.warmup}), flush=True)
+        return
 
     # ---------------- inputs (seed 5): X ~ N(0,1) bf16; W ~ N(0, 0.02), per-column scale amax/448, E4M3
     m, k, n_total = M_C5, K_C5, N_C5

@@ -69,7 +69,7 @@ int skl_b200_launch_gemm_tc(const skl_b200_gemm_args *args, uint32_t *dev_status
 /* Skinny int8 kernel: m <= 16, A rows and B columns contiguous in k (csa == 1, rsb == 1),
  * 16-byte aligned rows, k % 16 == 0, m*k bytes of A fit in shared memory. */
 int skl_b200_gemv_i8_supported(const skl_b200_gemm_args *args);
-int skl_b200_launch_gemv_i8(const skl_b200_gemm_args *args, void *stream);
+int skl_b200_launch_gemv_i8(const skl_b200_gemm_args *args, uint32_t *dev_status, void *stream);
 
 /* cvt: src_type in {F32, BF16}, dst_fmt in {F8E4M3, F8E5M2}. */
 int skl_b200_launch_cvt_to_f8(void *dst, const void *src, int src_type, int dst_fmt, int saturate,

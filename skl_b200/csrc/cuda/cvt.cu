@@ -89,6 +89,34 @@ __device__ __forceinline__ uint32_t f8_to_bf16_bits(uint32_t code) {
   return f2u(f) >> 16;
 }
 
+__device__ __forceinline__ bool has_zero_byte(uint32_t v) {
+  return ((v - 0x01010101u) & ~v & 0x80808080u) != 0u;
+}
+
+// Four fp8 codes (one 32-bit word, lowest byte first) -> four bf16 patterns in two words.
+// Normal codes are widened with packed integer arithmetic, two per word:
+//     E4M3: bf16 = sign<<8 | ((code & 0x7F) << 4) + (120 << 7)      E5M2: ... << 5) + (112 << 7)
+// A word that holds any code with a zero exponent field (zero, subnormal) or an all-ones one
+// (E4M3 NaN, E5M2 Inf / NaN) takes the per-element decoder instead.
+template <int FMT>
+__device__ __forceinline__ void f8x4_to_bf16x4(uint32_t w, uint32_t &lo, uint32_t &hi) {
+  constexpr uint32_t EXPF = FMT == SKL_DT_F8E4M3 ? 0x78787878u : 0x7C7C7C7Cu;
+  const uint32_t e = w & EXPF;
+  // E4M3's only non-finite code is exponent and mantissa all ones; E5M2's are every all-ones exponent
+  const uint32_t top = FMT == SKL_DT_F8E4M3 ? ((w & 0x7F7F7F7Fu) ^ 0x7F7F7F7Fu) : (e ^ EXPF);
+  if (has_zero_byte(e) || has_zero_byte(top)) {
+    lo = f8_to_bf16_bits<FMT>(w & 0xFFu) | (f8_to_bf16_bits<FMT>((w >> 8) & 0xFFu) << 16);
+    hi = f8_to_bf16_bits<FMT>((w >> 16) & 0xFFu) | (f8_to_bf16_bits<FMT>(w >> 24) << 16);
+    return;
+  }
+  constexpr int SH = FMT == SKL_DT_F8E4M3 ? 4 : 5;
+  constexpr uint32_t BIAS = FMT == SKL_DT_F8E4M3 ? 0x3C003C00u : 0x38003800u;
+  const uint32_t x0 = __byte_perm(w, 0u, 0x4140);  // 0x00b1_00b0
+  const uint32_t x1 = __byte_perm(w, 0u, 0x4342);  // 0x00b3_00b2
+  lo = (((x0 & 0x007F007Fu) << SH) + BIAS) | ((x0 & 0x00800080u) << 8);
+  hi = (((x1 & 0x007F007Fu) << SH) + BIAS) | ((x1 & 0x00800080u) << 8);
+}
+
 template <int FMT>
 __global__ void __launch_bounds__(CVT_THREADS)
     cvt_f8_to_bf16_kernel(uint16_t *__restrict__ dst, const uint8_t *__restrict__ src, size_t n,
@@ -96,19 +124,26 @@ __global__ void __launch_bounds__(CVT_THREADS)
   const size_t stride = (size_t)gridDim.x * blockDim.x;
   const size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   const size_t nvec = vec_ok ? n / 16 : 0;
-  for (size_t v = tid; v < nvec; v += stride) {
-    uint4 q = __ldg(reinterpret_cast<const uint4 *>(src) + v);
-    uint32_t w[4] = {q.x, q.y, q.z, q.w};
-    uint32_t o[8];
+  // four independent 16-byte loads per thread per step: enough bytes in flight to cover HBM latency
+  for (size_t v0 = tid; v0 < nvec; v0 += 4 * stride) {
+    uint4 q[4];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      o[2 * i] = f8_to_bf16_bits<FMT>(w[i] & 0xFFu) | (f8_to_bf16_bits<FMT>((w[i] >> 8) & 0xFFu) << 16);
-      o[2 * i + 1] =
-          f8_to_bf16_bits<FMT>((w[i] >> 16) & 0xFFu) | (f8_to_bf16_bits<FMT>(w[i] >> 24) << 16);
+    for (int u = 0; u < 4; ++u) {
+      const size_t v = v0 + u * stride;
+      q[u] = v < nvec ? __ldg(reinterpret_cast<const uint4 *>(src) + v) : make_uint4(0, 0, 0, 0);
     }
-    uint4 *d = reinterpret_cast<uint4 *>(dst) + v * 2;
-    d[0] = make_uint4(o[0], o[1], o[2], o[3]);
-    d[1] = make_uint4(o[4], o[5], o[6], o[7]);
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const size_t v = v0 + u * stride;
+      if (v >= nvec) break;
+      uint32_t w[4] = {q[u].x, q[u].y, q[u].z, q[u].w};
+      uint32_t o[8];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) f8x4_to_bf16x4<FMT>(w[i], o[2 * i], o[2 * i + 1]);
+      uint4 *d = reinterpret_cast<uint4 *>(dst) + v * 2;
+      d[0] = make_uint4(o[0], o[1], o[2], o[3]);
+      d[1] = make_uint4(o[4], o[5], o[6], o[7]);
+    }
   }
   for (size_t i = nvec * 16 + tid; i < n; i += stride) dst[i] = (uint16_t)f8_to_bf16_bits<FMT>(src[i]);
 }
@@ -124,21 +159,27 @@ __global__ void __launch_bounds__(CVT_THREADS)
   if (vec_ok) {
     const size_t cvec = cols / 16;
     const size_t total = rows * cvec;
-    for (size_t v = tid; v < total; v += stride) {
-      size_t r = v / cvec, cv = v - r * cvec;
-      uint4 q = __ldg(reinterpret_cast<const uint4 *>(src + r * ld_src) + cv);
-      uint32_t w[4] = {q.x, q.y, q.z, q.w};
-      uint32_t o[8];
+    for (size_t v0 = tid; v0 < total; v0 += 4 * stride) {
+      uint4 q[4];
+      size_t rr[4], cc[4];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        o[2 * i] =
-            f8_to_bf16_bits<FMT>(w[i] & 0xFFu) | (f8_to_bf16_bits<FMT>((w[i] >> 8) & 0xFFu) << 16);
-        o[2 * i + 1] =
-            f8_to_bf16_bits<FMT>((w[i] >> 16) & 0xFFu) | (f8_to_bf16_bits<FMT>(w[i] >> 24) << 16);
+      for (int u = 0; u < 4; ++u) {
+        const size_t v = v0 + u * stride;
+        rr[u] = v / cvec;
+        cc[u] = v - rr[u] * cvec;
+        q[u] = v < total ? __ldg(reinterpret_cast<const uint4 *>(src + rr[u] * ld_src) + cc[u]) : make_uint4(0, 0, 0, 0);
       }
-      uint4 *d = reinterpret_cast<uint4 *>(dst + r * ld_dst) + cv * 2;
-      d[0] = make_uint4(o[0], o[1], o[2], o[3]);
-      d[1] = make_uint4(o[4], o[5], o[6], o[7]);
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        if (v0 + u * stride >= total) break;
+        uint32_t w[4] = {q[u].x, q[u].y, q[u].z, q[u].w};
+        uint32_t o[8];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) f8x4_to_bf16x4<FMT>(w[i], o[2 * i], o[2 * i + 1]);
+        uint4 *d = reinterpret_cast<uint4 *>(dst + rr[u] * ld_dst) + cc[u] * 2;
+        d[0] = make_uint4(o[0], o[1], o[2], o[3]);
+        d[1] = make_uint4(o[4], o[5], o[6], o[7]);
+      }
     }
   } else {
     const size_t total = rows * cols;

@@ -9,8 +9,11 @@
 // The kernel walks 64 x 64 tiles of the logical (i, j) index space.  Each tile is read with the
 // thread index running along the source's unit-stride direction, parked in shared memory, and
 // written with the thread index running along the destination's unit-stride direction, so both
-// sides are coalesced even when the two directions differ (the transposing cases).  Only addressed
-// destination elements are written.  Algorithmic bytes: 2 x elements x element size (+ padding).
+// sides are coalesced even when the two directions differ (the transposing cases).  Along the
+// unit-stride direction a thread moves 4 bytes at a time (4 / 2 / 1 elements) whenever the layout
+// keeps such a group contiguous and aligned; otherwise it falls back to single elements.  Only
+// addressed destination elements are written.  Algorithmic bytes: 2 x elements x element size
+// (+ padding written by pack).
 #include "numerics.cuh"
 
 namespace sklb {
@@ -19,70 +22,171 @@ namespace {
 constexpr int RT = 64;  // tile edge
 
 struct Side {
-  int64_t b0r, b0c;  // block extents (rows, cols); plain layout: the whole extent (>= 1)
   int64_t rs0, cs0, rs1, cs1;
+  uint32_t b0r, b0c;  // block extents (rows, cols); unused when plain
+  int plain;          // 1: offset = i*rs0 + j*cs0
+  int fast_j;         // 1: the unit stride runs along j
+  int vec_ok;         // groups of 4 bytes along the unit-stride direction are contiguous and aligned
 };
 
-__device__ __forceinline__ int64_t side_off(const Side &s, int64_t i, int64_t j) {
-  return (i / s.b0r) * s.rs1 + (i % s.b0r) * s.rs0 + (j / s.b0c) * s.cs1 + (j % s.b0c) * s.cs0;
+__device__ __forceinline__ int64_t side_off(const Side &s, uint32_t i, uint32_t j) {
+  if (s.plain) return (int64_t)i * s.rs0 + (int64_t)j * s.cs0;
+  const uint32_t bi = i / s.b0r, bj = j / s.b0c;
+  return (int64_t)bi * s.rs1 + (int64_t)(i - bi * s.b0r) * s.rs0 + (int64_t)bj * s.cs1 +
+         (int64_t)(j - bj * s.b0c) * s.cs0;
 }
 
 struct RelayoutParams {
-  int64_t MI, NJ;  // logical extent walked (padded extent for pack, real extent otherwise)
-  int64_t m, n;    // extent for which the source holds data
+  uint32_t MI, NJ;  // logical extent walked (padded extent for pack, real extent otherwise)
+  uint32_t m, n;    // extent for which the source holds data
   Side src, dst;
   uint32_t pad;
-  int src_fast_j;  // 1: source unit stride runs along j
-  int dst_fast_j;
-  int64_t tiles_j;
+  uint32_t tiles_i, tiles_j;
 };
 
 template <typename T>
 __global__ void __launch_bounds__(256) relayout_kernel(const T *__restrict__ src, T *__restrict__ dst,
                                                        const RelayoutParams p) {
+  constexpr int VEC = 4 / sizeof(T);   // elements per 4-byte group
+  constexpr int GROUPS = RT / VEC;     // groups along the fast direction of a tile
   __shared__ T tile[RT][RT + 4 / sizeof(T)];
-  for (int64_t t = blockIdx.x; t < p.tiles_j * ((p.MI + RT - 1) / RT); t += gridDim.x) {
-    const int64_t i0 = (t / p.tiles_j) * RT, j0 = (t % p.tiles_j) * RT;
-    for (int e = threadIdx.x; e < RT * RT; e += 256) {
-      int fast = e & (RT - 1), slow = e >> 6;
-      int ti = p.src_fast_j ? slow : fast, tj = p.src_fast_j ? fast : slow;
-      int64_t i = i0 + ti, j = j0 + tj;
-      T v = (T)p.pad;
-      if (i < p.m && j < p.n) v = src[side_off(p.src, i, j)];
-      tile[ti][tj] = v;
+  const uint32_t num_tiles = p.tiles_i * p.tiles_j;
+  for (uint32_t t = blockIdx.x; t < num_tiles; t += gridDim.x) {
+    const uint32_t i0 = (t / p.tiles_j) * RT, j0 = (t % p.tiles_j) * RT;
+
+    // ---- read phase: thread index along the source's unit stride
+    for (int e = threadIdx.x; e < RT * GROUPS; e += 256) {
+      const int grp = e % GROUPS, slow = e / GROUPS;
+      const int f0 = grp * VEC;
+      const int ti = p.src.fast_j ? slow : f0, tj = p.src.fast_j ? f0 : slow;
+      const uint32_t i = i0 + ti, j = j0 + tj;
+      const uint32_t lim_fast = p.src.fast_j ? p.n : p.m;
+      const uint32_t pos_fast = p.src.fast_j ? j : i;
+      const bool slow_in = p.src.fast_j ? (i < p.m) : (j < p.n);
+      T v[VEC];
+      if (VEC > 1 && p.src.vec_ok && slow_in && pos_fast + VEC <= lim_fast) {
+        const uint32_t w = *reinterpret_cast<const uint32_t *>(src + side_off(p.src, i, j));
+#pragma unroll
+        for (int q = 0; q < VEC; ++q) v[q] = (T)(w >> (8 * sizeof(T) * q));
+      } else {
+#pragma unroll
+        for (int q = 0; q < VEC; ++q) {
+          const uint32_t ii = p.src.fast_j ? i : i + q, jj = p.src.fast_j ? j + q : j;
+          v[q] = (ii < p.m && jj < p.n) ? src[side_off(p.src, ii, jj)] : (T)p.pad;
+        }
+      }
+#pragma unroll
+      for (int q = 0; q < VEC; ++q) {
+        if (p.src.fast_j)
+          tile[ti][tj + q] = v[q];
+        else
+          tile[ti + q][tj] = v[q];
+      }
     }
     __syncthreads();
-    for (int e = threadIdx.x; e < RT * RT; e += 256) {
-      int fast = e & (RT - 1), slow = e >> 6;
-      int ti = p.dst_fast_j ? slow : fast, tj = p.dst_fast_j ? fast : slow;
-      int64_t i = i0 + ti, j = j0 + tj;
-      if (i < p.MI && j < p.NJ) dst[side_off(p.dst, i, j)] = tile[ti][tj];
+
+    // ---- write phase: thread index along the destination's unit stride
+    for (int e = threadIdx.x; e < RT * GROUPS; e += 256) {
+      const int grp = e % GROUPS, slow = e / GROUPS;
+      const int f0 = grp * VEC;
+      const int ti = p.dst.fast_j ? slow : f0, tj = p.dst.fast_j ? f0 : slow;
+      const uint32_t i = i0 + ti, j = j0 + tj;
+      const uint32_t lim_fast = p.dst.fast_j ? p.NJ : p.MI;
+      const uint32_t pos_fast = p.dst.fast_j ? j : i;
+      const bool slow_in = p.dst.fast_j ? (i < p.MI) : (j < p.NJ);
+      if (!slow_in || pos_fast >= lim_fast) continue;
+      T v[VEC];
+#pragma unroll
+      for (int q = 0; q < VEC; ++q) v[q] = p.dst.fast_j ? tile[ti][tj + q] : tile[ti + q][tj];
+      if (VEC > 1 && p.dst.vec_ok && pos_fast + VEC <= lim_fast) {
+        uint32_t w = 0;
+#pragma unroll
+        for (int q = 0; q < VEC; ++q) w |= (uint32_t)v[q] << (8 * sizeof(T) * q);
+        *reinterpret_cast<uint32_t *>(dst + side_off(p.dst, i, j)) = w;
+      } else {
+#pragma unroll
+        for (int q = 0; q < VEC; ++q) {
+          const uint32_t ii = p.dst.fast_j ? i : i + q, jj = p.dst.fast_j ? j + q : j;
+          if (ii < p.MI && jj < p.NJ) dst[side_off(p.dst, ii, jj)] = v[q];
+        }
+      }
     }
     __syncthreads();
   }
 }
 
+int relayout_grid(uint64_t tiles) {
+  static int sms = 0;
+  if (sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (sms <= 0) sms = 148;
+  }
+  const uint64_t cap = (uint64_t)sms * 8;  // 8 resident CTAs of 256 threads per SM
+  return (int)(tiles < cap ? tiles : cap);
+}
+
+// Can 4-byte groups along the unit-stride direction be moved as one word?  Needs a true unit stride,
+// every other stride and the base a multiple of the group, and blocks that do not split a group.
+void finish_side(Side &s, const void *base, size_t esize) {
+  const int64_t vec = 4 / (int64_t)esize;
+  const int64_t unit = s.fast_j ? s.cs0 : s.rs0;
+  const int64_t other0 = s.fast_j ? s.rs0 : s.cs0;
+  bool ok = vec > 1 && unit == 1 && (reinterpret_cast<uintptr_t>(base) & 3u) == 0 && other0 % vec == 0;
+  if (ok && !s.plain) {
+    const uint32_t bfast = s.fast_j ? s.b0c : s.b0r;
+    ok = bfast % vec == 0 && s.rs1 % vec == 0 && s.cs1 % vec == 0;
+  }
+  s.vec_ok = ok ? 1 : 0;
+}
+
 int launch_relayout(size_t esize, const void *src, void *dst, RelayoutParams p, cudaStream_t s) {
-  if (p.MI <= 0 || p.NJ <= 0) return 0;
+  if (p.MI == 0 || p.NJ == 0) return 0;
+  finish_side(p.src, src, esize);
+  finish_side(p.dst, dst, esize);
+  p.tiles_i = (p.MI + RT - 1) / RT;
   p.tiles_j = (p.NJ + RT - 1) / RT;
-  int64_t tiles = p.tiles_j * ((p.MI + RT - 1) / RT);
-  int64_t grid = tiles < (int64_t)148 * 16 ? tiles : (int64_t)148 * 16;
+  const int grid = relayout_grid((uint64_t)p.tiles_i * p.tiles_j);
   switch (esize) {
     case 1:
-      relayout_kernel<uint8_t><<<(unsigned)grid, 256, 0, s>>>((const uint8_t *)src, (uint8_t *)dst, p);
+      relayout_kernel<uint8_t><<<grid, 256, 0, s>>>((const uint8_t *)src, (uint8_t *)dst, p);
       break;
     case 2:
-      relayout_kernel<uint16_t><<<(unsigned)grid, 256, 0, s>>>((const uint16_t *)src, (uint16_t *)dst, p);
+      relayout_kernel<uint16_t><<<grid, 256, 0, s>>>((const uint16_t *)src, (uint16_t *)dst, p);
       break;
     default:
-      relayout_kernel<uint32_t><<<(unsigned)grid, 256, 0, s>>>((const uint32_t *)src, (uint32_t *)dst, p);
+      relayout_kernel<uint32_t><<<grid, 256, 0, s>>>((const uint32_t *)src, (uint32_t *)dst, p);
       break;
   }
   SKLB_COUNT_LAUNCH();
   return (int)cudaGetLastError();
 }
 
-inline int64_t nz(int64_t v) { return v > 0 ? v : 1; }
+Side plain_side(size_t rs, size_t cs) {
+  Side s{};
+  s.rs0 = (int64_t)rs;
+  s.cs0 = (int64_t)cs;
+  s.plain = 1;
+  s.fast_j = (cs == 1 || rs != 1) ? 1 : 0;
+  return s;
+}
+
+Side blocked_side(size_t m0, size_t n0, size_t rs0, size_t cs0, size_t rs1, size_t cs1) {
+  Side s{};
+  s.rs0 = (int64_t)rs0;
+  s.cs0 = (int64_t)cs0;
+  s.rs1 = (int64_t)rs1;
+  s.cs1 = (int64_t)cs1;
+  s.b0r = (uint32_t)m0;
+  s.b0c = (uint32_t)n0;
+  s.plain = 0;
+  s.fast_j = (cs0 == 1 || rs0 != 1) ? 1 : 0;
+  return s;
+}
+
+// extents are walked with 32-bit indices
+bool fits(size_t a, size_t b) { return a < (1ull << 31) && b < (1ull << 31); }
 
 }  // namespace
 }  // namespace sklb
@@ -93,17 +197,16 @@ extern "C" int skl_b200_launch_pack(size_t esize, size_t m, size_t n, const void
                                     size_t cs, size_t m0, size_t n0, void *dst, size_t rs0,
                                     size_t cs0, size_t rs1, size_t cs1, uint32_t pad, void *stream) {
   if (m0 == 0 || n0 == 0) return 0;
-  RelayoutParams p;
-  const int64_t m1 = (int64_t)((m + m0 - 1) / m0), n1 = (int64_t)((n + n0 - 1) / n0);
-  p.MI = m1 * (int64_t)m0;
-  p.NJ = n1 * (int64_t)n0;
-  p.m = (int64_t)m;
-  p.n = (int64_t)n;
-  p.src = Side{nz(p.MI), nz(p.NJ), (int64_t)rs, (int64_t)cs, 0, 0};
-  p.dst = Side{(int64_t)m0, (int64_t)n0, (int64_t)rs0, (int64_t)cs0, (int64_t)rs1, (int64_t)cs1};
+  const size_t m1 = (m + m0 - 1) / m0, n1 = (n + n0 - 1) / n0;
+  if (!fits(m1 * m0, n1 * n0) || !fits(m0, n0)) return (int)cudaErrorInvalidValue;
+  RelayoutParams p{};
+  p.MI = (uint32_t)(m1 * m0);
+  p.NJ = (uint32_t)(n1 * n0);
+  p.m = (uint32_t)m;
+  p.n = (uint32_t)n;
+  p.src = plain_side(rs, cs);
+  p.dst = blocked_side(m0, n0, rs0, cs0, rs1, cs1);
   p.pad = pad;
-  p.src_fast_j = (cs == 1 || rs != 1) ? 1 : 0;
-  p.dst_fast_j = (cs0 == 1 || rs0 != 1) ? 1 : 0;
   return launch_relayout(esize, src, dst, p, (cudaStream_t)stream);
 }
 
@@ -111,30 +214,30 @@ extern "C" int skl_b200_launch_unpack(size_t esize, size_t m0, size_t n0, const 
                                       size_t cs0, size_t rs1, size_t cs1, size_t m, size_t n,
                                       void *dst, size_t rs, size_t cs, void *stream) {
   if (m0 == 0 || n0 == 0) return 0;
-  RelayoutParams p;
-  p.MI = (int64_t)m;
-  p.NJ = (int64_t)n;
-  p.m = (int64_t)m;
-  p.n = (int64_t)n;
-  p.src = Side{(int64_t)m0, (int64_t)n0, (int64_t)rs0, (int64_t)cs0, (int64_t)rs1, (int64_t)cs1};
-  p.dst = Side{nz(p.MI), nz(p.NJ), (int64_t)rs, (int64_t)cs, 0, 0};
+  if (!fits(m, n) || !fits(m0, n0)) return (int)cudaErrorInvalidValue;
+  RelayoutParams p{};
+  p.MI = (uint32_t)m;
+  p.NJ = (uint32_t)n;
+  p.m = (uint32_t)m;
+  p.n = (uint32_t)n;
+  p.src = blocked_side(m0, n0, rs0, cs0, rs1, cs1);
+  p.dst = plain_side(rs, cs);
   p.pad = 0;
-  p.src_fast_j = (cs0 == 1 || rs0 != 1) ? 1 : 0;
-  p.dst_fast_j = (cs == 1 || rs != 1) ? 1 : 0;
   return launch_relayout(esize, src, dst, p, (cudaStream_t)stream);
 }
 
 extern "C" int skl_b200_launch_transpose(size_t esize, size_t m, size_t n, const void *a, size_t rsa,
                                          void *at, size_t rsat, void *stream) {
-  RelayoutParams p;
-  p.MI = (int64_t)m;
-  p.NJ = (int64_t)n;
-  p.m = (int64_t)m;
-  p.n = (int64_t)n;
-  p.src = Side{nz(p.MI), nz(p.NJ), (int64_t)rsa, 1, 0, 0};
-  p.dst = Side{nz(p.MI), nz(p.NJ), 1, (int64_t)rsat, 0, 0};  // at[j*rsat + i]
+  if (!fits(m, n)) return (int)cudaErrorInvalidValue;
+  RelayoutParams p{};
+  p.MI = (uint32_t)m;
+  p.NJ = (uint32_t)n;
+  p.m = (uint32_t)m;
+  p.n = (uint32_t)n;
+  p.src = plain_side(rsa, 1);
+  p.src.fast_j = 1;
+  p.dst = plain_side(1, rsat);  // at[j*rsat + i]
+  p.dst.fast_j = 0;
   p.pad = 0;
-  p.src_fast_j = 1;
-  p.dst_fast_j = 0;
   return launch_relayout(esize, a, at, p, (cudaStream_t)stream);
 }

@@ -423,7 +423,9 @@ static void run_gemm(skl_b200_gemm_args *g) {
   const int prof = g_ctx.prof_ev && g_ctx.prof_used < g_ctx.prof_cap;
   if (prof) (void)cudaEventRecord(g_ctx.prof_ev[2 * g_ctx.prof_used], (cudaStream_t)g_ctx.stream);
   if (path == SKL_B200_PATH_GEMV) {
-    rc = skl_b200_launch_gemv_i8(g, g_ctx.stream);
+    uint32_t *st = device_status_words();
+    if (!st) return;
+    rc = skl_b200_launch_gemv_i8(g, st, g_ctx.stream);
   } else if (path == SKL_B200_PATH_TCGEN05) {
     uint32_t *st = device_status_words();
     if (!st) return;

@@ -34,13 +34,17 @@ def test_host_pointers_are_staged(skl, t):
 
 # tile-edge classes for the tensor-core kernel: (m, n, k)
 TC_SHAPES = [(127, 255, 63), (128, 256, 64), (129, 257, 65), (128, 256, 128), (256, 512, 129), (1, 256, 64),
-             (128, 16, 64), (130, 40, 1), (385, 300, 200), (64, 1000, 320), (300, 128, 1024)]
+             (128, 16, 64), (130, 40, 1), (385, 300, 200), (64, 1000, 320), (300, 128, 1024), (255, 256, 448),
+             (257, 513, 96), (1024, 768, 512)]
 
 
 @pytest.mark.parametrize("t", ALL_T)
 @pytest.mark.parametrize("layout", ["rkr", "rrr", "ckr", "crr", "rkc", "rrp"])
-def test_tensor_core_path(skl, t, layout):
-    """Every operand-major combination (A k-major / m-major, B k-major / n-major) and C layouts."""
+@pytest.mark.parametrize("pair", ["0", "2"])
+def test_tensor_core_path(skl, t, layout, pair, monkeypatch):
+    """Every operand-major combination (A k-major / m-major, B k-major / n-major) and C layouts, on
+    the one-CTA kernel (pair = 0) and on the two-CTA cta_group::2 kernel (pair = 2: whenever legal)."""
+    monkeypatch.setenv("SKL_B200_TC_PAIR", pair)
     for i, (m, n, k) in enumerate(TC_SHAPES):
         alpha, beta = ((2, 3) if i % 3 == 0 else (1, 0))
         check_gemm_rc(skl, t, m, n, k, layout, alpha, beta, where="device", path=S.PATH_TCGEN05, align=16,
@@ -52,10 +56,23 @@ def test_tensor_core_matches_generic_bits_for_int8_and_bound_for_float(skl, t):
     check_gemm_rc(skl, t, 512, 512, 1024, "rrr", 1, 0, where="device", path=0, expect_path=S.PATH_TCGEN05)
 
 
-def test_config1_int8_512x512x1024_bit_exact(skl):
+@pytest.mark.parametrize("pair", ["0", "2"])
+def test_config1_int8_512x512x1024_bit_exact(skl, pair, monkeypatch):
     """BASELINE config 1: A row-major, B K x N row-major, int32 out, alpha 1, beta 0; both pointer domains."""
+    monkeypatch.setenv("SKL_B200_TC_PAIR", pair)
     for where in ("device", "host"):
         check_gemm_rc(skl, H.I8, 512, 512, 1024, "rrr", 1, 0, where=where, seed=1, expect_path=S.PATH_TCGEN05)
+
+
+@pytest.mark.parametrize("t", ALL_T)
+def test_many_tiles_per_cta_and_raster_groups(skl, t, monkeypatch):
+    """More tiles than SMs, so every CTA walks several tiles through both TMEM accumulators, with a
+    small rasterisation group so group edges and the short last group are exercised."""
+    monkeypatch.setenv("SKL_B200_RASTER_GM", "3")
+    for pair in ("0", "2"):
+        monkeypatch.setenv("SKL_B200_TC_PAIR", pair)
+        check_gemm_rc(skl, t, 128 * 13 + 5, 256 * 14 + 9, 192, "rkr", 1, 0, where="device", path=S.PATH_TCGEN05, align=16,
+                      expect_path=S.PATH_TCGEN05, seed=9, all_codes=False)
 
 
 def test_unaligned_problem_falls_back_to_generic(skl):
