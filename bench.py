@@ -254,10 +254,11 @@ def make_workloads(torch, S, lib):
             return gemm_ex(m, n, k, code, code, code, a, b, c), 2.0 * m * n * k, "tflops", 40
         return build
 
-    def gemv(mm):
+    def gemv(mm, n=14336):
         def build():
             # config 4; rotate over weight copies totalling > 2x L2 so every pass streams from HBM
-            n, k, copies = 14336, 4096, 6
+            k = 4096
+            copies = max(2, min(8, (360 << 20) // (n * k) + 1))
             w = torch.randint(-127, 128, (copies, n, k), dtype=torch.int8, device=dev, generator=g)
             sw = torch.rand((n,), device=dev, generator=g) * 1e-2 + 5e-3
             x = torch.randint(-127, 128, (mm, k), dtype=torch.int8, device=dev, generator=g)
@@ -317,6 +318,10 @@ def make_workloads(torch, S, lib):
     W["bf16_4096_bf16out"] = half(torch.bfloat16, S.BF16)
     W["fp16_4096_fp16out"] = half(torch.float16, S.F16)
     W["gemv_i8_m1"], W["gemv_i8_m4"], W["gemv_i8_m16"] = gemv(1), gemv(4), gemv(16)
+    # the same kernels at other row counts: separates the fixed cost of a launch from the streaming rate
+    for rows in (1184, 4736, 28672, 57344):
+        W[f"gemv_i8_m1_n{rows}"] = gemv(1, rows)
+        W[f"gemv_i8_m16_n{rows}"] = gemv(16, rows)
     W["cvt_sat_f32_f8e4m3_128M"] = cvt_f32_e4m3
     W["cvt_f8e4m3_bf16_256M"] = cvt_e4m3_bf16
     W["transpose_e8_16384"] = transpose_e8
@@ -380,6 +385,8 @@ def also_configs(torch, S, lib, peaks):
     """Short device-resident measurements of the other BASELINE configs and companions (1 GPU)."""
     out = {}
     for name, build in make_workloads(torch, S, lib).items():
+        if "_n" in name.rsplit("_m", 1)[-1]:
+            continue  # row-count sweeps are for --only
         out[name] = run_workload(torch, S, lib, peaks, build)
         torch.cuda.empty_cache()
     return out

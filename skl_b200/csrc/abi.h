@@ -51,6 +51,8 @@ typedef struct skl_b200_gemm_args {
   float alpha_f, beta_f;   /* SKL_EPI_FLOAT */
   const float *row_scale;  /* m entries or NULL (SKL_EPI_FLOAT) */
   const float *col_scale;  /* n entries or NULL (SKL_EPI_FLOAT) */
+  int32_t col_scale_first; /* 0: v*row_scale then *col_scale (the defined order); 1: the reverse, used
+                              when a problem is handed over transposed so the two vectors swap roles */
 } skl_b200_gemm_args;
 
 /* Device status word written by kernels whose bounded waits expire: 0 = ok, else a stage code. */

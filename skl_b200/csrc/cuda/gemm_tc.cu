@@ -56,6 +56,7 @@ struct TcParams {
   int32_t alpha_i, beta_i;
   float alpha_f, beta_f;
   const float *row_scale, *col_scale;
+  int col_scale_first;
   uint32_t *status;
 };
 
@@ -161,6 +162,20 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
         "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
       : "r"(taddr));
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// 16 columns (the narrow-tile kernel); the upper half of r is cleared.
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]),
+        "=r"(r[15])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 16; i < 32; ++i) r[i] = 0u;
 }
 
 // Shared-memory matrix descriptor (tcgen05): start address, leading / stride byte offsets in 16-byte
@@ -294,8 +309,9 @@ __device__ __forceinline__ void epilogue_chunk(const TcParams &p, const uint32_t
   for (int e = 0; e < 32; ++e) {
     float acc = ACC_INT ? (float)(int32_t)r[e] : __uint_as_float(r[e]);
     float x = __fmul_rn(p.alpha_f, acc);
-    if (p.row_scale) x = __fmul_rn(x, rs);
+    if (p.row_scale && !p.col_scale_first) x = __fmul_rn(x, rs);
     if (p.col_scale && e < ncols) x = __fmul_rn(x, __ldg(p.col_scale + col0 + e));
+    if (p.row_scale && p.col_scale_first) x = __fmul_rn(x, rs);
     v[e] = x;
   }
   const int64_t base = (int64_t)row * p.rsc + (int64_t)col0 * p.csc;
@@ -489,7 +505,10 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
       for (int c0 = 0; c0 < BN; c0 += 32) {
         if (n0 + c0 >= p.N) break;  // uniform across the warp
         uint32_t r[32];
-        tmem_ld32(taddr + c0, r);
+        if (BN >= 32)
+          tmem_ld32(taddr + c0, r);
+        else
+          tmem_ld16(taddr + c0, r);
         if (row < p.M) epilogue_chunk<KIND == KIND_I8>(p, r, row, n0 + c0);
       }
       tc_fence_before();
@@ -811,7 +830,10 @@ int sm_count() {
   return sms;
 }
 
-int pick_bn(int64_t M, int64_t N, int kind) {
+int pick_bn(int64_t M, int64_t N, int kind, bool b_mn_major) {
+  // A k-major B with at most 16 columns: the skinny case.  A 128 x 16 tile streams the tall operand
+  // through 8 stages of 18 KiB per SM, which keeps HBM busy; the MMA work is negligible.
+  if (N <= 16 && !b_mn_major) return 16;
   const int64_t tm = (M + BM - 1) / BM;
   const int sms = sm_count();
   const int cand[3] = {256, 128, 64};
@@ -912,7 +934,7 @@ bool use_pair_kernel(int kind, int64_t M, int64_t N, const OperandView &vb) {
   const int mode = pair_mode();
   if (mode == 0) return false;
   (void)vb;
-  if (mode == 2) return true;
+  if (mode == 2) return N > 16;
   // needs at least two 128-row slabs per tile to be useful and enough tiles to fill the machine
   const int64_t tiles = ((M + 255) / 256) * ((N + 255) / 256);
   return kind == KIND_I8 && M > 128 && tiles >= sm_count() / 2;
@@ -951,7 +973,7 @@ extern "C" int skl_b200_launch_gemm_tc(const skl_b200_gemm_args *g, uint32_t *de
   const OperandView vb = classify(g->b, N, K, g->csb0, g->rsb0, es);
   if (kind < 0 || !va.ok || !vb.ok) return (int)cudaErrorInvalidValue;
   const bool pair = use_pair_kernel(kind, M, N, vb);
-  const int bn = pair ? 256 : pick_bn(M, N, kind);
+  const int bn = pair ? 256 : pick_bn(M, N, kind, vb.mn_major != 0);
   const int tile_rows = pair ? 2 * BM : BM;
 
   CUtensorMap tmA, tmB;
@@ -996,6 +1018,7 @@ extern "C" int skl_b200_launch_gemm_tc(const skl_b200_gemm_args *g, uint32_t *de
   p.beta_f = g->beta_f;
   p.row_scale = g->row_scale;
   p.col_scale = g->col_scale;
+  p.col_scale_first = g->col_scale_first;
   p.status = dev_status;
   cudaStream_t s = (cudaStream_t)stream;
 
@@ -1016,6 +1039,8 @@ extern "C" int skl_b200_launch_gemm_tc(const skl_b200_gemm_args *g, uint32_t *de
     TC_DISPATCH(256)
   } else if (bn == 128) {
     TC_DISPATCH(128)
+  } else if (bn == 16) {
+    TC_DISPATCH(16)
   } else {
     return launch_cfg<64, KIND_F16>(tmA, tmB, p, s);
   }

@@ -21,6 +21,11 @@
 
 enum { WS_A = 0, WS_B, WS_C, WS_ROW, WS_COL, WS_WIDEN, WS_COUNT };
 
+/* largest m the dp4a skinny kernel serves; above it the transposed tensor-core route is faster */
+#ifndef SKINNY_DP4A_MAX
+#define SKINNY_DP4A_MAX 2
+#endif
+
 typedef struct {
   void *ptr;
   size_t cap;
@@ -418,6 +423,29 @@ static void run_gemm(skl_b200_gemm_args *g) {
       path = SKL_B200_PATH_GEMV;
     else if (tc_ok && (double)M * (double)N * (double)K >= 32768.0)
       path = SKL_B200_PATH_TCGEN05;
+  }
+  /* Skinny int8 with more than SKINNY_DP4A_MAX activation rows: dp4a on the CUDA cores cannot keep up
+   * with HBM there (two warp instructions per clock per SM against 4*m dp4a per 16 weight bytes), so
+   * the problem is handed to the tensor-core kernel transposed -- the weights become the 128-row
+   * operand, the activations the (at most 16-column) narrow one, C is written through swapped strides. */
+  skl_b200_gemm_args swapped;
+  int dp4a_max = SKINNY_DP4A_MAX;
+  {
+    const char *e = getenv("SKL_B200_SKINNY_DP4A_MAX"); /* tuning override */
+    if (e) dp4a_max = atoi(e);
+  }
+  if (path == SKL_B200_PATH_GEMV && (int)g->m0 > dp4a_max && g_ctx.force_path != SKL_B200_PATH_GEMV) {
+    swapped = *g;
+    swapped.m0 = g->n0; swapped.n0 = g->m0;
+    swapped.a = g->b; swapped.rsa0 = g->csb0; swapped.csa0 = g->rsb0;
+    swapped.b = g->a; swapped.rsb0 = g->csa0; swapped.csb0 = g->rsa0;
+    swapped.rsc0 = g->csc0; swapped.csc0 = g->rsc0;
+    swapped.row_scale = g->col_scale; swapped.col_scale = g->row_scale;
+    swapped.col_scale_first = 1; /* keep (acc * row_scale[m]) * col_scale[n] */
+    if (skl_b200_gemm_tc_supported(&swapped)) {
+      g = &swapped;
+      path = SKL_B200_PATH_TCGEN05;
+    }
   }
   int rc = 0;
   const int prof = g_ctx.prof_ev && g_ctx.prof_used < g_ctx.prof_cap;

@@ -1,6 +1,8 @@
 """Runs one GEMM through the C ABI (host or device pointers) and checks it against the oracle."""
 from __future__ import annotations
 
+import os
+
 import numpy as np
 
 import helpers as H
@@ -68,7 +70,12 @@ def check_gemm_rc(lib, t, m, n, k, layout="rrr", alpha=1, beta=0, where="device"
     tc = H.I32 if t == H.I8 else H.F32
     C = H.Strided(tc, m, n, rsc, csc, g)
     want = C.copy()
-    orc.port_gemm_rc(t, t, m, n, k, alpha, A.view, rsa, csa, B.view, rsb, csb, beta, want.view, rsc, csc)
+    if m * n * max(k, 1) > (1 << 22):  # rows are independent: thread the oracle over row slabs
+        orc.rows_in_parallel(lambda i0, cnt: orc.port_gemm_rc(t, t, cnt, n, k, alpha, A.view[i0 * rsa:], rsa, csa, B.view,
+                                                              rsb, csb, beta, want.view[i0 * rsc:], rsc, csc),
+                             m, min(16, os.cpu_count() or 1))
+    else:
+        orc.port_gemm_rc(t, t, m, n, k, alpha, A.view, rsa, csa, B.view, rsb, csb, beta, want.view, rsc, csc)
     before = C.copy()
     lib.skl_b200_force_path(path)
     try:

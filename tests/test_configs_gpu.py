@@ -1,0 +1,208 @@
+"""The five BASELINE configurations at their full sizes, through the C ABI with device-resident operands.
+
+The scalar oracle cannot finish a full 4096^3 .. 16384 x 4096 x 14336 product in seconds, so each
+case is checked two ways: (1) exactly the reference's arithmetic on sampled rows of C -- every class of
+row inside a 128-row tile (first, last, interior, tile edges +-1) at full N and K, i.e. every column
+tile and every k slab; (2) a property over ALL elements that needs no oracle: for C = A.B the row sums
+obey sum_j C[i,j] = sum_k A[i,k] * (sum_j B[k,j]), exact in integers and to rounding in floats.
+Inputs are seeded synthetic tensors with the configured distributions (there is no dataset behind
+these configs).  Tolerances: int8 bit-exact; bf16/fp16 output <= 1e-2 relative plus the reference
+suite's forward bound; fp8 within one bf16 ulp of the oracle's rounded result plus that bound."""
+import os
+
+import numpy as np
+import pytest
+
+import helpers as H
+import skl_b200 as S
+from oracle import pyoracle as orc
+
+pytestmark = pytest.mark.gpu
+P = orc._p
+THREADS = min(16, os.cpu_count() or 1)
+
+
+def sample_rows(m, extra, seed):
+    base = [0, 1, 63, 64, 127, 128, 129, 255, 256, m // 2 - 1, m // 2, m - 129, m - 128, m - 1]
+    g = H.rng(seed)
+    rows = sorted(set([r for r in base if 0 <= r < m] + [int(v) for v in g.integers(0, m, extra)]))
+    return np.array(rows, dtype=np.int64)
+
+
+def oracle_rows(ta, a_rows, tb, b_host, rsb, csb, n, k, alpha, col_scale, tc):
+    """orc_gemm_ex on the sampled rows (rows threaded); a_rows is (r, k) contiguous."""
+    r = a_rows.shape[0]
+    out = np.zeros((r, n), H.NP_STORE[tc])
+
+    def slab(i0, cnt):
+        orc.port_gemm_ex(cnt, n, k, ta, a_rows[i0:], k, 1, tb, b_host, rsb, csb, alpha, None, col_scale, 0.0, tc,
+                         out[i0:], n, 1)
+
+    orc.rows_in_parallel(slab, r, THREADS)
+    return out
+
+
+def test_config1_companion_int8_8192_bit_exact_samples_and_checksum(skl):
+    import torch
+
+    m = n = k = 8192
+    g = torch.Generator(device="cuda")
+    g.manual_seed(1)
+    a = torch.randint(-128, 128, (m, k), dtype=torch.int8, device="cuda", generator=g)
+    b = torch.randint(-128, 128, (k, n), dtype=torch.int8, device="cuda", generator=g)
+    c = torch.full((m, n), 7, dtype=torch.int32, device="cuda")
+    skl.skl_gemm_i8_i8_i32_sm100a(m, n, k, 1, a.data_ptr(), k, b.data_ptr(), n, 0, c.data_ptr(), n)
+    S.check()
+    assert skl.skl_b200_last_path() == S.PATH_TCGEN05
+    # all elements: exact row-sum identity in int64
+    bsum = b.to(torch.int64).sum(dim=1)
+    want_rowsum = (a.to(torch.float64) @ bsum.to(torch.float64)).to(torch.int64)  # |values| < 2^53: exact
+    assert torch.equal(c.to(torch.int64).sum(dim=1), want_rowsum)
+    # sampled rows: the reference's own arithmetic
+    rows = sample_rows(m, 6, 11)
+    a_rows = a[torch.from_numpy(rows).cuda()].cpu().numpy()
+    b_host = b.cpu().numpy()
+    want = np.zeros((rows.size, n), np.int32)
+    orc.rows_in_parallel(lambda i0, cnt: orc.port_gemm_rc(H.I8, H.I8, cnt, n, k, 1, a_rows[i0:], k, 1, b_host, n, 1, 0,
+                                                          want[i0:], n, 1), rows.size, THREADS)
+    got = c[torch.from_numpy(rows).cuda()].cpu().numpy()
+    assert np.array_equal(got, want)
+
+
+@pytest.mark.parametrize("t,tdt", [(H.BF16, "bfloat16"), (H.F16, "float16")])
+def test_config2_half_4096(skl, t, tdt):
+    import torch
+
+    m = n = k = 4096
+    g = torch.Generator(device="cuda")
+    g.manual_seed(2)
+    dt = getattr(torch, tdt)
+    a = (torch.randn((m, k), device="cuda", generator=g) / 64.0).to(dt)
+    b = (torch.randn((k, n), device="cuda", generator=g) / 64.0).to(dt)
+    c = torch.zeros((m, n), dtype=dt, device="cuda")
+    skl.skl_gemm_ex_sm100a(m, n, k, t, a.data_ptr(), k, 1, t, b.data_ptr(), n, 1, 1.0, None, None, 0.0, t, c.data_ptr(), n, 1)
+    S.check()
+    assert skl.skl_b200_last_path() == S.PATH_TCGEN05
+    # all elements: row-sum identity to rounding (fp64 reference of the sums)
+    rs = c.to(torch.float64).sum(dim=1)
+    want = a.to(torch.float64) @ b.to(torch.float64).sum(dim=1)
+    scale = (a.abs().to(torch.float64) @ b.abs().to(torch.float64).sum(dim=1))
+    assert bool(((rs - want).abs() <= 4e-3 * scale + 1e-6).all())
+    rows = sample_rows(m, 4, 22)
+    idx = torch.from_numpy(rows).cuda()
+    a_rows = a[idx].view(torch.int16).cpu().numpy().view(np.uint16)
+    b_host = b.view(torch.int16).cpu().numpy().view(np.uint16)
+    want_rows = oracle_rows(t, a_rows, t, b_host, n, 1, n, k, 1.0, None, t)
+    got = c[idx].view(torch.int16).cpu().numpy().view(np.uint16)
+    ref = H.to_f32(t, want_rows).astype(np.float64)
+    out = H.to_f32(t, got).astype(np.float64)
+    bound = H.skl_forward_bound(t, a_rows, t, b_host, 1.0, 0.0, None, k)
+    assert np.all(np.abs(out - ref) <= 1e-2 * np.abs(ref) + bound)
+
+
+@pytest.mark.parametrize("ta", [H.F8E4M3, H.F8E5M2])
+def test_config3_fp8_8192_from_cvt(skl, ta):
+    """Operands produced by the library's cvt from fp32 N(0,1) with per-tensor scales amax/max_finite;
+    alpha = s_a * s_b; bf16 output.  ta = E5M2 is the mixed E5M2 x E4M3 run."""
+    import torch
+
+    m = n = k = 8192
+    g = torch.Generator(device="cuda")
+    g.manual_seed(3)
+    xa = torch.randn((m, k), device="cuda", generator=g)
+    xb = torch.randn((k, n), device="cuda", generator=g)
+    fmax_a = 448.0 if ta == H.F8E4M3 else 57344.0
+    s_a = float(xa.abs().max()) / fmax_a
+    s_b = float(xb.abs().max()) / 448.0
+    a8 = torch.empty((m, k), dtype=torch.uint8, device="cuda")
+    b8 = torch.empty((k, n), dtype=torch.uint8, device="cuda")
+    cvt_a = skl.skl_cvt_sat_f32_f8e4m3_sm100a if ta == H.F8E4M3 else skl.skl_cvt_sat_f32_f8e5m2_sm100a
+    cvt_a(a8.data_ptr(), xa.data_ptr(), 1.0 / s_a, m * k)
+    S.check()
+    skl.skl_cvt_sat_f32_f8e4m3_sm100a(b8.data_ptr(), xb.data_ptr(), 1.0 / s_b, k * n)
+    S.check()
+    rows = sample_rows(m, 2, 33)
+    idx = torch.from_numpy(rows).cuda()
+    # the conversion itself, byte-exact on the sampled rows of A and on a slab of B
+    xa_rows = xa[idx].cpu().numpy()
+    want8 = np.zeros(xa_rows.shape, np.uint8)
+    orc.port().orc_cvt_f32_f8(P(want8), P(xa_rows), 1.0 / s_a, xa_rows.size, ta, 1)
+    a_rows = a8[idx].cpu().numpy()
+    assert np.array_equal(a_rows, want8)
+    xb_slab = xb[:64].cpu().numpy()
+    wantb = np.zeros(xb_slab.shape, np.uint8)
+    orc.port().orc_cvt_f32_f8(P(wantb), P(xb_slab), 1.0 / s_b, xb_slab.size, H.F8E4M3, 1)
+    assert np.array_equal(b8[:64].cpu().numpy(), wantb)
+    del xa, xb
+    c = torch.zeros((m, n), dtype=torch.bfloat16, device="cuda")
+    alpha = float(np.float32(s_a) * np.float32(s_b))
+    skl.skl_gemm_ex_sm100a(m, n, k, ta, a8.data_ptr(), k, 1, H.F8E4M3, b8.data_ptr(), n, 1, alpha, None, None, 0.0, H.BF16,
+                           c.data_ptr(), n, 1)
+    S.check()
+    assert skl.skl_b200_last_path() == S.PATH_TCGEN05
+    b_host = b8.cpu().numpy()
+    want_rows = oracle_rows(ta, a_rows, H.F8E4M3, b_host, n, 1, n, k, alpha, None, H.BF16)
+    got = c[idx].view(torch.int16).cpu().numpy().view(np.uint16)
+    ref = H.bf16_bits_to_f32(want_rows).astype(np.float64)
+    out = H.bf16_bits_to_f32(got).astype(np.float64)
+    bound = H.skl_forward_bound(ta, a_rows, H.F8E4M3, b_host, alpha, 0.0, None, k)
+    assert np.all(np.abs(out - ref) <= H.bf16_ulp(ref) + bound)
+
+
+@pytest.mark.parametrize("mm", [1, 4, 16])
+def test_config4_rows_sum_property(skl, mm):
+    """Config 4 is covered element by element in test_gemv_ex_gpu.py; here the all-element property on
+    device-resident operands with the int32 SKL entry point (exact)."""
+    import torch
+
+    n, k = 14336, 4096
+    g = torch.Generator(device="cuda")
+    g.manual_seed(4)
+    w = torch.randint(-127, 128, (n, k), dtype=torch.int8, device="cuda", generator=g)
+    x = torch.randint(-127, 128, (mm, k), dtype=torch.int8, device="cuda", generator=g)
+    y = torch.zeros((mm, n), dtype=torch.int32, device="cuda")
+    skl.skl_gemm_i8rc_i8rc_i32rc_sm100a(mm, n, k, 1, x.data_ptr(), k, 1, w.data_ptr(), 1, k, 0, y.data_ptr(), n, 1)
+    S.check()
+    assert skl.skl_b200_last_path() == (S.PATH_GEMV if mm <= 2 else S.PATH_TCGEN05)
+    want = (x.to(torch.float64) @ w.to(torch.float64).T).to(torch.int32)  # exact: |acc| < 2^26
+    assert torch.equal(y, want)
+
+
+def test_config5_mlp_projection_full_size(skl):
+    import torch
+
+    m, k, n = 16384, 4096, 14336
+    g = torch.Generator(device="cuda")
+    g.manual_seed(5)
+    x = torch.randn((m, k), device="cuda", generator=g).to(torch.bfloat16)
+    w32 = torch.randn((k, n), device="cuda", generator=g) * 0.02
+    scale = (w32.abs().amax(dim=0) / 448.0).contiguous()
+    wq = (w32 / scale[None, :]).contiguous()
+    w8 = torch.empty((k, n), dtype=torch.uint8, device="cuda")
+    skl.skl_cvt_sat_f32_f8e4m3_sm100a(w8.data_ptr(), wq.data_ptr(), 1.0, k * n)
+    S.check()
+    del w32, wq
+    c = torch.zeros((m, n), dtype=torch.bfloat16, device="cuda")
+    skl.skl_gemm_ex_sm100a(m, n, k, H.BF16, x.data_ptr(), k, 1, H.F8E4M3, w8.data_ptr(), n, 1, 1.0, None, scale.data_ptr(),
+                           0.0, H.BF16, c.data_ptr(), n, 1)
+    S.check()
+    assert skl.skl_b200_last_path() == S.PATH_TCGEN05
+    # the same result from two column shards addressed as a column-parallel layer would (b + start, same rsb)
+    c2 = torch.zeros((m, n), dtype=torch.bfloat16, device="cuda")
+    for part in range(2):
+        s0, cnt = S.shard_columns(n, 2, part, 256)
+        skl.skl_gemm_ex_sm100a(m, cnt, k, H.BF16, x.data_ptr(), k, 1, H.F8E4M3, w8.data_ptr() + s0, n, 1, 1.0, None,
+                               scale.data_ptr() + 4 * s0, 0.0, H.BF16, c2.data_ptr() + 2 * s0, n, 1)
+        S.check()
+    assert torch.equal(c, c2)
+    rows = sample_rows(m, 2, 55)
+    idx = torch.from_numpy(rows).cuda()
+    a_rows = x[idx].view(torch.int16).cpu().numpy().view(np.uint16)
+    w_host = w8.cpu().numpy()
+    s_host = scale.cpu().numpy()
+    want_rows = oracle_rows(H.BF16, a_rows, H.F8E4M3, w_host, n, 1, n, k, 1.0, s_host, H.BF16)
+    got = c[idx].view(torch.int16).cpu().numpy().view(np.uint16)
+    ref = H.bf16_bits_to_f32(want_rows).astype(np.float64)
+    out = H.bf16_bits_to_f32(got).astype(np.float64)
+    bound = H.skl_forward_bound(H.BF16, a_rows, H.F8E4M3, w_host, 1.0, 0.0, None, k) * np.abs(s_host)[None, :]
+    assert np.all(np.abs(out - ref) <= 1e-2 * np.abs(ref) + bound)

@@ -16,8 +16,12 @@ def test_gemv_int32_bit_exact(skl, m):
     """Weights "[N][K]" (layout 'k'), activations row-major; int32 out with alpha/beta."""
     for (n, k, alpha, beta) in [(14336, 4096, 1, 0), (1000, 512, 2, 3), (5, 16, 1, 0), (257, 4096, 1, 1),
                                 (4099, 1024, 1, 0)]:
-        used = check_gemm_rc(skl, H.I8, m, n, k, "rkr", alpha, beta, where="device", seed=m)
+        # the dp4a streaming kernel, for every m it accepts
+        used = check_gemm_rc(skl, H.I8, m, n, k, "rkr", alpha, beta, where="device", seed=m, path=S.PATH_GEMV)
         assert used == S.PATH_GEMV
+        # automatic dispatch: dp4a up to m = 2, the transposed narrow tensor-core tile above
+        used = check_gemm_rc(skl, H.I8, m, n, k, "rkr", alpha, beta, where="device", seed=m)
+        assert used == (S.PATH_GEMV if m <= 2 else S.PATH_TCGEN05)
 
 
 def ex_case(skl, m, n, k, ta, tb, tc, layout, alpha, beta, use_rs, use_cs, where, seed, force=0, amp=1.0):
@@ -66,9 +70,12 @@ def test_config4_decode_gemv_dequantised(skl, m):
     per-row scale, fp32 out = ((float)acc * s_x[i]) * s_w[j].  The accumulator is exact, so the result
     must equal the oracle's bit for bit."""
     for where in ("device", "host"):
-        _, _, _, want, got, _, _ = ex_case(skl, m, 14336, 4096, H.I8, H.I8, H.F32, "rkr", 1.0, 0.0, True, True, where, 40 + m)
-        assert skl.skl_b200_last_path() == S.PATH_GEMV
-        assert np.array_equal(got.view(np.uint32), want.get().view(np.uint32))
+        for force in (0, S.PATH_GEMV):
+            _, _, _, want, got, _, _ = ex_case(skl, m, 14336, 4096, H.I8, H.I8, H.F32, "rkr", 1.0, 0.0, True, True, where,
+                                               40 + m, force)
+            expect = S.PATH_GEMV if (m <= 2 or force) else S.PATH_TCGEN05
+            assert skl.skl_b200_last_path() == expect
+            assert np.array_equal(got.view(np.uint32), want.get().view(np.uint32))
 
 
 @pytest.mark.parametrize("pair", [(H.I8, H.I8), (H.BF16, H.BF16), (H.F16, H.F16), (H.F8E4M3, H.F8E4M3),
