@@ -36,6 +36,7 @@ if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
 M_C5, K_C5, N_C5 = 16384, 4096, 14336
+C5_DRAM_BYTES_PER_LAUNCH_1GPU = 711.6e6 + 448.2e6
 
 
 def measured_peaks():
@@ -522,7 +523,9 @@ def main() -> None:
     roofline = {"bound": "tensor", "kernel": "gemm_tc_kernel<256, f16> (bf16 x bf16 -> fp32 in TMEM -> bf16)",
                 "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": (achieved / peak if achieved else None),
                 "peak_kind": f"{peak_kind}, of {peaks['source']}", "kernel_ms": kern_ms,
-                "traffic": None}
+                # dram__bytes_read + dram__bytes_write of one launch at the 1-GPU shape, from the ncu capture
+                # summarised in profiles/gemm_tc_kernel_bf16_c5.md (algorithmic: 0.70e9); not captured per shard
+                "traffic": (C5_DRAM_BYTES_PER_LAUNCH_1GPU if world == 1 else None)}
 
     line = {
         "metric": "gemm_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
