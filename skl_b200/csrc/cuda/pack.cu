@@ -115,6 +115,87 @@ __global__ void __launch_bounds__(256) relayout_kernel(const T *__restrict__ src
   }
 }
 
+// ---- fast path 1: no change of direction (source and destination share the unit-stride direction).
+// No shared memory: each thread moves one 16-byte group along the unit-stride direction, so a warp
+// reads and writes 512 contiguous bytes per row.  Requires 16-byte aligned groups on both sides (base,
+// other strides, block extents along the unit-stride direction all multiples of the group).
+template <typename T>
+__global__ void __launch_bounds__(256) copy_groups_kernel(const T *__restrict__ src, T *__restrict__ dst,
+                                                          const RelayoutParams p) {
+  constexpr uint32_t G = 16 / sizeof(T);  // elements per group
+  const bool fj = p.src.fast_j != 0;
+  const uint32_t fast_ext = fj ? p.NJ : p.MI, slow_ext = fj ? p.MI : p.NJ;
+  const uint32_t fast_src = fj ? p.n : p.m, slow_src = fj ? p.m : p.n;
+  const uint32_t groups = (fast_ext + G - 1) / G;
+  const uint64_t total = (uint64_t)groups * slow_ext;
+  for (uint64_t e = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (uint64_t)gridDim.x * blockDim.x) {
+    const uint32_t slow = (uint32_t)(e / groups), f0 = (uint32_t)(e - (uint64_t)slow * groups) * G;
+    const uint32_t i = fj ? slow : f0, j = fj ? f0 : slow;
+    T *d = dst + side_off(p.dst, i, j);
+    if (slow < slow_src && f0 + G <= fast_src && f0 + G <= fast_ext) {
+      *reinterpret_cast<uint4 *>(d) = __ldg(reinterpret_cast<const uint4 *>(src + side_off(p.src, i, j)));
+    } else {
+      // group touches the padding region or the ragged edge: element by element
+      for (uint32_t q = 0; q < G && f0 + q < fast_ext; ++q) {
+        const uint32_t ii = fj ? i : i + q, jj = fj ? j + q : j;
+        const T v = (ii < p.m && jj < p.n) ? src[side_off(p.src, ii, jj)] : (T)p.pad;
+        dst[side_off(p.dst, ii, jj)] = v;
+      }
+    }
+  }
+}
+
+// ---- fast path 2: plain 2-D transpose (source unit stride along j, destination along i) of 8-bit
+// elements.  Each thread owns a 4 x 4 byte micro-tile: four 4-byte loads (a warp reads 2 rows x 64
+// bytes per load), an in-register 4 x 4 byte transpose with byte permutes, four 4-byte stores into a
+// transposed shared-memory tile, then every thread writes one 16-byte run of a destination row.
+__global__ void __launch_bounds__(256) transpose8_kernel(const uint8_t *__restrict__ src, uint8_t *__restrict__ dst,
+                                                         const RelayoutParams p) {
+  __shared__ uint32_t tileT[RT][RT / 4 + 1];  // [j][i / 4], one pad word per row
+  const uint32_t num_tiles = p.tiles_i * p.tiles_j;
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+  for (uint32_t t = blockIdx.x; t < num_tiles; t += gridDim.x) {
+    const uint32_t i0 = (t / p.tiles_j) * RT, j0 = (t % p.tiles_j) * RT;
+    const bool full = i0 + RT <= p.m && j0 + RT <= p.n;
+    if (full) {
+      uint32_t r[4];
+#pragma unroll
+      for (int q = 0; q < 4; ++q)
+        r[q] = __ldg(reinterpret_cast<const uint32_t *>(src + (int64_t)(i0 + 4 * ty + q) * p.src.rs0 + j0 + 4 * tx));
+      // r[q] byte b = element (row 4ty+q, col 4tx+b); c[b] byte q = the same element
+      const uint32_t a0 = __byte_perm(r[0], r[1], 0x5140), a1 = __byte_perm(r[0], r[1], 0x7362);
+      const uint32_t b0 = __byte_perm(r[2], r[3], 0x5140), b1 = __byte_perm(r[2], r[3], 0x7362);
+      const uint32_t c0 = __byte_perm(a0, b0, 0x5410), c1 = __byte_perm(a0, b0, 0x7632);
+      const uint32_t c2 = __byte_perm(a1, b1, 0x5410), c3 = __byte_perm(a1, b1, 0x7632);
+      tileT[4 * tx + 0][ty] = c0;
+      tileT[4 * tx + 1][ty] = c1;
+      tileT[4 * tx + 2][ty] = c2;
+      tileT[4 * tx + 3][ty] = c3;
+      __syncthreads();
+      const int row = threadIdx.x >> 2, quarter = threadIdx.x & 3;  // destination row j, 16-byte run
+      const uint4 v = make_uint4(tileT[row][4 * quarter], tileT[row][4 * quarter + 1], tileT[row][4 * quarter + 2],
+                                 tileT[row][4 * quarter + 3]);
+      *reinterpret_cast<uint4 *>(dst + (int64_t)(j0 + row) * p.dst.cs0 + i0 + 16 * quarter) = v;
+      __syncthreads();
+    } else {
+      // ragged edge tile: element by element, still coalesced along each side's unit stride
+      uint8_t *tb = reinterpret_cast<uint8_t *>(&tileT[0][0]);  // viewed as [j][i] bytes, pitch 68
+      for (int e = threadIdx.x; e < RT * RT; e += 256) {
+        const int tj = e & 63, ti = e >> 6;
+        const uint32_t i = i0 + ti, j = j0 + tj;
+        if (i < p.m && j < p.n) tb[tj * 68 + ti] = src[(int64_t)i * p.src.rs0 + j];
+      }
+      __syncthreads();
+      for (int e = threadIdx.x; e < RT * RT; e += 256) {
+        const int ti = e & 63, tj = e >> 6;
+        const uint32_t i = i0 + ti, j = j0 + tj;
+        if (i < p.m && j < p.n) dst[(int64_t)j * p.dst.cs0 + i] = tb[tj * 68 + ti];
+      }
+      __syncthreads();
+    }
+  }
+}
+
 int relayout_grid(uint64_t tiles) {
   static int sms = 0;
   if (sms == 0) {
@@ -141,6 +222,19 @@ void finish_side(Side &s, const void *base, size_t esize) {
   s.vec_ok = ok ? 1 : 0;
 }
 
+// 16-byte groups along the unit-stride direction: contiguous, aligned, never split by a block edge.
+bool groups16_ok(const Side &s, const void *base, size_t esize) {
+  const int64_t vec = 16 / (int64_t)esize;
+  const int64_t unit = s.fast_j ? s.cs0 : s.rs0;
+  const int64_t other0 = s.fast_j ? s.rs0 : s.cs0;
+  if (unit != 1 || (reinterpret_cast<uintptr_t>(base) & 15u) != 0 || other0 % vec != 0) return false;
+  if (!s.plain) {
+    const uint32_t bfast = s.fast_j ? s.b0c : s.b0r;
+    if (bfast % vec != 0 || s.rs1 % vec != 0 || s.cs1 % vec != 0) return false;
+  }
+  return true;
+}
+
 int launch_relayout(size_t esize, const void *src, void *dst, RelayoutParams p, cudaStream_t s) {
   if (p.MI == 0 || p.NJ == 0) return 0;
   finish_side(p.src, src, esize);
@@ -148,6 +242,31 @@ int launch_relayout(size_t esize, const void *src, void *dst, RelayoutParams p, 
   p.tiles_i = (p.MI + RT - 1) / RT;
   p.tiles_j = (p.NJ + RT - 1) / RT;
   const int grid = relayout_grid((uint64_t)p.tiles_i * p.tiles_j);
+  if (p.src.fast_j == p.dst.fast_j && groups16_ok(p.src, src, esize) && groups16_ok(p.dst, dst, esize)) {
+    const uint64_t fast_ext = p.src.fast_j ? p.NJ : p.MI, slow_ext = p.src.fast_j ? p.MI : p.NJ;
+    const uint64_t total = ((fast_ext * esize + 15) / 16) * slow_ext;
+    const int g = relayout_grid((total + 255) / 256);
+    switch (esize) {
+      case 1:
+        copy_groups_kernel<uint8_t><<<g, 256, 0, s>>>((const uint8_t *)src, (uint8_t *)dst, p);
+        break;
+      case 2:
+        copy_groups_kernel<uint16_t><<<g, 256, 0, s>>>((const uint16_t *)src, (uint16_t *)dst, p);
+        break;
+      default:
+        copy_groups_kernel<uint32_t><<<g, 256, 0, s>>>((const uint32_t *)src, (uint32_t *)dst, p);
+        break;
+    }
+    SKLB_COUNT_LAUNCH();
+    return (int)cudaGetLastError();
+  }
+  if (esize == 1 && p.src.plain && p.dst.plain && p.src.fast_j && !p.dst.fast_j && p.src.cs0 == 1 && p.dst.rs0 == 1 &&
+      p.MI == p.m && p.NJ == p.n && (reinterpret_cast<uintptr_t>(src) & 3u) == 0 && p.src.rs0 % 4 == 0 &&
+      (reinterpret_cast<uintptr_t>(dst) & 15u) == 0 && p.dst.cs0 % 16 == 0) {
+    transpose8_kernel<<<grid, 256, 0, s>>>((const uint8_t *)src, (uint8_t *)dst, p);
+    SKLB_COUNT_LAUNCH();
+    return (int)cudaGetLastError();
+  }
   switch (esize) {
     case 1:
       relayout_kernel<uint8_t><<<grid, 256, 0, s>>>((const uint8_t *)src, (uint8_t *)dst, p);

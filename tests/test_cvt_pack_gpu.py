@@ -114,7 +114,7 @@ def test_integer_encoder_on_device_equals_oracle_sample(skl):
 
 
 PACK_CASES = [(128, 128, 8, 8), (13, 10, 4, 3), (1, 1, 1, 1), (65, 3, 64, 1), (7, 9, 16, 16), (200, 150, 32, 64),
-              (64, 64, 64, 64), (3, 300, 1, 128), (0, 4, 2, 2)]
+              (64, 64, 64, 64), (3, 300, 1, 128), (0, 4, 2, 2), (256, 192, 128, 64), (250, 176, 32, 48), (96, 512, 96, 16)]
 
 
 @pytest.mark.parametrize("e", [8, 16, 32])
@@ -161,8 +161,9 @@ def test_transpose(skl, e):
     dt = {8: np.uint8, 16: np.uint16, 32: np.uint32}[e]
     g = H.rng(300 + e)
     fn = getattr(skl, f"skl_transpose_e{e}_sm100a")
-    for (m, n) in [(0, 0), (1, 1), (63, 65), (64, 64), (65, 63), (127, 129), (257, 255), (1, 300), (300, 1), (1000, 513)]:
-        for pad_a, pad_t in ((0, 0), (3, 5)):
+    for (m, n) in [(0, 0), (1, 1), (63, 65), (64, 64), (65, 63), (127, 129), (257, 255), (1, 300), (300, 1), (1000, 513),
+                   (256, 320), (130, 200), (16, 1024)]:
+        for pad_a, pad_t in ((0, 0), (3, 5), ((-n) % 16, (-m) % 16)):  # the last keeps both pitches 16-byte multiples
             rsa, rsat = n + pad_a, m + pad_t
             a = g.integers(0, 255, size=max(1, m * rsa)).astype(dt)
             want = np.full(max(1, n * rsat), 0x33, dtype=dt)
