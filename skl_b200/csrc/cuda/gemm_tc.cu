@@ -47,6 +47,10 @@ struct TcParams {
   int M, N, K;
   int tiles_m, tiles_n, num_kb;
   int raster_gm;   // m-tiles per rasterisation group (tiles of one group are visited n-major)
+  // Tail splitting (one-CTA kernel): the tiles left over after the last full round of the grid are cut
+  // into `tail_split` column strips each, one strip per CTA, so the last round is short instead of idle.
+  int main_tiles, tail_round, tail_units, tail_split;
+  uint32_t idesc_tail;  // instruction descriptor with N = BN / tail_split
   int a_mn, b_mn;  // 1: operand is MN-major in global/shared memory
   uint32_t idesc;
   void *c;
@@ -203,6 +207,35 @@ __device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int
   mi = first + (r - ni * cur);
 }
 
+// Work unit `it` of this CTA in the one-CTA kernel: a full tile, or one strip of a split tail tile.
+struct TileUnit {
+  int m0, n0, ncols;
+  uint32_t idesc;
+};
+template <int BN>
+__device__ __forceinline__ bool get_unit(const TcParams &p, int it, TileUnit &u) {
+  const int t = (int)blockIdx.x + it * (int)gridDim.x;
+  int mi, ni;
+  if (t < p.main_tiles) {
+    tile_coords(t, p.tiles_m, p.tiles_n, p.raster_gm, mi, ni);
+    u.m0 = mi * BM;
+    u.n0 = ni * BN;
+    u.ncols = BN;
+    u.idesc = p.idesc;
+    return true;
+  }
+  if (it == p.tail_round && (int)blockIdx.x < p.tail_units) {
+    const int tt = p.main_tiles + (int)blockIdx.x / p.tail_split, sub = (int)blockIdx.x % p.tail_split;
+    tile_coords(tt, p.tiles_m, p.tiles_n, p.raster_gm, mi, ni);
+    u.ncols = BN / p.tail_split;
+    u.m0 = mi * BM;
+    u.n0 = ni * BN + sub * u.ncols;
+    u.idesc = p.idesc_tail;
+    return true;
+  }
+  return false;
+}
+
 // ---- two-CTA (cta_group::2) helpers
 __device__ __forceinline__ uint32_t cluster_ctarank() {
   uint32_t r;
@@ -253,9 +286,12 @@ __device__ __forceinline__ void umma_pair(uint32_t tmem_d, uint64_t adesc, uint6
         : "memory");
   }
 }
-// Arrives on the barrier at `cluster_bar` (either CTA of the pair) once all MMAs issued so far are done.
-__device__ __forceinline__ void umma_commit_pair(uint32_t cluster_bar) {
-  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_bar)
+// One commit that arrives on the barrier at the same shared-memory offset in both CTAs of the pair
+// (a commit signal, not a data load: nothing is copied).
+__device__ __forceinline__ void umma_commit_pair_both(uint32_t bar) {
+  const uint16_t mask = 3;
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar),
+               "h"(mask)
                : "memory");
 }
 
@@ -408,18 +444,15 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  const int num_tiles = p.tiles_m * p.tiles_n;
-
   if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer
     if (lane == 0) {
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int t = blockIdx.x; ok && t < num_tiles; t += gridDim.x) {
-        int mi, ni;
-        tile_coords(t, p.tiles_m, p.tiles_n, p.raster_gm, mi, ni);
-        const int m0 = mi * BM, n0 = ni * BN;
+      TileUnit u;
+      for (int it = 0; ok && get_unit<BN>(p, it, u); ++it) {
+        const int m0 = u.m0, n0 = u.n0;  // a tail strip loads the full-width B box from its first column
         for (int kb = 0; kb < p.num_kb; ++kb) {
           if (!mbar_wait(empty_bar + 8 * stage, phase ^ 1u, abort_flag, p.status, ERR_WAIT_EMPTY)) {
             ok = false;
@@ -460,7 +493,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
       const uint32_t a_lbo = p.a_mn ? ATOM_BYTES : 16, b_lbo = p.b_mn ? ATOM_BYTES : 16;
       const uint32_t a_adv = p.a_mn ? (UMMA_KE * SLAB_BYTES) >> 4 : 32 >> 4;
       const uint32_t b_adv = p.b_mn ? (UMMA_KE * SLAB_BYTES) >> 4 : 32 >> 4;
-      for (int t = blockIdx.x; ok && t < num_tiles; t += gridDim.x) {
+      TileUnit u;
+      for (int it = 0; ok && get_unit<BN>(p, it, u); ++it) {
         if (!mbar_wait(tempty_bar + 8 * acc, acc_phase ^ 1u, abort_flag, p.status, ERR_WAIT_TMEM_EMPTY))
           break;
         tc_fence_after();
@@ -475,7 +509,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
           const uint64_t da = make_smem_desc(sa, a_lbo, 1024), db = make_smem_desc(sb, b_lbo, 1024);
 #pragma unroll
           for (int k = 0; k < SLAB_BYTES / 32; ++k)
-            umma<KIND>(d_tmem, da + (uint64_t)(k * a_adv), db + (uint64_t)(k * b_adv), p.idesc,
+            umma<KIND>(d_tmem, da + (uint64_t)(k * a_adv), db + (uint64_t)(k * b_adv), u.idesc,
                        (uint32_t)((kb | k) != 0));
           umma_commit(empty_bar + 8 * stage);
           if (++stage == Cfg::STAGES) {
@@ -493,16 +527,15 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
     // ---------------------------------------------------------------- epilogue warps
     const int quad = warp & 3;
     uint32_t acc = 0, acc_phase = 0;
-    for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
-      int mi, ni;
-      tile_coords(t, p.tiles_m, p.tiles_n, p.raster_gm, mi, ni);
-      const int m0 = mi * BM, n0 = ni * BN;
+    TileUnit u;
+    for (int it = 0; get_unit<BN>(p, it, u); ++it) {
+      const int m0 = u.m0, n0 = u.n0;
       if (!mbar_wait(tfull_bar + 8 * acc, acc_phase, abort_flag, p.status, ERR_WAIT_TMEM_FULL)) break;
       tc_fence_after();
       const int row = m0 + quad * 32 + lane;
       const uint32_t taddr = tmem_base + acc * BN + ((uint32_t)(quad * 32) << 16);
 #pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 32) {
+      for (int c0 = 0; c0 < u.ncols; c0 += 32) {
         if (n0 + c0 >= p.N) break;  // uniform across the warp
         uint32_t r[32];
         if (BN >= 32)
@@ -535,11 +568,13 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
 // B; one thread of CTA 0 issues the MMAs for both; each CTA's TMEM receives the accumulator for its
 // 128 rows and all BN columns, and each CTA's epilogue warps store those rows.  Per SM this halves the
 // shared-memory traffic for B (both the TMA writes and the tensor-core reads), which is what bounds
-// the one-CTA kernel.  Synchronisation, all through mbarriers and without any multicast:
+// the one-CTA kernel.  Synchronisation, all through mbarriers:
 //   full[s]    lives in CTA 0; both CTAs' TMA loads credit their bytes to it (cta_group::2 loads);
-//   empty[s]   one per CTA; the MMA thread commits to both (two tcgen05.commit, local and remote);
-//   tfull[a]   one per CTA; committed to both when a tile's MMAs are issued;
+//   empty[s]   one per CTA; one tcgen05.commit signals the barrier at the same offset in both CTAs
+//              (two separate commits, local and remote, cost 5-10 % on every shape);
+//   tfull[a]   one per CTA; signalled in both the same way when a tile's MMAs are issued;
 //   tempty[a]  lives in CTA 0, 256 arrivals: the epilogue threads of both CTAs (remote arrive from CTA 1).
+// No operand data is ever multicast: each CTA fetches its own bytes.
 // The pair is held together by a cluster barrier after set-up and before TMEM is released.
 template <int BN>
 struct Tc2Config {
@@ -658,7 +693,6 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
       const uint32_t a_lbo = p.a_mn ? ATOM_BYTES : 16, b_lbo = p.b_mn ? ATOM_BYTES : 16;
       const uint32_t a_adv = p.a_mn ? (UMMA_KE * SLAB_BYTES) >> 4 : 32 >> 4;
       const uint32_t b_adv = p.b_mn ? (UMMA_KE * SLAB_BYTES) >> 4 : 32 >> 4;
-      const uint32_t peer_empty = mapa(empty_bar, 1), peer_tfull = mapa(tfull_bar, 1);
       for (int t = pair; ok && t < num_tiles; t += num_pairs) {
         if (!mbar_wait(tempty_bar + 8 * acc, acc_phase ^ 1u, abort_flag, p.status, ERR_WAIT_TMEM_EMPTY))
           break;
@@ -676,16 +710,14 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
           for (int k = 0; k < SLAB_BYTES / 32; ++k)
             umma_pair<KIND>(d_tmem, da + (uint64_t)(k * a_adv), db + (uint64_t)(k * b_adv), p.idesc,
                             (uint32_t)((kb | k) != 0));
-          umma_commit_pair(empty_bar + 8 * stage);
-          umma_commit_pair(peer_empty + 8 * stage);
+          umma_commit_pair_both(empty_bar + 8 * stage);
           if (++stage == Cfg::STAGES) {
             stage = 0;
             phase ^= 1u;
           }
         }
         if (!ok) break;
-        umma_commit_pair(tfull_bar + 8 * acc);
-        umma_commit_pair(peer_tfull + 8 * acc);
+        umma_commit_pair_both(tfull_bar + 8 * acc);
         acc ^= 1u;
         if (acc == 0) acc_phase ^= 1u;
       }
@@ -1001,6 +1033,29 @@ extern "C" int skl_b200_launch_gemm_tc(const skl_b200_gemm_args *g, uint32_t *de
     if (gm < 1) gm = 1;
     if (gm > p.tiles_m) gm = p.tiles_m;
     p.raster_gm = (int)gm;
+  }
+  {
+    // tail splitting: only the one-CTA kernel with 256-wide tiles; strips must keep whole swizzle atoms
+    const int T = p.tiles_m * p.tiles_n, G = T < sm_count() ? T : sm_count();
+    p.main_tiles = T;
+    p.tail_round = 0;
+    p.tail_units = 0;
+    p.tail_split = 1;
+    const int rem = T % G;
+    const char *e = getenv("SKL_B200_TC_TAIL_SPLIT");
+    const bool enabled = !(e && atoi(e) == 0);
+    if (enabled && !pair && bn == 256 && T > G && rem > 0 && rem * 2 <= G) {
+      const int atom_cols = vb.mn_major ? SLAB_BYTES / es : 32;  // columns per MN-major box; else the epilogue chunk
+      int split = 2;
+      if (rem * 4 <= G && bn / 4 >= atom_cols && bn / 4 >= 32) split = 4;
+      if (bn / split >= atom_cols) {
+        p.main_tiles = T - rem;
+        p.tail_round = p.main_tiles / G;
+        p.tail_split = split;
+        p.tail_units = rem * split;
+      }
+    }
+    p.idesc_tail = (p.idesc & ~(0x3Fu << 17)) | ((uint32_t)((bn / p.tail_split) >> 3) << 17);
   }
   p.c = g->c;
   p.rsc = g->rsc0;

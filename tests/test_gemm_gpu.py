@@ -151,3 +151,16 @@ def test_packed_operands(skl, t):
                     else:
                         assert np.allclose(got, want, rtol=1e-5, atol=1e-5)
                         assert np.array_equal(got[-9:], want[-9:])
+
+
+@pytest.mark.parametrize("t", ALL_T)
+@pytest.mark.parametrize("layout", ["rkr", "rrr"])
+def test_tail_round_is_split_into_strips(skl, t, layout, monkeypatch):
+    """Tile counts that leave a short last round on a 148-SM part (150 and 160 tiles of 128 x 256): the
+    leftover tiles are cut into 4 or 2 column strips; results must not depend on the split."""
+    for (m, n) in [(128 * 30, 256 * 5), (128 * 32 - 7, 256 * 5 - 9)]:
+        for split in ("1", "0"):
+            monkeypatch.setenv("SKL_B200_TC_TAIL_SPLIT", split)
+            monkeypatch.setenv("SKL_B200_TC_PAIR", "0")
+            check_gemm_rc(skl, t, m, n, 256, layout, 1, 0, where="device", path=S.PATH_TCGEN05, align=16,
+                          expect_path=S.PATH_TCGEN05, seed=5, all_codes=False)
