@@ -21,6 +21,8 @@
 
 enum { WS_A = 0, WS_B, WS_C, WS_ROW, WS_COL, WS_WIDEN, WS_COUNT };
 
+#define PIPE_MAX_CHUNKS 16
+
 /* largest m the dp4a skinny kernel serves; above it the transposed tensor-core route is faster */
 #ifndef SKINNY_DP4A_MAX
 #define SKINNY_DP4A_MAX 2
@@ -45,9 +47,13 @@ typedef struct {
   /* optional timing of the main GEMM kernel of each call: pairs of events on the launch stream */
   cudaEvent_t *prof_ev;
   int prof_cap, prof_used;
+  /* row-chunk pipeline for host operands */
+  int pipe_ready;
+  cudaStream_t s_in, s_out;
+  cudaEvent_t ev_in[PIPE_MAX_CHUNKS], ev_done[PIPE_MAX_CHUNKS], ev_ready;
 } ctx_t;
 
-static __thread ctx_t g_ctx = {0, 0, SKL_B200_OK, {0}, SKL_B200_PATH_NONE, 0, 0, -1, 0, {{0, 0}}, 0, 0, 0};
+static __thread ctx_t g_ctx = {0, 0, SKL_B200_OK, {0}, SKL_B200_PATH_NONE, 0, 0, -1, 0, {{0, 0}}, 0, 0, 0, 0, 0, 0, {0}, {0}, 0};
 
 static void set_err(skl_b200_status_t s) {
   if (g_ctx.status == SKL_B200_OK) g_ctx.status = s;
@@ -71,6 +77,16 @@ static void release_resources(void) {
   }
   if (g_ctx.dev_status) (void)cudaFreeHost(g_ctx.dev_status);
   g_ctx.dev_status = 0;
+  if (g_ctx.pipe_ready) {
+    (void)cudaStreamDestroy(g_ctx.s_in);
+    (void)cudaStreamDestroy(g_ctx.s_out);
+    for (int i = 0; i < PIPE_MAX_CHUNKS; ++i) {
+      (void)cudaEventDestroy(g_ctx.ev_in[i]);
+      (void)cudaEventDestroy(g_ctx.ev_done[i]);
+    }
+    (void)cudaEventDestroy(g_ctx.ev_ready);
+    g_ctx.pipe_ready = 0;
+  }
   g_ctx.device = -1;
 }
 
@@ -318,99 +334,42 @@ static int stage_out_end(const out_stage_t *o) {
 
 /* ------------------------------------------------------------------ GEMM driver */
 
-static void run_gemm(skl_b200_gemm_args *g) {
-  if (!begin_call()) return;
-  g_ctx.last_path = SKL_B200_PATH_NONE;
+/* bf16 x fp8: widen the fp8 operand exactly to bf16 when that makes the tensor-core path usable.
+ * Rewrites g->b / tb / strides to the widened copy.  Returns 0 on failure. */
+static int widen_fp8_operand(skl_b200_gemm_args *g) {
+  const uint64_t K = g->k0 * g->k1;
+  if (!(g->ta == SKL_DT_BF16 && (g->tb == SKL_DT_F8E4M3 || g->tb == SKL_DT_F8E5M2) && g->k1 == 1 && g->n1 == 1 &&
+        g->m1 == 1 && K != 0 && g_ctx.force_path != SKL_B200_PATH_GENERIC))
+    return 1;
+  size_t rows = 0, cols = 0, ld_src = 0;
+  int k_major = 0;
+  if (g->rsb0 == 1 && (g->n0 == 1 || (uint64_t)g->csb0 >= g->k0)) {
+    rows = (size_t)g->n0; cols = (size_t)g->k0; ld_src = (size_t)g->csb0; k_major = 1;
+  } else if (g->csb0 == 1 && (g->k0 == 1 || (uint64_t)g->rsb0 >= g->n0)) {
+    rows = (size_t)g->k0; cols = (size_t)g->n0; ld_src = (size_t)g->rsb0;
+  }
+  if (rows == 0) return 1;
+  size_t ld_dst = (cols + 7) & ~(size_t)7; /* 16-byte aligned rows */
+  void *wide = workspace(WS_WIDEN, rows * ld_dst * 2);
+  if (!wide) return 0;
+  if (!cuda_ok((cudaError_t)skl_b200_launch_cvt_f8_to_bf16_2d(wide, ld_dst, g->b, ld_src, g->tb, rows, cols, g_ctx.stream)))
+    return 0;
+  g->b = wide;
+  g->tb = SKL_DT_BF16;
+  if (k_major) {
+    g->rsb0 = 1;
+    g->csb0 = (int64_t)ld_dst;
+  } else {
+    g->rsb0 = (int64_t)ld_dst;
+    g->csb0 = 1;
+  }
+  return 1;
+}
+
+/* Chooses the kernel family for a device-resident problem and enqueues it on the library stream. */
+static int dispatch_launch(const skl_b200_gemm_args *gin) {
+  skl_b200_gemm_args local = *gin, *g = &local;
   const uint64_t M = g->m0 * g->m1, N = g->n0 * g->n1, K = g->k0 * g->k1;
-  if (M == 0 || N == 0) {
-    end_call();
-    return;
-  }
-  if (!g->c || (K != 0 && (!g->a || !g->b))) {
-    set_err(SKL_B200_ERR_INVALID_ARGUMENT);
-    return;
-  }
-  const size_t ea = dt_size(g->ta), eb = dt_size(g->tb), ec = dt_size(g->tc);
-  int host_any = 0;
-
-  /* operands */
-  if (K != 0 && !on_device(g->a)) {
-    host_any = 1;
-    size_t bytes = span4(g->m0, g->k0, g->m1, g->k1, g->rsa0, g->csa0, g->rsa1, g->csa1) * ea;
-    g->a = stage_in(WS_A, g->a, bytes);
-    if (!g->a) return;
-  }
-  if (K != 0 && !on_device(g->b)) {
-    host_any = 1;
-    size_t bytes = span4(g->k0, g->n0, g->k1, g->n1, g->rsb0, g->csb0, g->rsb1, g->csb1) * eb;
-    g->b = stage_in(WS_B, g->b, bytes);
-    if (!g->b) return;
-  }
-  if (g->row_scale && !on_device(g->row_scale)) {
-    host_any = 1;
-    g->row_scale = (const float *)stage_in(WS_ROW, g->row_scale, (size_t)M * sizeof(float));
-    if (!g->row_scale) return;
-  }
-  if (g->col_scale && !on_device(g->col_scale)) {
-    host_any = 1;
-    g->col_scale = (const float *)stage_in(WS_COL, g->col_scale, (size_t)N * sizeof(float));
-    if (!g->col_scale) return;
-  }
-
-  /* output */
-  out_stage_t out;
-  int c_host = !on_device(g->c);
-  if (c_host) {
-    host_any = 1;
-    size_t span = span4(g->m0, g->n0, g->m1, g->n1, g->rsc0, g->csc0, g->rsc1, g->csc1) * ec;
-    int need_old = (g->epilogue == SKL_EPI_INT) ? (g->beta_i != 0) : (g->beta_f != 0.0f);
-    size_t width = 0, height = 0, pitch = 0;
-    if (g->m1 == 1 && g->n1 == 1) {
-      if (g->csc0 == 1 && (uint64_t)g->rsc0 >= g->n0) {
-        width = (size_t)g->n0 * ec;
-        height = (size_t)g->m0;
-        pitch = (size_t)g->rsc0 * ec;
-      } else if (g->rsc0 == 1 && (uint64_t)g->csc0 >= g->m0) {
-        width = (size_t)g->m0 * ec;
-        height = (size_t)g->n0;
-        pitch = (size_t)g->csc0 * ec;
-      }
-      if (height == 1) pitch = width; /* a single run: any pitch >= width is legal for the 2-D copy */
-    }
-    if (!stage_out_begin(&out, g->c, span, width, height, pitch, need_old)) return;
-    g->c = out.dev;
-  }
-
-  /* bf16 x fp8: widen the fp8 operand exactly to bf16 when that makes the tensor-core path usable */
-  if (g->ta == SKL_DT_BF16 && (g->tb == SKL_DT_F8E4M3 || g->tb == SKL_DT_F8E5M2) && g->k1 == 1 &&
-      g->n1 == 1 && g->m1 == 1 && K != 0 && g_ctx.force_path != SKL_B200_PATH_GENERIC) {
-    size_t rows = 0, cols = 0, ld_src = 0;
-    int k_major = 0;
-    if (g->rsb0 == 1 && (g->n0 == 1 || (uint64_t)g->csb0 >= g->k0)) {
-      rows = (size_t)g->n0; cols = (size_t)g->k0; ld_src = (size_t)g->csb0; k_major = 1;
-    } else if (g->csb0 == 1 && (g->k0 == 1 || (uint64_t)g->rsb0 >= g->n0)) {
-      rows = (size_t)g->k0; cols = (size_t)g->n0; ld_src = (size_t)g->rsb0;
-    }
-    if (rows != 0) {
-      size_t ld_dst = (cols + 7) & ~(size_t)7; /* 16-byte aligned rows */
-      void *wide = workspace(WS_WIDEN, rows * ld_dst * 2);
-      if (!wide) return;
-      if (!cuda_ok((cudaError_t)skl_b200_launch_cvt_f8_to_bf16_2d(wide, ld_dst, g->b, ld_src, g->tb, rows, cols,
-                                                                 g_ctx.stream)))
-        return;
-      g->b = wide;
-      g->tb = SKL_DT_BF16;
-      if (k_major) {
-        g->rsb0 = 1;
-        g->csb0 = (int64_t)ld_dst;
-      } else {
-        g->rsb0 = (int64_t)ld_dst;
-        g->csb0 = 1;
-      }
-    }
-  }
-
-  /* dispatch */
   int path = SKL_B200_PATH_GENERIC;
   const int gemv_ok = K != 0 && skl_b200_gemv_i8_supported(g);
   const int tc_ok = K != 0 && skl_b200_gemm_tc_supported(g);
@@ -452,11 +411,11 @@ static void run_gemm(skl_b200_gemm_args *g) {
   if (prof) (void)cudaEventRecord(g_ctx.prof_ev[2 * g_ctx.prof_used], (cudaStream_t)g_ctx.stream);
   if (path == SKL_B200_PATH_GEMV) {
     uint32_t *st = device_status_words();
-    if (!st) return;
+    if (!st) return 0;
     rc = skl_b200_launch_gemv_i8(g, st, g_ctx.stream);
   } else if (path == SKL_B200_PATH_TCGEN05) {
     uint32_t *st = device_status_words();
-    if (!st) return;
+    if (!st) return 0;
     rc = skl_b200_launch_gemm_tc(g, st, g_ctx.stream);
   } else {
     rc = skl_b200_launch_gemm_generic(g, g_ctx.stream);
@@ -466,7 +425,179 @@ static void run_gemm(skl_b200_gemm_args *g) {
     g_ctx.prof_used++;
   }
   g_ctx.last_path = (skl_b200_path_t)path;
-  if (!cuda_ok((cudaError_t)rc)) return;
+  return cuda_ok((cudaError_t)rc);
+}
+
+/* Side streams and events for the row-chunk pipeline (created on first use, kept per thread). */
+static int pipe_resources(void) {
+  if (g_ctx.pipe_ready) return 1;
+  if (!cuda_ok(cudaStreamCreateWithFlags(&g_ctx.s_in, cudaStreamNonBlocking))) return 0;
+  if (!cuda_ok(cudaStreamCreateWithFlags(&g_ctx.s_out, cudaStreamNonBlocking))) return 0;
+  for (int i = 0; i < PIPE_MAX_CHUNKS; ++i) {
+    if (!cuda_ok(cudaEventCreateWithFlags(&g_ctx.ev_in[i], cudaEventDisableTiming))) return 0;
+    if (!cuda_ok(cudaEventCreateWithFlags(&g_ctx.ev_done[i], cudaEventDisableTiming))) return 0;
+  }
+  if (!cuda_ok(cudaEventCreateWithFlags(&g_ctx.ev_ready, cudaEventDisableTiming))) return 0;
+  g_ctx.pipe_ready = 1;
+  return 1;
+}
+
+/* Large row-major problems with A and/or C in host memory: instead of "copy everything in, compute,
+ * copy everything out" the rows are cut into chunks and the three phases overlap -- chunk i+1's rows
+ * of A travel host-to-device while chunk i is computed and chunk i-1's rows of C travel back, the two
+ * copy directions on their own streams so the link runs full duplex.  B, the scale vectors and the
+ * fp8 widening are done once, before the first chunk.  Returns 1 if the pipeline ran (successfully or
+ * not), 0 if the problem does not qualify and the caller should take the plain route. */
+static int run_gemm_pipelined(skl_b200_gemm_args *g, int a_host, int c_host, int *host_any) {
+  const uint64_t M = g->m0, N = g->n0, K = g->k0;
+  if (g->m1 != 1 || g->n1 != 1 || g->k1 != 1 || K == 0 || M < 4096) return 0;
+  if (!a_host && !c_host) return 0;
+  const size_t ea = dt_size(g->ta), ec = dt_size(g->tc);
+  if (a_host && !(g->csa0 == 1 && (uint64_t)g->rsa0 >= K)) return 0;
+  if (!(g->csc0 == 1 && (uint64_t)g->rsc0 >= N)) return 0;
+  if ((a_host ? M * K * ea : 0) + (c_host ? M * N * ec : 0) < ((size_t)32 << 20)) return 0;
+  {
+    const char *e = getenv("SKL_B200_HOST_PIPELINE"); /* 0 disables */
+    if (e && atoi(e) == 0) return 0;
+  }
+  if (!pipe_resources()) return 1;
+  *host_any = 1;
+  cudaStream_t main_s = (cudaStream_t)g_ctx.stream;
+
+  const void *host_a = g->a;
+  void *host_c = g->c;
+  uint8_t *dev_a = (uint8_t *)g->a, *dev_c = (uint8_t *)g->c;
+  if (a_host) {
+    dev_a = (uint8_t *)workspace(WS_A, (size_t)((M - 1) * (uint64_t)g->rsa0 + K) * ea);
+    if (!dev_a) return 1;
+  }
+  if (c_host) {
+    dev_c = (uint8_t *)workspace(WS_C, (size_t)((M - 1) * (uint64_t)g->rsc0 + N) * ec);
+    if (!dev_c) return 1;
+  }
+  if (!widen_fp8_operand(g)) return 1;
+  /* the copy streams start after everything already queued on the library stream (B, scales, widening) */
+  if (!cuda_ok(cudaEventRecord(g_ctx.ev_ready, main_s))) return 1;
+  if (!cuda_ok(cudaStreamWaitEvent(g_ctx.s_out, g_ctx.ev_ready, 0))) return 1;
+
+  int chunks = (int)(M / 2048);
+  if (chunks > PIPE_MAX_CHUNKS) chunks = PIPE_MAX_CHUNKS;
+  if (chunks < 2) chunks = 2;
+  const uint64_t rows_per = ((M + chunks - 1) / chunks + 255) / 256 * 256; /* whole 256-row tiles */
+  const int need_old = (g->epilogue == SKL_EPI_INT) ? (g->beta_i != 0) : (g->beta_f != 0.0f);
+  int c_idx = 0;
+  for (uint64_t i0 = 0; i0 < M; i0 += rows_per, ++c_idx) {
+    const uint64_t rows = (M - i0) < rows_per ? (M - i0) : rows_per;
+    const size_t a_off = (size_t)(i0 * (uint64_t)g->rsa0) * ea, c_off = (size_t)(i0 * (uint64_t)g->rsc0) * ec;
+    if (a_host) {
+      if (!cuda_ok(cudaMemcpy2DAsync(dev_a + a_off, (size_t)g->rsa0 * ea, (const uint8_t *)host_a + a_off,
+                                     (size_t)g->rsa0 * ea, (size_t)K * ea, (size_t)rows, cudaMemcpyHostToDevice,
+                                     g_ctx.s_in)))
+        return 1;
+    }
+    if (c_host && need_old) {
+      if (!cuda_ok(cudaMemcpy2DAsync(dev_c + c_off, (size_t)g->rsc0 * ec, (const uint8_t *)host_c + c_off,
+                                     (size_t)g->rsc0 * ec, (size_t)N * ec, (size_t)rows, cudaMemcpyHostToDevice,
+                                     g_ctx.s_in)))
+        return 1;
+    }
+    if (a_host || (c_host && need_old)) {
+      if (!cuda_ok(cudaEventRecord(g_ctx.ev_in[c_idx], g_ctx.s_in))) return 1;
+      if (!cuda_ok(cudaStreamWaitEvent(main_s, g_ctx.ev_in[c_idx], 0))) return 1;
+    }
+    skl_b200_gemm_args part = *g;
+    part.m0 = rows;
+    part.a = dev_a + a_off;
+    part.c = dev_c + c_off;
+    if (part.row_scale) part.row_scale += i0;
+    if (!dispatch_launch(&part)) return 1;
+    if (c_host) {
+      if (!cuda_ok(cudaEventRecord(g_ctx.ev_done[c_idx], main_s))) return 1;
+      if (!cuda_ok(cudaStreamWaitEvent(g_ctx.s_out, g_ctx.ev_done[c_idx], 0))) return 1;
+      if (!cuda_ok(cudaMemcpy2DAsync((uint8_t *)host_c + c_off, (size_t)g->rsc0 * ec, dev_c + c_off,
+                                     (size_t)g->rsc0 * ec, (size_t)N * ec, (size_t)rows, cudaMemcpyDeviceToHost,
+                                     g_ctx.s_out)))
+        return 1;
+    }
+  }
+  (void)cuda_ok(cudaStreamSynchronize(g_ctx.s_in));
+  (void)cuda_ok(cudaStreamSynchronize(g_ctx.s_out));
+  return 1;
+}
+
+static void run_gemm(skl_b200_gemm_args *g) {
+  if (!begin_call()) return;
+  g_ctx.last_path = SKL_B200_PATH_NONE;
+  const uint64_t M = g->m0 * g->m1, N = g->n0 * g->n1, K = g->k0 * g->k1;
+  if (M == 0 || N == 0) {
+    end_call();
+    return;
+  }
+  if (!g->c || (K != 0 && (!g->a || !g->b))) {
+    set_err(SKL_B200_ERR_INVALID_ARGUMENT);
+    return;
+  }
+  const size_t ea = dt_size(g->ta), eb = dt_size(g->tb), ec = dt_size(g->tc);
+  int host_any = 0;
+  const int a_host = K != 0 && !on_device(g->a);
+  const int c_host = !on_device(g->c);
+
+  /* B and the scale vectors are staged whole in either route */
+  if (K != 0 && !on_device(g->b)) {
+    host_any = 1;
+    size_t bytes = span4(g->k0, g->n0, g->k1, g->n1, g->rsb0, g->csb0, g->rsb1, g->csb1) * eb;
+    g->b = stage_in(WS_B, g->b, bytes);
+    if (!g->b) return;
+  }
+  if (g->row_scale && !on_device(g->row_scale)) {
+    host_any = 1;
+    g->row_scale = (const float *)stage_in(WS_ROW, g->row_scale, (size_t)M * sizeof(float));
+    if (!g->row_scale) return;
+  }
+  if (g->col_scale && !on_device(g->col_scale)) {
+    host_any = 1;
+    g->col_scale = (const float *)stage_in(WS_COL, g->col_scale, (size_t)N * sizeof(float));
+    if (!g->col_scale) return;
+  }
+
+  if (run_gemm_pipelined(g, a_host, c_host, &host_any)) {
+    finish(host_any);
+    end_call();
+    return;
+  }
+
+  if (a_host) {
+    host_any = 1;
+    size_t bytes = span4(g->m0, g->k0, g->m1, g->k1, g->rsa0, g->csa0, g->rsa1, g->csa1) * ea;
+    g->a = stage_in(WS_A, g->a, bytes);
+    if (!g->a) return;
+  }
+
+  /* output */
+  out_stage_t out;
+  if (c_host) {
+    host_any = 1;
+    size_t span = span4(g->m0, g->n0, g->m1, g->n1, g->rsc0, g->csc0, g->rsc1, g->csc1) * ec;
+    int need_old = (g->epilogue == SKL_EPI_INT) ? (g->beta_i != 0) : (g->beta_f != 0.0f);
+    size_t width = 0, height = 0, pitch = 0;
+    if (g->m1 == 1 && g->n1 == 1) {
+      if (g->csc0 == 1 && (uint64_t)g->rsc0 >= g->n0) {
+        width = (size_t)g->n0 * ec;
+        height = (size_t)g->m0;
+        pitch = (size_t)g->rsc0 * ec;
+      } else if (g->rsc0 == 1 && (uint64_t)g->csc0 >= g->m0) {
+        width = (size_t)g->m0 * ec;
+        height = (size_t)g->n0;
+        pitch = (size_t)g->csc0 * ec;
+      }
+      if (height == 1) pitch = width; /* a single run: any pitch >= width is legal for the 2-D copy */
+    }
+    if (!stage_out_begin(&out, g->c, span, width, height, pitch, need_old)) return;
+    g->c = out.dev;
+  }
+
+  if (!widen_fp8_operand(g)) return;
+  if (!dispatch_launch(g)) return;
 
   if (c_host && !stage_out_end(&out)) return;
   finish(host_any);

@@ -164,3 +164,34 @@ def test_tail_round_is_split_into_strips(skl, t, layout, monkeypatch):
             monkeypatch.setenv("SKL_B200_TC_PAIR", "0")
             check_gemm_rc(skl, t, m, n, 256, layout, 1, 0, where="device", path=S.PATH_TCGEN05, align=16,
                           expect_path=S.PATH_TCGEN05, seed=5, all_codes=False)
+
+
+@pytest.mark.parametrize("beta", [0.0, 0.5])
+def test_large_host_operands_take_the_row_chunk_pipeline(skl, beta, monkeypatch):
+    """A and C in host memory and large enough for the chunked copy/compute/copy-back pipeline: the result
+    must equal the unpipelined route bit for bit, and C's padding columns must survive."""
+    import torch
+
+    m, n, k, rsc = 4096 + 300, 2048 + 8, 1024, 2048 + 24
+    g = H.rng(77)
+    a = H.random_operand(H.BF16, (m, k), g)
+    b = H.random_operand(H.BF16, (k, n), g)
+    c0 = g.uniform(-1, 1, (m, rsc)).astype(np.float32)
+    outs = []
+    for mode in ("1", "0"):
+        monkeypatch.setenv("SKL_B200_HOST_PIPELINE", mode)
+        c = c0.copy()
+        skl.skl_gemm_bf16rc_bf16rc_f32rc_sm100a(m, n, k, 1.5, S.ptr(a), k, 1, S.ptr(b), n, 1, beta, S.ptr(c), rsc, 1)
+        S.check()
+        assert skl.skl_b200_last_path() == S.PATH_TCGEN05
+        assert np.array_equal(c[:, n:], c0[:, n:]), "columns outside the matrix were written"
+        outs.append(c)
+    assert np.array_equal(outs[0], outs[1])
+    # and against the oracle on a few rows
+    from oracle import pyoracle as orc
+    rows = [0, 1, 2047, 2048, 2303, 2304, m - 1]
+    for r in rows:
+        want = c0[r:r + 1, :n].copy()
+        orc.port_gemm_rc(H.BF16, H.BF16, 1, n, k, 1.5, a[r:], k, 1, b, n, 1, beta, want, n, 1)
+        bound = H.skl_forward_bound(H.BF16, a[r:r + 1], H.BF16, b, 1.5, beta, c0[r:r + 1, :n], k)
+        assert np.all(np.abs(outs[0][r:r + 1, :n].astype(np.float64) - want) <= bound)
