@@ -233,6 +233,34 @@ SKL_FUNC void skl_gemm_ex_sm100a(size_t m, size_t n, size_t k, skl_b200_dtype_t 
                                  const float *col_scale, float beta, skl_b200_dtype_t tc, void *c,
                                  size_t rsc, size_t csc);
 
+/* ------------------------------------------------------------------ GEMM with fused epilogue kernels
+ * SKL's matrix-engine GEMMs apply a "fused kernel" to every accumulator tile before it is stored
+ * (src/gemm/fused-kernel-API.md:85-108); the one it ships is alpha/beta scaling, the two it documents as
+ * examples are adding a bias row vector (:170-192) and tracking the global maximum of the product
+ * (:194-217).  This entry provides those on top of the extended epilogue above:
+ *
+ *     v = alpha*(float)acc;  v *= row_scale[i];  v *= col_scale[j];     (each when its pointer != NULL)
+ *     v = v + bias[j]                      when bias != NULL (n entries)
+ *     v = beta*(float)C[i,j] + v           when beta != 0
+ *     *global_max = max(*global_max, v)    when global_max != NULL (NaN results are ignored; the caller
+ *                                          initialises it, e.g. to -INFINITY; updated atomically)
+ *     C[i,j] = narrow(v)
+ *
+ * Pointers in the struct may be host or device memory, like every other argument. */
+typedef struct skl_b200_fused {
+  float alpha;
+  float beta;
+  const float *row_scale; /* m entries or NULL */
+  const float *col_scale; /* n entries or NULL */
+  const float *bias;      /* n entries or NULL */
+  float *global_max;      /* one float or NULL */
+} skl_b200_fused_t;
+
+SKL_FUNC void skl_gemm_fused_sm100a(size_t m, size_t n, size_t k, skl_b200_dtype_t ta, const void *a,
+                                    size_t rsa, size_t csa, skl_b200_dtype_t tb, const void *b,
+                                    size_t rsb, size_t csb, const skl_b200_fused_t *f,
+                                    skl_b200_dtype_t tc, void *c, size_t rsc, size_t csc);
+
 /* ------------------------------------------------------------------ GEMM without device allocation
  * No counterpart in the reference: SKL's kernels never allocate because they never need scratch
  * memory, whereas the bf16 x fp8 case above widens B into a workspace obtained with cudaMalloc.

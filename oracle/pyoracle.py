@@ -82,6 +82,8 @@ def port():
             [_SZ] * 4 + [_F, _VP] + [_SZ] * 4
         lib.orc_gemm_ex.argtypes = [_SZ, _SZ, _SZ, _I, _VP, _SZ, _SZ, _I, _VP, _SZ, _SZ, _F, _VP, _VP,
                                     _F, _I, _VP, _SZ, _SZ]
+        lib.orc_gemm_fused.argtypes = [_SZ, _SZ, _SZ, _I, _VP, _SZ, _SZ, _I, _VP, _SZ, _SZ, _F, _VP, _VP, _VP, _VP,
+                                       _F, _I, _VP, _SZ, _SZ]
         lib.orc_pack.argtypes = [_SZ, _SZ, _SZ, _VP, _SZ, _SZ, _SZ, _SZ, _VP, _SZ, _SZ, _SZ, _SZ,
                                  C.c_uint32]
         lib.orc_unpack.argtypes = [_SZ, _SZ, _SZ, _VP, _SZ, _SZ, _SZ, _SZ, _SZ, _SZ, _VP, _SZ, _SZ]
@@ -164,6 +166,12 @@ def port_gemm_ex(m, n, k, ta, a, rsa, csa, tb, b, rsb, csb, alpha, row_scale, co
                  rsc, csc) -> None:
     port().orc_gemm_ex(m, n, k, ta, _p(a), rsa, csa, tb, _p(b), rsb, csb, float(alpha), _p(row_scale),
                        _p(col_scale), float(beta), tc, _p(c), rsc, csc)
+
+
+def port_gemm_fused(m, n, k, ta, a, rsa, csa, tb, b, rsb, csb, alpha, row_scale, col_scale, bias, global_max, beta,
+                    tc, c, rsc, csc) -> None:
+    port().orc_gemm_fused(m, n, k, ta, _p(a), rsa, csa, tb, _p(b), rsb, csb, float(alpha), _p(row_scale),
+                          _p(col_scale), _p(bias), _p(global_max), float(beta), tc, _p(c), rsc, csc)
 
 
 _ESIZE = {I8: 1, BF16: 2, F16: 2, F8E4M3: 1, F8E5M2: 1, F32: 4, I32: 4}

@@ -356,9 +356,10 @@ static inline void store_c(int tc, void *c, size_t idx, float v) {
   }
 }
 
-void orc_gemm_ex(size_t m, size_t n, size_t k, int ta, const void *a, size_t rsa, size_t csa, int tb,
-                 const void *b, size_t rsb, size_t csb, float alpha, const float *row_scale,
-                 const float *col_scale, float beta, int tc, void *c, size_t rsc, size_t csc) {
+void orc_gemm_fused(size_t m, size_t n, size_t k, int ta, const void *a, size_t rsa, size_t csa, int tb,
+                    const void *b, size_t rsb, size_t csb, float alpha, const float *row_scale,
+                    const float *col_scale, const float *bias, float *global_max, float beta, int tc, void *c,
+                    size_t rsc, size_t csc) {
   for (size_t i = 0; i < m; ++i) {
     for (size_t j = 0; j < n; ++j) {
       float v;
@@ -385,14 +386,26 @@ void orc_gemm_ex(size_t m, size_t n, size_t k, int ta, const void *a, size_t rsa
       if (col_scale) {
         v = v * col_scale[j];
       }
+      if (bias) {
+        v = v + bias[j];
+      }
       size_t idx = i * rsc + j * csc;
       if (beta != 0.0f) {
         float left = beta * load_c(tc, c, idx);
         v = left + v;
       }
+      if (global_max && v > *global_max) { /* false for NaN, as in the reference's example kernel */
+        *global_max = v;
+      }
       store_c(tc, c, idx, v);
     }
   }
+}
+
+void orc_gemm_ex(size_t m, size_t n, size_t k, int ta, const void *a, size_t rsa, size_t csa, int tb,
+                 const void *b, size_t rsb, size_t csb, float alpha, const float *row_scale,
+                 const float *col_scale, float beta, int tc, void *c, size_t rsc, size_t csc) {
+  orc_gemm_fused(m, n, k, ta, a, rsa, csa, tb, b, rsb, csb, alpha, row_scale, col_scale, 0, 0, beta, tc, c, rsc, csc);
 }
 
 /* ------------------------------------------------------------------ pack / unpack / transpose */

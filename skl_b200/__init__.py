@@ -66,6 +66,7 @@ SIGNATURES = {
     "skl_gemm_f8e5m2rcprc_f8e5m2rcprc_f32rcprc_sm100a": (_GEMM_P_F, None),
     "skl_gemm_ex_sm100a": ([_SZ, _SZ, _SZ, _I, _VP, _SZ, _SZ, _I, _VP, _SZ, _SZ, _F, _VP, _VP, _F, _I,
                             _VP, _SZ, _SZ], None),
+    "skl_gemm_fused_sm100a": ([_SZ, _SZ, _SZ, _I, _VP, _SZ, _SZ, _I, _VP, _SZ, _SZ, _VP, _I, _VP, _SZ, _SZ], None),
     "skl_gemm_bf16_f8e4m3_bf16_noalloc_sm100a": ([_SZ, _SZ, _SZ, _F, _VP, _SZ, _SZ, _VP, _SZ, _SZ, _VP, _VP, _SZ,
                                                   _SZ, _VP, C.c_char_p, _SZ], _I),
     "skl_cvt_f32_f8e4m3_sm100a": ([_VP, _VP, _F, _SZ], None),
@@ -126,6 +127,12 @@ def ptr(x) -> int:
     if hasattr(x, "ctypes"):
         return x.ctypes.data
     return int(x)
+
+
+class Fused(C.Structure):
+    """skl_b200_fused_t"""
+    _fields_ = [("alpha", C.c_float), ("beta", C.c_float), ("row_scale", C.c_void_p), ("col_scale", C.c_void_p),
+                ("bias", C.c_void_p), ("global_max", C.c_void_p)]
 
 
 class SklB200Error(RuntimeError):

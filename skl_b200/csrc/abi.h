@@ -53,6 +53,10 @@ typedef struct skl_b200_gemm_args {
   const float *col_scale;  /* n entries or NULL (SKL_EPI_FLOAT) */
   int32_t col_scale_first; /* 0: v*row_scale then *col_scale (the defined order); 1: the reverse, used
                               when a problem is handed over transposed so the two vectors swap roles */
+  const float *bias;       /* NULL, or a vector added after the scales (SKL_EPI_FLOAT): n entries indexed by
+                              column, or m entries indexed by row when bias_per_row is set (transposed hand-over) */
+  int32_t bias_per_row;
+  float *global_max;       /* NULL, or one device float raised to the largest result value (NaN ignored) */
 } skl_b200_gemm_args;
 
 /* Device status word written by kernels whose bounded waits expire: 0 = ok, else a stage code. */

@@ -123,6 +123,7 @@ __global__ void __launch_bounds__(256) gemm_generic_kernel(const GenericParams p
     __syncthreads();
   }
 
+  float local_max = -INFINITY;
 #pragma unroll
   for (int r = 0; r < 4; ++r) {
     int64_t i = row0 + ty + 16 * r;
@@ -139,10 +140,16 @@ __global__ void __launch_bounds__(256) gemm_generic_kernel(const GenericParams p
         *cp = (int32_t)(old + prod);
       } else {
         float v = epilogue_value((float)acc[r][c], g.alpha_f, g.row_scale, g.col_scale, i, j);
+        if (g.bias) v = __fadd_rn(v, g.bias[g.bias_per_row ? i : j]);
         if (g.beta_f != 0.0f) v = __fadd_rn(__fmul_rn(g.beta_f, load_c_f32(g.tc, g.c, o)), v);
+        if (v == v) local_max = fmaxf(local_max, v);
         store_c_f32(g.tc, g.c, o, v);
       }
     }
+  }
+  if (g.epilogue == SKL_EPI_FLOAT && g.global_max) {
+    local_max = warp_max_f32(local_max);
+    if ((tid & 31) == 0 && local_max != -INFINITY) atomic_max_f32(g.global_max, local_max);
   }
 }
 

@@ -61,6 +61,9 @@ struct TcParams {
   float alpha_f, beta_f;
   const float *row_scale, *col_scale;
   int col_scale_first;
+  const float *bias;
+  int bias_per_row;
+  float *global_max;
   uint32_t *status;
 };
 
@@ -307,9 +310,10 @@ struct TcConfig {
 };
 
 // ------------------------------------------------------------------ epilogue for 32 accumulator columns
+// Returns the largest value written (for the optional global maximum); -INFINITY for the int epilogue.
 template <bool ACC_INT>
-__device__ __forceinline__ void epilogue_chunk(const TcParams &p, const uint32_t (&r)[32], int row,
-                                               int col0) {
+__device__ __forceinline__ float epilogue_chunk(const TcParams &p, const uint32_t (&r)[32], int row,
+                                                int col0) {
   const int ncols = (p.N - col0) < 32 ? (p.N - col0) : 32;
   if (p.epilogue == SKL_EPI_INT) {
     int32_t *crow = (int32_t *)p.c + (int64_t)row * p.rsc + (int64_t)col0 * p.csc;
@@ -336,7 +340,7 @@ __device__ __forceinline__ void epilogue_chunk(const TcParams &p, const uint32_t
         }
       }
     }
-    return;
+    return -INFINITY;
   }
   // float epilogue
   float v[32];
@@ -348,6 +352,7 @@ __device__ __forceinline__ void epilogue_chunk(const TcParams &p, const uint32_t
     if (p.row_scale && !p.col_scale_first) x = __fmul_rn(x, rs);
     if (p.col_scale && e < ncols) x = __fmul_rn(x, __ldg(p.col_scale + col0 + e));
     if (p.row_scale && p.col_scale_first) x = __fmul_rn(x, rs);
+    if (p.bias && e < ncols) x = __fadd_rn(x, p.bias_per_row ? __ldg(p.bias + row) : __ldg(p.bias + col0 + e));
     v[e] = x;
   }
   const int64_t base = (int64_t)row * p.rsc + (int64_t)col0 * p.csc;
@@ -356,6 +361,12 @@ __device__ __forceinline__ void epilogue_chunk(const TcParams &p, const uint32_t
     for (int e = 0; e < 32; ++e)
       if (e < ncols)
         v[e] = __fadd_rn(__fmul_rn(p.beta_f, load_c_f32(p.tc, p.c, base + (int64_t)e * p.csc)), v[e]);
+  }
+  float vmax = -INFINITY;
+  if (p.global_max) {
+#pragma unroll
+    for (int e = 0; e < 32; ++e)
+      if (e < ncols && v[e] == v[e]) vmax = fmaxf(vmax, v[e]);
   }
   if (p.c_vec_ok && ncols == 32) {
     if (p.tc == SKL_DT_F32) {
@@ -389,6 +400,7 @@ __device__ __forceinline__ void epilogue_chunk(const TcParams &p, const uint32_t
     for (int e = 0; e < 32; ++e)
       if (e < ncols) store_c_f32(p.tc, p.c, base + (int64_t)e * p.csc, v[e]);
   }
+  return vmax;
 }
 
 // ------------------------------------------------------------------ the kernel
@@ -527,6 +539,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
     // ---------------------------------------------------------------- epilogue warps
     const int quad = warp & 3;
     uint32_t acc = 0, acc_phase = 0;
+    float tile_max = -INFINITY;  // running maximum of this thread's results (optional global maximum)
     TileUnit u;
     for (int it = 0; get_unit<BN>(p, it, u); ++it) {
       const int m0 = u.m0, n0 = u.n0;
@@ -542,12 +555,16 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
           tmem_ld32(taddr + c0, r);
         else
           tmem_ld16(taddr + c0, r);
-        if (row < p.M) epilogue_chunk<KIND == KIND_I8>(p, r, row, n0 + c0);
+        if (row < p.M) tile_max = fmaxf(tile_max, epilogue_chunk<KIND == KIND_I8>(p, r, row, n0 + c0));
       }
       tc_fence_before();
       mbar_arrive(tempty_bar + 8 * acc);
       acc ^= 1u;
       if (acc == 0) acc_phase ^= 1u;
+    }
+    if (p.global_max) {
+      tile_max = warp_max_f32(tile_max);
+      if (lane == 0 && tile_max != -INFINITY) atomic_max_f32(p.global_max, tile_max);
     }
   }
 
@@ -726,6 +743,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
     // ---------------------------------------------------------------- epilogue warps (both CTAs)
     const int quad = warp & 3;
     uint32_t acc = 0, acc_phase = 0;
+    float tile_max = -INFINITY;
     const uint32_t leader_tempty = mapa(tempty_bar, 0);
     for (int t = pair; t < num_tiles; t += num_pairs) {
       int mi, ni;
@@ -740,12 +758,16 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         if (n0 + c0 >= p.N) break;
         uint32_t r[32];
         tmem_ld32(taddr + c0, r);
-        if (row < p.M) epilogue_chunk<KIND == KIND_I8>(p, r, row, n0 + c0);
+        if (row < p.M) tile_max = fmaxf(tile_max, epilogue_chunk<KIND == KIND_I8>(p, r, row, n0 + c0));
       }
       tc_fence_before();
       mbar_arrive_cluster(leader_tempty + 8 * acc);
       acc ^= 1u;
       if (acc == 0) acc_phase ^= 1u;
+    }
+    if (p.global_max) {
+      tile_max = warp_max_f32(tile_max);
+      if (lane == 0 && tile_max != -INFINITY) atomic_max_f32(p.global_max, tile_max);
     }
   }
 
@@ -851,12 +873,16 @@ uint32_t fmt_code(int kind, int dt) {
   return dt == SKL_DT_F8E5M2 ? 1u : 0u;
 }
 
+int current_device() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) (void)cudaGetLastError();
+  return (dev < 0 || dev >= 64) ? 0 : dev;
+}
+
 int sm_count() {
   static int sms = 0;
   if (sms == 0) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, current_device());
     if (sms <= 0) sms = 148;
   }
   return sms;
@@ -889,12 +915,13 @@ int pick_bn(int64_t M, int64_t N, int kind, bool b_mn_major) {
 template <int BN, int KIND>
 int launch_cfg(const CUtensorMap &ta, const CUtensorMap &tb, const TcParams &p, cudaStream_t s) {
   using Cfg = TcConfig<BN>;
-  static bool attr_set = false;
-  if (!attr_set) {
+  static bool attr_set[64] = {};  // per device: function attributes do not carry over between devices
+  const int dev = current_device();
+  if (!attr_set[dev]) {
     cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, KIND>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          Cfg::SMEM_BYTES);
     if (e != cudaSuccess) return (int)e;
-    attr_set = true;
+    attr_set[dev] = true;
   }
   int grid = p.tiles_m * p.tiles_n;
   if (grid > sm_count()) grid = sm_count();
@@ -906,8 +933,13 @@ int launch_cfg(const CUtensorMap &ta, const CUtensorMap &tb, const TcParams &p, 
 template <int BN, int KIND>
 int launch_cfg2(const CUtensorMap &ta, const CUtensorMap &tb, const TcParams &p, cudaStream_t s) {
   using Cfg = Tc2Config<BN>;
-  static int max_pairs = -1;
-  if (max_pairs < 0) {
+  static int max_pairs_dev[64];
+  static bool pairs_known[64] = {};
+  const int dev = current_device();
+  int &max_pairs = max_pairs_dev[dev];
+  if (!pairs_known[dev]) {
+    pairs_known[dev] = true;
+    max_pairs = -1;
     cudaError_t e = cudaFuncSetAttribute(gemm_tc2_kernel<BN, KIND>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          Cfg::SMEM_BYTES);
     if (e != cudaSuccess) return (int)e;
@@ -1074,6 +1106,9 @@ extern "C" int skl_b200_launch_gemm_tc(const skl_b200_gemm_args *g, uint32_t *de
   p.row_scale = g->row_scale;
   p.col_scale = g->col_scale;
   p.col_scale_first = g->col_scale_first;
+  p.bias = g->bias;
+  p.bias_per_row = g->bias_per_row;
+  p.global_max = g->global_max;
   p.status = dev_status;
   cudaStream_t s = (cudaStream_t)stream;
 

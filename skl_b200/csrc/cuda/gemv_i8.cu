@@ -37,7 +37,8 @@ struct GemvParams {
   int epilogue, tc;
   int32_t alpha_i, beta_i;
   float alpha_f, beta_f;
-  const float *row_scale, *col_scale;
+  const float *row_scale, *col_scale, *bias;
+  float *global_max;
   uint32_t *status;
 };
 
@@ -110,19 +111,23 @@ __device__ __forceinline__ void warp_fold(int32_t (&v)[V], int lane) {
 
 // rs / cs: the row and column scale of this element, fetched ahead of time (1.0f when absent; the
 // multiplication is skipped then, so the result is the same as without a scale vector).
-__device__ __forceinline__ void gemv_store(const GemvParams &p, int mi, int j, int32_t a, float rs, float cs) {
+// Returns the stored value (float epilogue) for the optional global maximum, else -INFINITY.
+__device__ __forceinline__ float gemv_store(const GemvParams &p, int mi, int j, int32_t a, float rs, float cs,
+                                            float bias) {
   const int64_t o = (int64_t)mi * p.rsc + (int64_t)j * p.csc;
   if (p.epilogue == SKL_EPI_INT) {
     int32_t *cp = (int32_t *)p.c + o;
     uint32_t old = p.beta_i != 0 ? (uint32_t)p.beta_i * (uint32_t)*cp : 0u;
     *cp = (int32_t)(old + (uint32_t)p.alpha_i * (uint32_t)a);
-  } else {
-    float v = __fmul_rn(p.alpha_f, (float)a);
-    if (p.row_scale) v = __fmul_rn(v, rs);
-    if (p.col_scale) v = __fmul_rn(v, cs);
-    if (p.beta_f != 0.0f) v = __fadd_rn(__fmul_rn(p.beta_f, load_c_f32(p.tc, p.c, o)), v);
-    store_c_f32(p.tc, p.c, o, v);
+    return -INFINITY;
   }
+  float v = __fmul_rn(p.alpha_f, (float)a);
+  if (p.row_scale) v = __fmul_rn(v, rs);
+  if (p.col_scale) v = __fmul_rn(v, cs);
+  if (p.bias) v = __fadd_rn(v, bias);
+  if (p.beta_f != 0.0f) v = __fadd_rn(__fmul_rn(p.beta_f, load_c_f32(p.tc, p.c, o)), v);
+  store_c_f32(p.tc, p.c, o, v);
+  return (v == v) ? v : -INFINITY;
 }
 
 template <int MP>
@@ -191,6 +196,7 @@ __global__ void __launch_bounds__(GV_THREADS, 1) gemv_i8_kernel(const GemvParams
   int q0 = 0, c_slot = 0;
   uint32_t c_par = 0;  // parity of the ring pass the consumer is in
   bool ok = true;
+  float warp_max = -INFINITY;  // this lane's largest result so far (optional global maximum)
   for (int g = 0; ok && q0 < n_items; ++g) {
     const int rc = g < full_groups ? GV_R : tail_rows;  // rows in this group
     const int row0 = row_begin + g * GV_R;
@@ -202,13 +208,14 @@ __global__ void __launch_bounds__(GV_THREADS, 1) gemv_i8_kernel(const GemvParams
     constexpr int W = V >= 32 ? V / 32 : 1;
     constexpr int LOGV = V >= 32 ? 5 : (V == 16 ? 4 : (V == 8 ? 3 : 2));
     const int share = 5 - LOGV;  // 2^share lanes hold the same finished value
-    float rs_pre[W], cs_pre[W];
+    float rs_pre[W], cs_pre[W], bias_pre[W];
 #pragma unroll
     for (int w = 0; w < W; ++w) {
       const int idx = (lane >> share) * W + w;  // = r*MP + mi
       const int r = idx / MP, mi = idx - r * MP;
       rs_pre[w] = (p.row_scale && mi < p.m) ? __ldg(p.row_scale + mi) : 1.0f;
       cs_pre[w] = (p.col_scale && r < rc) ? __ldg(p.col_scale + row0 + r) : 1.0f;
+      bias_pre[w] = (p.bias && r < rc) ? __ldg(p.bias + row0 + r) : 0.0f;
     }
 
     for (int seg = 0; seg < NSEG && ok; ++seg) {
@@ -273,9 +280,14 @@ __global__ void __launch_bounds__(GV_THREADS, 1) gemv_i8_kernel(const GemvParams
       for (int w = 0; w < W; ++w) {
         const int idx = (lane >> share) * W + w;  // = r*MP + mi
         const int r = idx / MP, mi = idx - r * MP;
-        if (r < rc && mi < p.m) gemv_store(p, mi, row0 + r, acc[w], rs_pre[w], cs_pre[w]);
+        if (r < rc && mi < p.m)
+          warp_max = fmaxf(warp_max, gemv_store(p, mi, row0 + r, acc[w], rs_pre[w], cs_pre[w], bias_pre[w]));
       }
     }
+  }
+  if (p.global_max) {
+    warp_max = warp_max_f32(warp_max);
+    if (lane == 0 && warp_max != -INFINITY) atomic_max_f32(p.global_max, warp_max);
   }
 }
 
@@ -336,6 +348,8 @@ extern "C" int skl_b200_launch_gemv_i8(const skl_b200_gemm_args *g, uint32_t *de
   p.beta_f = g->beta_f;
   p.row_scale = g->row_scale;
   p.col_scale = g->col_scale;
+  p.bias = g->bias;
+  p.global_max = g->global_max;
   p.status = dev_status;
   int mp = 1;
   while (mp < p.m) mp <<= 1;
@@ -362,11 +376,13 @@ extern "C" int skl_b200_launch_gemv_i8(const skl_b200_gemm_args *g, uint32_t *de
   cudaError_t e = cudaSuccess;
 #define GV_LAUNCH(MPV)                                                                             \
   do {                                                                                             \
-    static bool attr_set = false;                                                                  \
-    if (!attr_set) {                                                                               \
+    static bool attr_set[64] = {}; /* per device */                                                \
+    int dev = 0;                                                                                   \
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = 0;                       \
+    if (!attr_set[dev]) {                                                                          \
       e = cudaFuncSetAttribute(gemv_i8_kernel<MPV>, cudaFuncAttributeMaxDynamicSharedMemorySize,   \
                                (int)GV_SMEM_BUDGET);                                               \
-      attr_set = (e == cudaSuccess);                                                               \
+      attr_set[dev] = (e == cudaSuccess);                                                          \
     }                                                                                              \
     if (e == cudaSuccess) gemv_i8_kernel<MPV><<<grid, GV_THREADS, smem, s>>>(p);                   \
   } while (0)

@@ -235,4 +235,21 @@ __device__ __forceinline__ float epilogue_value(float acc, float alpha, const fl
   return v;
 }
 
+// *addr = max(*addr, v) for floats (NaN never wins): the IEEE ordering of non-negative floats equals the
+// ordering of their bit patterns as signed integers, that of negative floats the reverse as unsigned.
+__device__ __forceinline__ void atomic_max_f32(float *addr, float v) {
+  if (!(v == v)) return;
+  if (v >= 0.0f)
+    atomicMax(reinterpret_cast<int *>(addr), __float_as_int(v));
+  else
+    atomicMin(reinterpret_cast<unsigned int *>(addr), __float_as_uint(v));
+}
+
+// Largest value across the warp (lanes without a value pass -INFINITY); every lane gets the result.
+__device__ __forceinline__ float warp_max_f32(float v) {
+#pragma unroll
+  for (int off = 16; off >= 1; off >>= 1) v = fmaxf(v, __shfl_xor_sync(0xFFFFFFFFu, v, off));
+  return v;
+}
+
 }  // namespace sklb

@@ -19,7 +19,7 @@
 
 /* ------------------------------------------------------------------ per-thread context */
 
-enum { WS_A = 0, WS_B, WS_C, WS_ROW, WS_COL, WS_WIDEN, WS_COUNT };
+enum { WS_A = 0, WS_B, WS_C, WS_ROW, WS_COL, WS_WIDEN, WS_BIAS, WS_GMAX, WS_COUNT };
 
 #define PIPE_MAX_CHUNKS 16
 
@@ -401,6 +401,7 @@ static int dispatch_launch(const skl_b200_gemm_args *gin) {
     swapped.rsc0 = g->csc0; swapped.csc0 = g->rsc0;
     swapped.row_scale = g->col_scale; swapped.col_scale = g->row_scale;
     swapped.col_scale_first = 1; /* keep (acc * row_scale[m]) * col_scale[n] */
+    swapped.bias_per_row = 1;    /* the bias is indexed by the original column = the transposed row */
     if (skl_b200_gemm_tc_supported(&swapped)) {
       g = &swapped;
       path = SKL_B200_PATH_TCGEN05;
@@ -560,7 +561,22 @@ static void run_gemm(skl_b200_gemm_args *g) {
     if (!g->col_scale) return;
   }
 
+  if (g->bias && !on_device(g->bias)) {
+    host_any = 1;
+    g->bias = (const float *)stage_in(WS_BIAS, g->bias, (size_t)N * sizeof(float));
+    if (!g->bias) return;
+  }
+  float *host_gmax = 0;
+  if (g->global_max && !on_device(g->global_max)) {
+    host_any = 1;
+    host_gmax = g->global_max;
+    g->global_max = (float *)stage_in(WS_GMAX, host_gmax, sizeof(float));
+    if (!g->global_max) return;
+  }
+
   if (run_gemm_pipelined(g, a_host, c_host, &host_any)) {
+    if (host_gmax && g_ctx.status == SKL_B200_OK)
+      cuda_ok(cudaMemcpyAsync(host_gmax, g->global_max, sizeof(float), cudaMemcpyDeviceToHost, (cudaStream_t)g_ctx.stream));
     finish(host_any);
     end_call();
     return;
@@ -600,6 +616,9 @@ static void run_gemm(skl_b200_gemm_args *g) {
   if (!dispatch_launch(g)) return;
 
   if (c_host && !stage_out_end(&out)) return;
+  if (host_gmax &&
+      !cuda_ok(cudaMemcpyAsync(host_gmax, g->global_max, sizeof(float), cudaMemcpyDeviceToHost, (cudaStream_t)g_ctx.stream)))
+    return;
   finish(host_any);
   end_call();
 }
@@ -607,7 +626,8 @@ static void run_gemm(skl_b200_gemm_args *g) {
 static void gemm_plain(int ta, int tb, int tc, int epi, size_t m, size_t n, size_t k, const void *a,
                        size_t rsa, size_t csa, const void *b, size_t rsb, size_t csb, void *c,
                        size_t rsc, size_t csc, int32_t alpha_i, int32_t beta_i, float alpha_f,
-                       float beta_f, const float *row_scale, const float *col_scale) {
+                       float beta_f, const float *row_scale, const float *col_scale, const float *bias,
+                       float *global_max) {
   skl_b200_gemm_args g;
   memset(&g, 0, sizeof g);
   g.m0 = m; g.n0 = n; g.k0 = k;
@@ -621,6 +641,7 @@ static void gemm_plain(int ta, int tb, int tc, int epi, size_t m, size_t n, size
   g.alpha_i = alpha_i; g.beta_i = beta_i;
   g.alpha_f = alpha_f; g.beta_f = beta_f;
   g.row_scale = row_scale; g.col_scale = col_scale;
+  g.bias = bias; g.global_max = global_max;
   run_gemm(&g);
 }
 
@@ -651,14 +672,14 @@ void skl_gemm_i8rc_i8rc_i32rc_sm100a(size_t m, size_t n, size_t k, int32_t alpha
                                      size_t rsa, size_t csa, const int8_t *b, size_t rsb, size_t csb,
                                      int32_t beta, int32_t *c, size_t rsc, size_t csc) {
   gemm_plain(SKL_DT_I8, SKL_DT_I8, SKL_DT_I32, SKL_EPI_INT, m, n, k, a, rsa, csa, b, rsb, csb, c, rsc, csc,
-             alpha, beta, 0.0f, 0.0f, 0, 0);
+             alpha, beta, 0.0f, 0.0f, 0, 0, 0, 0);
 }
 
 #define SKL_B200_DEF_GEMM_RC_F32(NAME, TYPE, DT)                                                      \
   void NAME(size_t m, size_t n, size_t k, float alpha, const TYPE *a, size_t rsa, size_t csa,         \
             const TYPE *b, size_t rsb, size_t csb, float beta, float *c, size_t rsc, size_t csc) {    \
     gemm_plain(DT, DT, SKL_DT_F32, SKL_EPI_FLOAT, m, n, k, a, rsa, csa, b, rsb, csb, c, rsc, csc, 0, 0, \
-               alpha, beta, 0, 0);                                                                    \
+               alpha, beta, 0, 0, 0, 0);                                                              \
   }
 SKL_B200_DEF_GEMM_RC_F32(skl_gemm_bf16rc_bf16rc_f32rc_sm100a, skl_bf16_t, SKL_DT_BF16)
 SKL_B200_DEF_GEMM_RC_F32(skl_gemm_f16rc_f16rc_f32rc_sm100a, skl_f16_t, SKL_DT_F16)
@@ -722,10 +743,14 @@ SKL_B200_DEF_GEMM_PACKED_F32(skl_gemm_f8e5m2rcprc_f8e5m2rcprc_f32rcprc_sm100a, u
 /* extended epilogue */
 static int is_f8(int t) { return t == SKL_DT_F8E4M3 || t == SKL_DT_F8E5M2; }
 
-void skl_gemm_ex_sm100a(size_t m, size_t n, size_t k, skl_b200_dtype_t ta, const void *a, size_t rsa,
-                        size_t csa, skl_b200_dtype_t tb, const void *b, size_t rsb, size_t csb,
-                        float alpha, const float *row_scale, const float *col_scale, float beta,
-                        skl_b200_dtype_t tc, void *c, size_t rsc, size_t csc) {
+void skl_gemm_fused_sm100a(size_t m, size_t n, size_t k, skl_b200_dtype_t ta, const void *a, size_t rsa,
+                           size_t csa, skl_b200_dtype_t tb, const void *b, size_t rsb, size_t csb,
+                           const skl_b200_fused_t *f, skl_b200_dtype_t tc, void *c, size_t rsc, size_t csc) {
+  if (!f) {
+    g_ctx.status = SKL_B200_ERR_INVALID_ARGUMENT;
+    g_ctx.cuda_err[0] = 0;
+    return;
+  }
   int pair_ok = (ta == SKL_B200_I8 && tb == SKL_B200_I8) || (is_f8(ta) && is_f8(tb)) ||
                 (ta == SKL_B200_BF16 && tb == SKL_B200_BF16) || (ta == SKL_B200_F16 && tb == SKL_B200_F16) ||
                 (ta == SKL_B200_BF16 && is_f8(tb));
@@ -736,7 +761,21 @@ void skl_gemm_ex_sm100a(size_t m, size_t n, size_t k, skl_b200_dtype_t ta, const
     return;
   }
   gemm_plain((int)ta, (int)tb, (int)tc, SKL_EPI_FLOAT, m, n, k, a, rsa, csa, b, rsb, csb, c, rsc, csc, 0, 0,
-             alpha, beta, row_scale, col_scale);
+             f->alpha, f->beta, f->row_scale, f->col_scale, f->bias, f->global_max);
+}
+
+void skl_gemm_ex_sm100a(size_t m, size_t n, size_t k, skl_b200_dtype_t ta, const void *a, size_t rsa,
+                        size_t csa, skl_b200_dtype_t tb, const void *b, size_t rsb, size_t csb,
+                        float alpha, const float *row_scale, const float *col_scale, float beta,
+                        skl_b200_dtype_t tc, void *c, size_t rsc, size_t csc) {
+  skl_b200_fused_t f;
+  f.alpha = alpha;
+  f.beta = beta;
+  f.row_scale = row_scale;
+  f.col_scale = col_scale;
+  f.bias = 0;
+  f.global_max = 0;
+  skl_gemm_fused_sm100a(m, n, k, ta, a, rsa, csa, tb, b, rsb, csb, &f, tc, c, rsc, csc);
 }
 
 /* ------------------------------------------------------------------ cvt */
