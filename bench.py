@@ -293,14 +293,18 @@ def make_workloads(torch, S, lib):
             lib.skl_cvt_f8e4m3_bf16_sm100a(dst.data_ptr(), src.data_ptr(), n)
         return call, 3.0 * n, "gbs", 10
 
-    def transpose_e8():
-        m = n = 16384
-        a = torch.randint(0, 256, (m, n), dtype=torch.uint8, device=dev, generator=g)
-        at = torch.empty((n, m), dtype=torch.uint8, device=dev)
+    def transpose(e, m):
+        def make():
+            n = m
+            dt = {8: torch.uint8, 16: torch.int16, 32: torch.int32}[e]
+            a = torch.randint(0, 127, (m, n), dtype=dt, device=dev, generator=g)
+            at = torch.empty((n, m), dtype=dt, device=dev)
+            fn = getattr(lib, f"skl_transpose_e{e}_sm100a")
 
-        def call():
-            lib.skl_transpose_e8_sm100a(m, n, a.data_ptr(), n, at.data_ptr(), m)
-        return call, 2.0 * m * n, "gbs", 10
+            def call():
+                fn(m, n, a.data_ptr(), n, at.data_ptr(), m)
+            return call, 2.0 * m * n * (e // 8), "gbs", 10
+        return make
 
     def pack_e16():
         m, n, m0, n0 = 16384, 8192, 128, 64  # row-major bf16 matrix into 128 x 64 row-major blocks
@@ -325,7 +329,11 @@ def make_workloads(torch, S, lib):
         W[f"gemv_i8_m16_n{rows}"] = gemv(16, rows)
     W["cvt_sat_f32_f8e4m3_128M"] = cvt_f32_e4m3
     W["cvt_f8e4m3_bf16_256M"] = cvt_e4m3_bf16
-    W["transpose_e8_16384"] = transpose_e8
+    W["transpose_e8_16384"] = transpose(8, 16384)
+    W["transpose_e16_16384"] = transpose(16, 16384)
+    W["transpose_e32_8192"] = transpose(32, 8192)
+    W["transpose_e16_8192"] = transpose(16, 8192)
+    W["transpose_e32_16384"] = transpose(32, 16384)
     W["pack_e16_16384x8192"] = pack_e16
     return W
 

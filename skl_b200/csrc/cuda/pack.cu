@@ -145,51 +145,78 @@ __global__ void __launch_bounds__(256) copy_groups_kernel(const T *__restrict__ 
   }
 }
 
-// ---- fast path 2: plain 2-D transpose (source unit stride along j, destination along i) of 8-bit
-// elements.  Each thread owns a 4 x 4 byte micro-tile: four 4-byte loads (a warp reads 2 rows x 64
-// bytes per load), an in-register 4 x 4 byte transpose with byte permutes, four 4-byte stores into a
-// transposed shared-memory tile, then every thread writes one 16-byte run of a destination row.
-__global__ void __launch_bounds__(256) transpose8_kernel(const uint8_t *__restrict__ src, uint8_t *__restrict__ dst,
-                                                         const RelayoutParams p) {
-  __shared__ uint32_t tileT[RT][RT / 4 + 1];  // [j][i / 4], one pad word per row
-  const uint32_t num_tiles = p.tiles_i * p.tiles_j;
-  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+// ---- fast path 2: plain 2-D transpose (source unit stride along j, destination along i).
+// Each thread owns V x V micro-tiles with V = 4 / sizeof(T) (4 x 4 bytes, 2 x 2 halfwords, 1 word):
+// V loads of 4 bytes along the source rows, an in-register V x V transpose with byte permutes, V
+// stores of 4 bytes into a transposed shared-memory tile; then every thread writes 16-byte runs of the
+// destination rows.  Both global sides move whole 32-byte sectors.  The tile is TD x TD elements
+// (16 KB for bytes and words, 32 KB for halfwords) so that a resident CTA keeps enough bytes in flight
+// to cover the memory latency; a warp covers (32 / V) x V micro-tiles on the way in and 4 rows x 8 runs
+// on the way out, which with the odd row pitch touches 32 distinct banks both times.
+template <typename T, int TD>
+__global__ void __launch_bounds__(256) transpose_fast_kernel(const T *__restrict__ src, T *__restrict__ dst,
+                                                             const RelayoutParams p) {
+  constexpr int V = 4 / sizeof(T);
+  constexpr int WPR = TD / V;                  // 4-byte words per tile row
+  constexpr int PITCHW = WPR + 1;              // odd pitch in words
+  constexpr int TXW = 32 / V, TYW = V;         // micro-tiles one warp covers along j and along i
+  constexpr int WX = WPR / TXW;                // warp steps across a tile
+  constexpr int RUNS = TD * (int)sizeof(T) / 16;  // 16-byte runs per destination row
+  __shared__ uint32_t tileT[TD * PITCHW];      // [j][i / V]
+  const uint32_t tiles_i = (p.m + TD - 1) / TD, tiles_j = (p.n + TD - 1) / TD;
+  const uint32_t num_tiles = tiles_i * tiles_j;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   for (uint32_t t = blockIdx.x; t < num_tiles; t += gridDim.x) {
-    const uint32_t i0 = (t / p.tiles_j) * RT, j0 = (t % p.tiles_j) * RT;
-    const bool full = i0 + RT <= p.m && j0 + RT <= p.n;
+    const uint32_t i0 = (t / tiles_j) * TD, j0 = (t % tiles_j) * TD;
+    const bool full = i0 + TD <= p.m && j0 + TD <= p.n;
     if (full) {
-      uint32_t r[4];
+#pragma unroll 4
+      for (int w = warp; w < WX * (WPR / TYW); w += 8) {
+        const int tx = (w % WX) * TXW + lane % TXW;  // micro-tile column (along j)
+        const int ty = (w / WX) * TYW + lane / TXW;  // micro-tile row (along i)
+        uint32_t r[4];
 #pragma unroll
-      for (int q = 0; q < 4; ++q)
-        r[q] = __ldg(reinterpret_cast<const uint32_t *>(src + (int64_t)(i0 + 4 * ty + q) * p.src.rs0 + j0 + 4 * tx));
-      // r[q] byte b = element (row 4ty+q, col 4tx+b); c[b] byte q = the same element
-      const uint32_t a0 = __byte_perm(r[0], r[1], 0x5140), a1 = __byte_perm(r[0], r[1], 0x7362);
-      const uint32_t b0 = __byte_perm(r[2], r[3], 0x5140), b1 = __byte_perm(r[2], r[3], 0x7362);
-      const uint32_t c0 = __byte_perm(a0, b0, 0x5410), c1 = __byte_perm(a0, b0, 0x7632);
-      const uint32_t c2 = __byte_perm(a1, b1, 0x5410), c3 = __byte_perm(a1, b1, 0x7632);
-      tileT[4 * tx + 0][ty] = c0;
-      tileT[4 * tx + 1][ty] = c1;
-      tileT[4 * tx + 2][ty] = c2;
-      tileT[4 * tx + 3][ty] = c3;
+        for (int q = 0; q < V; ++q)
+          r[q] = __ldg(reinterpret_cast<const uint32_t *>(src + (int64_t)(i0 + V * ty + q) * p.src.rs0 + j0 + V * tx));
+        uint32_t *col = &tileT[(V * tx) * PITCHW + ty];
+        if (V == 4) {
+          // r[q] byte b = element (row q, col b); the word stored for column b holds byte q = the same element
+          const uint32_t a0 = __byte_perm(r[0], r[1], 0x5140), a1 = __byte_perm(r[0], r[1], 0x7362);
+          const uint32_t b0 = __byte_perm(r[2], r[3], 0x5140), b1 = __byte_perm(r[2], r[3], 0x7362);
+          col[0] = __byte_perm(a0, b0, 0x5410);
+          col[(V > 1) * PITCHW] = __byte_perm(a0, b0, 0x7632);
+          col[(V > 2) * 2 * PITCHW] = __byte_perm(a1, b1, 0x5410);
+          col[(V > 2) * 3 * PITCHW] = __byte_perm(a1, b1, 0x7632);
+        } else if (V == 2) {
+          col[0] = __byte_perm(r[0], r[1], 0x5410);  // (row 0, col 0), (row 1, col 0)
+          col[(V > 1) * PITCHW] = __byte_perm(r[0], r[1], 0x7632);
+        } else {
+          col[0] = r[0];
+        }
+      }
       __syncthreads();
-      const int row = threadIdx.x >> 2, quarter = threadIdx.x & 3;  // destination row j, 16-byte run
-      const uint4 v = make_uint4(tileT[row][4 * quarter], tileT[row][4 * quarter + 1], tileT[row][4 * quarter + 2],
-                                 tileT[row][4 * quarter + 3]);
-      *reinterpret_cast<uint4 *>(dst + (int64_t)(j0 + row) * p.dst.cs0 + i0 + 16 * quarter) = v;
+      for (int w = warp; w < (RUNS / 8) * (TD / 4); w += 8) {
+        const int run = (w % (RUNS / 8)) * 8 + lane % 8;
+        const int row = (w / (RUNS / 8)) * 4 + lane / 8;
+        const uint32_t *rp = &tileT[row * PITCHW + 4 * run];
+        const uint4 v = make_uint4(rp[0], rp[1], rp[2], rp[3]);
+        *reinterpret_cast<uint4 *>(reinterpret_cast<uint8_t *>(dst + (int64_t)(j0 + row) * p.dst.cs0 + i0) + 16 * run) = v;
+      }
       __syncthreads();
     } else {
       // ragged edge tile: element by element, still coalesced along each side's unit stride
-      uint8_t *tb = reinterpret_cast<uint8_t *>(&tileT[0][0]);  // viewed as [j][i] bytes, pitch 68
-      for (int e = threadIdx.x; e < RT * RT; e += 256) {
-        const int tj = e & 63, ti = e >> 6;
+      T *tb = reinterpret_cast<T *>(tileT);  // viewed as [j][i] elements
+      constexpr int PITCH = PITCHW * V;
+      for (int e = threadIdx.x; e < TD * TD; e += 256) {
+        const int tj = e % TD, ti = e / TD;
         const uint32_t i = i0 + ti, j = j0 + tj;
-        if (i < p.m && j < p.n) tb[tj * 68 + ti] = src[(int64_t)i * p.src.rs0 + j];
+        if (i < p.m && j < p.n) tb[tj * PITCH + ti] = src[(int64_t)i * p.src.rs0 + j];
       }
       __syncthreads();
-      for (int e = threadIdx.x; e < RT * RT; e += 256) {
-        const int ti = e & 63, tj = e >> 6;
+      for (int e = threadIdx.x; e < TD * TD; e += 256) {
+        const int ti = e % TD, tj = e / TD;
         const uint32_t i = i0 + ti, j = j0 + tj;
-        if (i < p.m && j < p.n) dst[(int64_t)j * p.dst.cs0 + i] = tb[tj * 68 + ti];
+        if (i < p.m && j < p.n) dst[(int64_t)j * p.dst.cs0 + i] = tb[tj * PITCH + ti];
       }
       __syncthreads();
     }
@@ -260,10 +287,38 @@ int launch_relayout(size_t esize, const void *src, void *dst, RelayoutParams p, 
     SKLB_COUNT_LAUNCH();
     return (int)cudaGetLastError();
   }
-  if (esize == 1 && p.src.plain && p.dst.plain && p.src.fast_j && !p.dst.fast_j && p.src.cs0 == 1 && p.dst.rs0 == 1 &&
-      p.MI == p.m && p.NJ == p.n && (reinterpret_cast<uintptr_t>(src) & 3u) == 0 && p.src.rs0 % 4 == 0 &&
-      (reinterpret_cast<uintptr_t>(dst) & 15u) == 0 && p.dst.cs0 % 16 == 0) {
-    transpose8_kernel<<<grid, 256, 0, s>>>((const uint8_t *)src, (uint8_t *)dst, p);
+  const int64_t v4 = 4 / (int64_t)esize, v16 = 16 / (int64_t)esize;
+  if (p.src.plain && p.dst.plain && p.src.fast_j && !p.dst.fast_j && p.src.cs0 == 1 && p.dst.rs0 == 1 &&
+      p.MI == p.m && p.NJ == p.n && (reinterpret_cast<uintptr_t>(src) & 3u) == 0 && p.src.rs0 % v4 == 0 &&
+      (reinterpret_cast<uintptr_t>(dst) & 15u) == 0 && p.dst.cs0 % v16 == 0) {
+    // One wave of resident CTAs: the halfword kernel's 32 KB tile fits fewer than 8 per SM, and CTAs left
+    // for a second wave would run it at a fraction of the occupancy.
+    static int resident[3] = {0, 0, 0};
+    const int which = esize == 1 ? 0 : esize == 2 ? 1 : 2;
+    if (resident[which] == 0) {
+      int per_sm = 0;
+      cudaError_t qe =
+          which == 0   ? cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, transpose_fast_kernel<uint8_t, 128>, 256, 0)
+          : which == 1 ? cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, transpose_fast_kernel<uint16_t, 128>, 256, 0)
+                       : cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, transpose_fast_kernel<uint32_t, 64>, 256, 0);
+      if (qe != cudaSuccess) (void)cudaGetLastError();
+      resident[which] = (qe == cudaSuccess && per_sm > 0) ? (per_sm < 8 ? per_sm : 8) : 4;
+    }
+    const uint64_t td = esize == 4 ? 64 : 128;
+    const uint64_t tiles = ((p.m + td - 1) / td) * ((p.n + td - 1) / td);
+    const uint64_t cap = (uint64_t)relayout_grid(~0ull) / 8 * (uint64_t)resident[which];
+    const int tg = (int)(tiles < cap ? tiles : cap);
+    switch (esize) {
+      case 1:
+        transpose_fast_kernel<uint8_t, 128><<<tg, 256, 0, s>>>((const uint8_t *)src, (uint8_t *)dst, p);
+        break;
+      case 2:
+        transpose_fast_kernel<uint16_t, 128><<<tg, 256, 0, s>>>((const uint16_t *)src, (uint16_t *)dst, p);
+        break;
+      default:
+        transpose_fast_kernel<uint32_t, 64><<<tg, 256, 0, s>>>((const uint32_t *)src, (uint32_t *)dst, p);
+        break;
+    }
     SKLB_COUNT_LAUNCH();
     return (int)cudaGetLastError();
   }
