@@ -298,6 +298,32 @@ __device__ __forceinline__ void umma_commit_pair_both(uint32_t bar) {
                : "memory");
 }
 
+// Per-warp shared-memory copies of the tile's column scales and column bias.  Each epilogue warp fills
+// its own copy before it waits for the accumulator, so the global loads hide behind the main loop and
+// the per-element reads are shared-memory broadcasts; only __syncwarp orders them.  Columns past N (and,
+// for tiles narrower than one 32-column chunk, past the tile) read as 1 and 0.
+template <int BN>
+struct EpiVectors {
+  static constexpr int COLS = BN < 32 ? 32 : BN;
+  static constexpr int BYTES = 4 /*warps*/ * 2 /*scale, bias*/ * COLS * 4;
+  __device__ static __forceinline__ float *scale(uint8_t *base, int quad) {
+    return reinterpret_cast<float *>(base) + quad * 2 * COLS;
+  }
+  __device__ static __forceinline__ float *bias(uint8_t *base, int quad) { return scale(base, quad) + COLS; }
+  __device__ static __forceinline__ void fill(const TcParams &p, float *cs, float *bs, int n0, int ncols, int lane) {
+    const bool col_bias = p.bias && !p.bias_per_row;
+    if (!p.col_scale && !col_bias) return;
+    const int lim = ncols < 32 ? 32 : ncols;
+    __syncwarp();  // this warp's reads of the previous tile's values are done
+    for (int i = lane; i < lim; i += 32) {
+      const bool in = i < ncols && n0 + i < p.N;
+      if (p.col_scale) cs[i] = in ? __ldg(p.col_scale + n0 + i) : 1.0f;
+      if (col_bias) bs[i] = in ? __ldg(p.bias + n0 + i) : 0.0f;
+    }
+    __syncwarp();
+  }
+};
+
 template <int BN>
 struct TcConfig {
   static constexpr int A_BYTES = BM * SLAB_BYTES;
@@ -306,14 +332,14 @@ struct TcConfig {
   static constexpr int STAGES_RAW = (220 * 1024) / STAGE_BYTES;
   static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
   static constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/ + EpiVectors<BN>::BYTES;
 };
 
 // ------------------------------------------------------------------ epilogue for 32 accumulator columns
 // Returns the largest value written (for the optional global maximum); -INFINITY for the int epilogue.
 template <bool ACC_INT>
-__device__ __forceinline__ float epilogue_chunk(const TcParams &p, const uint32_t (&r)[32], int row,
-                                                int col0) {
+__device__ __forceinline__ float epilogue_chunk(const TcParams &p, const uint32_t (&r)[32], int row, int col0,
+                                                const float *cs, const float *bs, float rs, float row_bias) {
   const int ncols = (p.N - col0) < 32 ? (p.N - col0) : 32;
   if (p.epilogue == SKL_EPI_INT) {
     int32_t *crow = (int32_t *)p.c + (int64_t)row * p.rsc + (int64_t)col0 * p.csc;
@@ -343,17 +369,46 @@ __device__ __forceinline__ float epilogue_chunk(const TcParams &p, const uint32_
     return -INFINITY;
   }
   // float epilogue
+  // cs / bs: this warp's shared-memory copies for these 32 columns (nullptr when the vector is absent);
+  // rs / row_bias: this row's scale and bias, loaded once per tile.
   float v[32];
-  const float rs = p.row_scale ? p.row_scale[row] : 1.0f;
 #pragma unroll
   for (int e = 0; e < 32; ++e) {
     float acc = ACC_INT ? (float)(int32_t)r[e] : __uint_as_float(r[e]);
-    float x = __fmul_rn(p.alpha_f, acc);
-    if (p.row_scale && !p.col_scale_first) x = __fmul_rn(x, rs);
-    if (p.col_scale && e < ncols) x = __fmul_rn(x, __ldg(p.col_scale + col0 + e));
-    if (p.row_scale && p.col_scale_first) x = __fmul_rn(x, rs);
-    if (p.bias && e < ncols) x = __fadd_rn(x, p.bias_per_row ? __ldg(p.bias + row) : __ldg(p.bias + col0 + e));
-    v[e] = x;
+    v[e] = __fmul_rn(p.alpha_f, acc);
+  }
+  if (p.row_scale && !p.col_scale_first) {
+#pragma unroll
+    for (int e = 0; e < 32; ++e) v[e] = __fmul_rn(v[e], rs);
+  }
+  if (cs) {
+    const float4 *cs4 = reinterpret_cast<const float4 *>(cs);
+#pragma unroll
+    for (int q = 0; q < 8; ++q) {
+      const float4 c4 = cs4[q];
+      v[4 * q] = __fmul_rn(v[4 * q], c4.x);
+      v[4 * q + 1] = __fmul_rn(v[4 * q + 1], c4.y);
+      v[4 * q + 2] = __fmul_rn(v[4 * q + 2], c4.z);
+      v[4 * q + 3] = __fmul_rn(v[4 * q + 3], c4.w);
+    }
+  }
+  if (p.row_scale && p.col_scale_first) {
+#pragma unroll
+    for (int e = 0; e < 32; ++e) v[e] = __fmul_rn(v[e], rs);
+  }
+  if (bs) {
+    const float4 *bs4 = reinterpret_cast<const float4 *>(bs);
+#pragma unroll
+    for (int q = 0; q < 8; ++q) {
+      const float4 b4 = bs4[q];
+      v[4 * q] = __fadd_rn(v[4 * q], b4.x);
+      v[4 * q + 1] = __fadd_rn(v[4 * q + 1], b4.y);
+      v[4 * q + 2] = __fadd_rn(v[4 * q + 2], b4.z);
+      v[4 * q + 3] = __fadd_rn(v[4 * q + 3], b4.w);
+    }
+  } else if (p.bias) {
+#pragma unroll
+    for (int e = 0; e < 32; ++e) v[e] = __fadd_rn(v[e], row_bias);
   }
   const int64_t base = (int64_t)row * p.rsc + (int64_t)col0 * p.csc;
   if (p.beta_f != 0.0f) {
@@ -540,12 +595,17 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
     const int quad = warp & 3;
     uint32_t acc = 0, acc_phase = 0;
     float tile_max = -INFINITY;  // running maximum of this thread's results (optional global maximum)
+    float *cs = EpiVectors<BN>::scale(bar_gen + 256, quad), *bs = EpiVectors<BN>::bias(bar_gen + 256, quad);
+    const bool has_cs = p.col_scale != nullptr, has_bs = p.bias != nullptr && !p.bias_per_row;
     TileUnit u;
     for (int it = 0; get_unit<BN>(p, it, u); ++it) {
       const int m0 = u.m0, n0 = u.n0;
+      const int row = m0 + quad * 32 + lane;
+      EpiVectors<BN>::fill(p, cs, bs, n0, u.ncols, lane);
+      const float rs = (p.row_scale && row < p.M) ? __ldg(p.row_scale + row) : 1.0f;
+      const float row_bias = (p.bias && p.bias_per_row && row < p.M) ? __ldg(p.bias + row) : 0.0f;
       if (!mbar_wait(tfull_bar + 8 * acc, acc_phase, abort_flag, p.status, ERR_WAIT_TMEM_FULL)) break;
       tc_fence_after();
-      const int row = m0 + quad * 32 + lane;
       const uint32_t taddr = tmem_base + acc * BN + ((uint32_t)(quad * 32) << 16);
 #pragma unroll 1
       for (int c0 = 0; c0 < u.ncols; c0 += 32) {
@@ -555,7 +615,9 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
           tmem_ld32(taddr + c0, r);
         else
           tmem_ld16(taddr + c0, r);
-        if (row < p.M) tile_max = fmaxf(tile_max, epilogue_chunk<KIND == KIND_I8>(p, r, row, n0 + c0));
+        if (row < p.M)
+          tile_max = fmaxf(tile_max, epilogue_chunk<KIND == KIND_I8>(p, r, row, n0 + c0, has_cs ? cs + c0 : nullptr,
+                                                                     has_bs ? bs + c0 : nullptr, rs, row_bias));
       }
       tc_fence_before();
       mbar_arrive(tempty_bar + 8 * acc);
@@ -601,7 +663,7 @@ struct Tc2Config {
   static constexpr int STAGES_RAW = (220 * 1024) / STAGE_BYTES;
   static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
   static constexpr int TMEM_COLS = 2 * BN;
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256 + EpiVectors<BN>::BYTES;
 };
 
 template <int BN, int KIND>
@@ -745,20 +807,27 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
     uint32_t acc = 0, acc_phase = 0;
     float tile_max = -INFINITY;
     const uint32_t leader_tempty = mapa(tempty_bar, 0);
+    float *cs = EpiVectors<BN>::scale(bar_gen + 256, quad), *bs = EpiVectors<BN>::bias(bar_gen + 256, quad);
+    const bool has_cs = p.col_scale != nullptr, has_bs = p.bias != nullptr && !p.bias_per_row;
     for (int t = pair; t < num_tiles; t += num_pairs) {
       int mi, ni;
       tile_coords(t, p.tiles_m, p.tiles_n, p.raster_gm, mi, ni);
       const int m0 = mi * (2 * BM) + (int)rank * BM, n0 = ni * BN;
+      const int row = m0 + quad * 32 + lane;
+      EpiVectors<BN>::fill(p, cs, bs, n0, BN, lane);
+      const float rs = (p.row_scale && row < p.M) ? __ldg(p.row_scale + row) : 1.0f;
+      const float row_bias = (p.bias && p.bias_per_row && row < p.M) ? __ldg(p.bias + row) : 0.0f;
       if (!mbar_wait(tfull_bar + 8 * acc, acc_phase, abort_flag, p.status, ERR_WAIT_TMEM_FULL)) break;
       tc_fence_after();
-      const int row = m0 + quad * 32 + lane;
       const uint32_t taddr = tmem_base + acc * BN + ((uint32_t)(quad * 32) << 16);
 #pragma unroll 1
       for (int c0 = 0; c0 < BN; c0 += 32) {
         if (n0 + c0 >= p.N) break;
         uint32_t r[32];
         tmem_ld32(taddr + c0, r);
-        if (row < p.M) tile_max = fmaxf(tile_max, epilogue_chunk<KIND == KIND_I8>(p, r, row, n0 + c0));
+        if (row < p.M)
+          tile_max = fmaxf(tile_max, epilogue_chunk<KIND == KIND_I8>(p, r, row, n0 + c0, has_cs ? cs + c0 : nullptr,
+                                                                     has_bs ? bs + c0 : nullptr, rs, row_bias));
       }
       tc_fence_before();
       mbar_arrive_cluster(leader_tempty + 8 * acc);
