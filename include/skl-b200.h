@@ -242,11 +242,30 @@ SKL_FUNC void skl_gemm_ex_sm100a(size_t m, size_t n, size_t k, skl_b200_dtype_t 
  *     v = alpha*(float)acc;  v *= row_scale[i];  v *= col_scale[j];     (each when its pointer != NULL)
  *     v = v + bias[j]                      when bias != NULL (n entries)
  *     v = beta*(float)C[i,j] + v           when beta != 0
+ *     v = act(v)                           when activation != SKL_B200_ACT_NONE (below)
  *     *global_max = max(*global_max, v)    when global_max != NULL (NaN results are ignored; the caller
  *                                          initialises it, e.g. to -INFINITY; updated atomically)
  *     C[i,j] = narrow(v)
  *
+ * Activations -- the step SKL names as the next candidate for fusion (src/gemm/README.md:46-47) -- follow the
+ * definitions of SKL's element-wise routines (ref/sigmoid/sigmoid_f32.c:10-28, ref/gelu/gelu_f32.c:12-22),
+ * evaluated in fp32; the tests hold them to ULP bounds taken from SKL's own activation tests
+ * (test/sigmoid/sigmoid_f32_zve32f.c, test/gelu/skl_gelu_f32_zve32f.c):
+ *     LOGISTIC  1 / (1 + exp(-act_param * v))                       skl_sigmoid_f32 with beta = act_param
+ *     SWISH     v / (1 + exp(-act_param * v))                       skl_swish_f32; act_param = 1 is skl_silu_f32
+ *     GELU      max(v, 0) - |v|/2 * erfc(|v| / sqrt 2)              skl_gelu_f32
+ *     SWIGLU    v / (1 + exp(-v)) * (C[i,j] + act_param)            skl_swiglu_f32 with gate = v, up = the value
+ *               already stored in C[i,j] (e.g. by the up-projection GEMM), delta = act_param; beta must be 0
+ *
  * Pointers in the struct may be host or device memory, like every other argument. */
+typedef enum skl_b200_activation {
+  SKL_B200_ACT_NONE = 0,
+  SKL_B200_ACT_LOGISTIC = 1,
+  SKL_B200_ACT_SWISH = 2,
+  SKL_B200_ACT_GELU = 3,
+  SKL_B200_ACT_SWIGLU = 4
+} skl_b200_activation_t;
+
 typedef struct skl_b200_fused {
   float alpha;
   float beta;
@@ -254,6 +273,8 @@ typedef struct skl_b200_fused {
   const float *col_scale; /* n entries or NULL */
   const float *bias;      /* n entries or NULL */
   float *global_max;      /* one float or NULL */
+  int activation;         /* skl_b200_activation_t */
+  float act_param;        /* see the table above */
 } skl_b200_fused_t;
 
 SKL_FUNC void skl_gemm_fused_sm100a(size_t m, size_t n, size_t k, skl_b200_dtype_t ta, const void *a,

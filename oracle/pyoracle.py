@@ -83,7 +83,9 @@ def port():
         lib.orc_gemm_ex.argtypes = [_SZ, _SZ, _SZ, _I, _VP, _SZ, _SZ, _I, _VP, _SZ, _SZ, _F, _VP, _VP,
                                     _F, _I, _VP, _SZ, _SZ]
         lib.orc_gemm_fused.argtypes = [_SZ, _SZ, _SZ, _I, _VP, _SZ, _SZ, _I, _VP, _SZ, _SZ, _F, _VP, _VP, _VP, _VP,
-                                       _F, _I, _VP, _SZ, _SZ]
+                                       _F, _I, _F, _I, _VP, _SZ, _SZ]
+        lib.orc_activation.argtypes = [_I, _F, _F, _F]
+        lib.orc_activation.restype = _F
         lib.orc_pack.argtypes = [_SZ, _SZ, _SZ, _VP, _SZ, _SZ, _SZ, _SZ, _VP, _SZ, _SZ, _SZ, _SZ,
                                  C.c_uint32]
         lib.orc_unpack.argtypes = [_SZ, _SZ, _SZ, _VP, _SZ, _SZ, _SZ, _SZ, _SZ, _SZ, _VP, _SZ, _SZ]
@@ -135,6 +137,9 @@ def ref():
             getattr(lib, f"skl_transpose_e{e}_ref").argtypes = [_SZ, _SZ, _VP, _SZ, _VP, _SZ]
         lib.skl_unpack_e8rcprc_e8rc_ref.argtypes = [_SZ, _SZ, _VP, _SZ, _SZ, _SZ, _SZ, _SZ, _SZ, _VP,
                                                     _SZ, _SZ]
+        if hasattr(lib, "skl_sigmoid_f32_ref"):  # a library built before the activation files were added lacks them
+            lib.skl_sigmoid_f32_ref.argtypes = [_VP, _F, _VP, _VP, _VP, _F, _SZ]
+            lib.skl_gelu_f32_ref.argtypes = [_VP, _VP, _SZ]
         _ref = lib
     return _ref
 
@@ -168,10 +173,14 @@ def port_gemm_ex(m, n, k, ta, a, rsa, csa, tb, b, rsb, csb, alpha, row_scale, co
                        _p(col_scale), float(beta), tc, _p(c), rsc, csc)
 
 
+ACT_NONE, ACT_LOGISTIC, ACT_SWISH, ACT_GELU, ACT_SWIGLU = range(5)
+
+
 def port_gemm_fused(m, n, k, ta, a, rsa, csa, tb, b, rsb, csb, alpha, row_scale, col_scale, bias, global_max, beta,
-                    tc, c, rsc, csc) -> None:
+                    tc, c, rsc, csc, activation: int = ACT_NONE, act_param: float = 0.0) -> None:
     port().orc_gemm_fused(m, n, k, ta, _p(a), rsa, csa, tb, _p(b), rsb, csb, float(alpha), _p(row_scale),
-                          _p(col_scale), _p(bias), _p(global_max), float(beta), tc, _p(c), rsc, csc)
+                          _p(col_scale), _p(bias), _p(global_max), float(beta), int(activation), float(act_param),
+                          tc, _p(c), rsc, csc)
 
 
 _ESIZE = {I8: 1, BF16: 2, F16: 2, F8E4M3: 1, F8E5M2: 1, F32: 4, I32: 4}

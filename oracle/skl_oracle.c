@@ -12,6 +12,7 @@
  */
 #include "skl_oracle.h"
 
+#include <math.h>
 #include <string.h>
 
 /* ------------------------------------------------------------------ bit casts */
@@ -356,10 +357,41 @@ static inline void store_c(int tc, void *c, size_t idx, float v) {
   }
 }
 
+/* ref/sigmoid/sigmoid_f32.c:10-28 (logistic in double, times the linear unit, times the gate, one final
+ * rounding) and ref/gelu/gelu_f32.c:12-22 (relu plus a double-precision erfc offset), for one element. */
+float orc_activation(int act, float p, float v, float up) {
+  switch (act) {
+  case ORC_ACT_LOGISTIC:
+  case ORC_ACT_SWISH:
+  case ORC_ACT_SWIGLU: {
+    const float beta = (act == ORC_ACT_SWIGLU) ? 1.0f : p;
+    const double x = v;
+    double o = 1. / (1. + exp(-beta * x));
+    if (act != ORC_ACT_LOGISTIC) {
+      o *= v;
+    }
+    if (act == ORC_ACT_SWIGLU) {
+      o *= (up + p);
+    }
+    return (float)o;
+  }
+  case ORC_ACT_GELU: {
+    const double sqrt2 = 0x1.6a09e667f3bcdp0;
+    float b = (v > 0) ? v : -0.f;
+    float h = -0.5f * fabsf(v);
+    double e = erfc(-sqrt2 * h);
+    double g = fma(h, e, b);
+    return (float)g;
+  }
+  default:
+    return v;
+  }
+}
+
 void orc_gemm_fused(size_t m, size_t n, size_t k, int ta, const void *a, size_t rsa, size_t csa, int tb,
                     const void *b, size_t rsb, size_t csb, float alpha, const float *row_scale,
-                    const float *col_scale, const float *bias, float *global_max, float beta, int tc, void *c,
-                    size_t rsc, size_t csc) {
+                    const float *col_scale, const float *bias, float *global_max, float beta, int activation,
+                    float act_param, int tc, void *c, size_t rsc, size_t csc) {
   for (size_t i = 0; i < m; ++i) {
     for (size_t j = 0; j < n; ++j) {
       float v;
@@ -394,6 +426,9 @@ void orc_gemm_fused(size_t m, size_t n, size_t k, int ta, const void *a, size_t 
         float left = beta * load_c(tc, c, idx);
         v = left + v;
       }
+      if (activation != ORC_ACT_NONE) {
+        v = orc_activation(activation, act_param, v, activation == ORC_ACT_SWIGLU ? load_c(tc, c, idx) : 0.0f);
+      }
       if (global_max && v > *global_max) { /* false for NaN, as in the reference's example kernel */
         *global_max = v;
       }
@@ -405,7 +440,8 @@ void orc_gemm_fused(size_t m, size_t n, size_t k, int ta, const void *a, size_t 
 void orc_gemm_ex(size_t m, size_t n, size_t k, int ta, const void *a, size_t rsa, size_t csa, int tb,
                  const void *b, size_t rsb, size_t csb, float alpha, const float *row_scale,
                  const float *col_scale, float beta, int tc, void *c, size_t rsc, size_t csc) {
-  orc_gemm_fused(m, n, k, ta, a, rsa, csa, tb, b, rsb, csb, alpha, row_scale, col_scale, 0, 0, beta, tc, c, rsc, csc);
+  orc_gemm_fused(m, n, k, ta, a, rsa, csa, tb, b, rsb, csb, alpha, row_scale, col_scale, 0, 0, beta, ORC_ACT_NONE, 0.0f, tc, c,
+                 rsc, csc);
 }
 
 /* ------------------------------------------------------------------ pack / unpack / transpose */

@@ -98,11 +98,17 @@ void orc_gemm_ex(size_t m, size_t n, size_t k, int ta, const void *a, size_t rsa
 /* The same with the two epilogue kernels the reference documents as examples of its fused-kernel hook
  * (src/gemm/fused-kernel-API.md:170-217): a bias row vector added after the scales, and the running global
  * maximum of the results (NaN ignored), both optional:
- *     v = alpha*acc; *row_scale[i]; *col_scale[j]; v = v + bias[j]; v = beta*C + v; *gmax = max(*gmax, v); C = narrow(v) */
+ *     v = alpha*acc; *row_scale[i]; *col_scale[j]; v = v + bias[j]; v = beta*C + v; v = act(v);
+ *     *gmax = max(*gmax, v); C = narrow(v)
+ * act is one of the reference's element-wise routines (ref/sigmoid/sigmoid_f32.c:10-28,
+ * ref/gelu/gelu_f32.c:12-22), evaluated in double and rounded once as they are there. */
+enum { ORC_ACT_NONE = 0, ORC_ACT_LOGISTIC = 1, ORC_ACT_SWISH = 2, ORC_ACT_GELU = 3, ORC_ACT_SWIGLU = 4 };
+/* LOGISTIC 1/(1+exp(-p*v)); SWISH that times v (p = 1: SiLU); GELU; SWIGLU silu(v)*(up + p). */
+float orc_activation(int act, float p, float v, float up);
 void orc_gemm_fused(size_t m, size_t n, size_t k, int ta, const void *a, size_t rsa, size_t csa, int tb,
                     const void *b, size_t rsb, size_t csb, float alpha, const float *row_scale,
-                    const float *col_scale, const float *bias, float *global_max, float beta, int tc, void *c,
-                    size_t rsc, size_t csc);
+                    const float *col_scale, const float *bias, float *global_max, float beta, int activation,
+                    float act_param, int tc, void *c, size_t rsc, size_t csc);
 
 /* ---- pack / unpack / transpose (ref/pack/pack_e8rc_e8rcprc.c:10-35, unpack_e8rcprc_e8rc.c:10-37,
  * transpose_e8.c:11-19 and the e16 / e32 siblings); esize is the element size in bytes (1, 2, 4). */

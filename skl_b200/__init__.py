@@ -132,7 +132,10 @@ def ptr(x) -> int:
 class Fused(C.Structure):
     """skl_b200_fused_t"""
     _fields_ = [("alpha", C.c_float), ("beta", C.c_float), ("row_scale", C.c_void_p), ("col_scale", C.c_void_p),
-                ("bias", C.c_void_p), ("global_max", C.c_void_p)]
+                ("bias", C.c_void_p), ("global_max", C.c_void_p), ("activation", C.c_int), ("act_param", C.c_float)]
+
+
+ACT_NONE, ACT_LOGISTIC, ACT_SWISH, ACT_GELU, ACT_SWIGLU = range(5)
 
 
 class SklB200Error(RuntimeError):

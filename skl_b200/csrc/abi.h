@@ -35,6 +35,16 @@ enum {
   SKL_EPI_FLOAT = 1
 };
 
+/* Activation applied to the float epilogue's value v (same numbering as skl_b200_activation_t); the
+ * definitions are the reference's scalar routines ref/sigmoid/sigmoid_f32.c:10-28 and ref/gelu/gelu_f32.c:12-22. */
+enum {
+  SKL_ACT_NONE = 0,
+  SKL_ACT_LOGISTIC = 1, /* 1 / (1 + exp(-p*v))                                  */
+  SKL_ACT_SWISH = 2,    /* v / (1 + exp(-p*v));  p = 1 is SiLU                   */
+  SKL_ACT_GELU = 3,     /* v * Phi(v), erf form                                  */
+  SKL_ACT_SWIGLU = 4    /* v / (1 + exp(-v)) * (C_old[i,j] + p); beta must be 0  */
+};
+
 /* One GEMM problem.  Plain matrices use m1 = n1 = k1 = 1 and *1 strides of 0. */
 typedef struct skl_b200_gemm_args {
   uint64_t m0, n0, k0; /* block extents (plain matrix: the matrix extents) */
@@ -57,6 +67,8 @@ typedef struct skl_b200_gemm_args {
                               column, or m entries indexed by row when bias_per_row is set (transposed hand-over) */
   int32_t bias_per_row;
   float *global_max;       /* NULL, or one device float raised to the largest result value (NaN ignored) */
+  int32_t activation;      /* SKL_ACT_*: applied after bias and beta*C, before the maximum and the narrowing */
+  float act_param;         /* logistic / swish: beta; swiglu: delta */
 } skl_b200_gemm_args;
 
 /* Device status word written by kernels whose bounded waits expire: 0 = ok, else a stage code. */

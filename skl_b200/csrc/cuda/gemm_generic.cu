@@ -142,6 +142,9 @@ __global__ void __launch_bounds__(256) gemm_generic_kernel(const GenericParams p
         float v = epilogue_value((float)acc[r][c], g.alpha_f, g.row_scale, g.col_scale, i, j);
         if (g.bias) v = __fadd_rn(v, g.bias[g.bias_per_row ? i : j]);
         if (g.beta_f != 0.0f) v = __fadd_rn(__fmul_rn(g.beta_f, load_c_f32(g.tc, g.c, o)), v);
+        if (g.activation)
+          v = activation_value(g.activation, g.act_param, v,
+                               g.activation == SKL_ACT_SWIGLU ? load_c_f32(g.tc, g.c, o) : 0.0f);
         if (v == v) local_max = fmaxf(local_max, v);
         store_c_f32(g.tc, g.c, o, v);
       }

@@ -64,6 +64,8 @@ struct TcParams {
   const float *bias;
   int bias_per_row;
   float *global_max;
+  int activation;
+  float act_param;
   uint32_t *status;
 };
 
@@ -337,7 +339,7 @@ struct TcConfig {
 
 // ------------------------------------------------------------------ epilogue for 32 accumulator columns
 // Returns the largest value written (for the optional global maximum); -INFINITY for the int epilogue.
-template <bool ACC_INT>
+template <bool ACC_INT, bool ACT>
 __device__ __forceinline__ float epilogue_chunk(const TcParams &p, const uint32_t (&r)[32], int row, int col0,
                                                 const float *cs, const float *bs, float rs, float row_bias) {
   const int ncols = (p.N - col0) < 32 ? (p.N - col0) : 32;
@@ -417,6 +419,24 @@ __device__ __forceinline__ float epilogue_chunk(const TcParams &p, const uint32_
       if (e < ncols)
         v[e] = __fadd_rn(__fmul_rn(p.beta_f, load_c_f32(p.tc, p.c, base + (int64_t)e * p.csc)), v[e]);
   }
+  if (ACT && p.activation) {
+    if (p.activation == SKL_ACT_SWIGLU) {
+#pragma unroll
+      for (int e = 0; e < 32; ++e)
+        if (e < ncols)
+          v[e] = activation_value(SKL_ACT_SWIGLU, p.act_param, v[e], load_c_f32(p.tc, p.c, base + (int64_t)e * p.csc));
+    } else if (p.activation == SKL_ACT_GELU) {
+#pragma unroll
+      for (int e = 0; e < 32; ++e) v[e] = gelu_f32(v[e]);
+    } else {
+      const bool times_v = p.activation == SKL_ACT_SWISH;
+#pragma unroll
+      for (int e = 0; e < 32; ++e) {
+        const float o = logistic_f32(p.act_param, v[e]);
+        v[e] = times_v ? __fmul_rn(o, v[e]) : o;
+      }
+    }
+  }
   float vmax = -INFINITY;
   if (p.global_max) {
 #pragma unroll
@@ -459,7 +479,7 @@ __device__ __forceinline__ float epilogue_chunk(const TcParams &p, const uint32_
 }
 
 // ------------------------------------------------------------------ the kernel
-template <int BN, int KIND>
+template <int BN, int KIND, bool ACT>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
     gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                    const TcParams p) {
@@ -616,7 +636,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         else
           tmem_ld16(taddr + c0, r);
         if (row < p.M)
-          tile_max = fmaxf(tile_max, epilogue_chunk<KIND == KIND_I8>(p, r, row, n0 + c0, has_cs ? cs + c0 : nullptr,
+          tile_max = fmaxf(tile_max, epilogue_chunk<KIND == KIND_I8, ACT>(p, r, row, n0 + c0, has_cs ? cs + c0 : nullptr,
                                                                      has_bs ? bs + c0 : nullptr, rs, row_bias));
       }
       tc_fence_before();
@@ -666,7 +686,7 @@ struct Tc2Config {
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256 + EpiVectors<BN>::BYTES;
 };
 
-template <int BN, int KIND>
+template <int BN, int KIND, bool ACT>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
     gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                     const TcParams p) {
@@ -826,7 +846,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         uint32_t r[32];
         tmem_ld32(taddr + c0, r);
         if (row < p.M)
-          tile_max = fmaxf(tile_max, epilogue_chunk<KIND == KIND_I8>(p, r, row, n0 + c0, has_cs ? cs + c0 : nullptr,
+          tile_max = fmaxf(tile_max, epilogue_chunk<KIND == KIND_I8, ACT>(p, r, row, n0 + c0, has_cs ? cs + c0 : nullptr,
                                                                      has_bs ? bs + c0 : nullptr, rs, row_bias));
       }
       tc_fence_before();
@@ -981,26 +1001,32 @@ int pick_bn(int64_t M, int64_t N, int kind, bool b_mn_major) {
   return best;
 }
 
-template <int BN, int KIND>
-int launch_cfg(const CUtensorMap &ta, const CUtensorMap &tb, const TcParams &p, cudaStream_t s) {
+template <int BN, int KIND, bool ACT>
+int launch_cfg_act(const CUtensorMap &ta, const CUtensorMap &tb, const TcParams &p, cudaStream_t s) {
   using Cfg = TcConfig<BN>;
   static bool attr_set[64] = {};  // per device: function attributes do not carry over between devices
   const int dev = current_device();
   if (!attr_set[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, KIND>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, KIND, ACT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          Cfg::SMEM_BYTES);
     if (e != cudaSuccess) return (int)e;
     attr_set[dev] = true;
   }
   int grid = p.tiles_m * p.tiles_n;
   if (grid > sm_count()) grid = sm_count();
-  gemm_tc_kernel<BN, KIND><<<grid, NUM_THREADS, Cfg::SMEM_BYTES, s>>>(ta, tb, p);
+  gemm_tc_kernel<BN, KIND, ACT><<<grid, NUM_THREADS, Cfg::SMEM_BYTES, s>>>(ta, tb, p);
   SKLB_COUNT_LAUNCH();
   return (int)cudaGetLastError();
 }
 
+// The activation code lives in instantiations of its own so that the plain epilogue carries none of it.
 template <int BN, int KIND>
-int launch_cfg2(const CUtensorMap &ta, const CUtensorMap &tb, const TcParams &p, cudaStream_t s) {
+int launch_cfg(const CUtensorMap &ta, const CUtensorMap &tb, const TcParams &p, cudaStream_t s) {
+  return p.activation ? launch_cfg_act<BN, KIND, true>(ta, tb, p, s) : launch_cfg_act<BN, KIND, false>(ta, tb, p, s);
+}
+
+template <int BN, int KIND, bool ACT>
+int launch_cfg2_act(const CUtensorMap &ta, const CUtensorMap &tb, const TcParams &p, cudaStream_t s) {
   using Cfg = Tc2Config<BN>;
   static int max_pairs_dev[64];
   static bool pairs_known[64] = {};
@@ -1009,7 +1035,7 @@ int launch_cfg2(const CUtensorMap &ta, const CUtensorMap &tb, const TcParams &p,
   if (!pairs_known[dev]) {
     pairs_known[dev] = true;
     max_pairs = -1;
-    cudaError_t e = cudaFuncSetAttribute(gemm_tc2_kernel<BN, KIND>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc2_kernel<BN, KIND, ACT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          Cfg::SMEM_BYTES);
     if (e != cudaSuccess) return (int)e;
     // how many 2-CTA clusters the device can hold at once (some SMs may have no free neighbour)
@@ -1025,7 +1051,7 @@ int launch_cfg2(const CUtensorMap &ta, const CUtensorMap &tb, const TcParams &p,
     q.attrs = qa;
     q.numAttrs = 1;
     int n = 0;
-    e = cudaOccupancyMaxActiveClusters(&n, gemm_tc2_kernel<BN, KIND>, &q);
+    e = cudaOccupancyMaxActiveClusters(&n, gemm_tc2_kernel<BN, KIND, ACT>, &q);
     if (e != cudaSuccess || n <= 0) {
       (void)cudaGetLastError();
       n = sm_count() / 2;
@@ -1046,10 +1072,15 @@ int launch_cfg2(const CUtensorMap &ta, const CUtensorMap &tb, const TcParams &p,
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc2_kernel<BN, KIND>, ta, tb, p);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc2_kernel<BN, KIND, ACT>, ta, tb, p);
   SKLB_COUNT_LAUNCH();
   if (e != cudaSuccess) return (int)e;
   return (int)cudaGetLastError();
+}
+
+template <int BN, int KIND>
+int launch_cfg2(const CUtensorMap &ta, const CUtensorMap &tb, const TcParams &p, cudaStream_t s) {
+  return p.activation ? launch_cfg2_act<BN, KIND, true>(ta, tb, p, s) : launch_cfg2_act<BN, KIND, false>(ta, tb, p, s);
 }
 
 // 0 = never, 1 = when the heuristic says so (default), 2 = whenever the layout allows it
@@ -1178,6 +1209,8 @@ extern "C" int skl_b200_launch_gemm_tc(const skl_b200_gemm_args *g, uint32_t *de
   p.bias = g->bias;
   p.bias_per_row = g->bias_per_row;
   p.global_max = g->global_max;
+  p.activation = g->activation;
+  p.act_param = g->act_param;
   p.status = dev_status;
   cudaStream_t s = (cudaStream_t)stream;
 

@@ -39,6 +39,8 @@ struct GemvParams {
   float alpha_f, beta_f;
   const float *row_scale, *col_scale, *bias;
   float *global_max;
+  int activation;
+  float act_param;
   uint32_t *status;
 };
 
@@ -126,6 +128,8 @@ __device__ __forceinline__ float gemv_store(const GemvParams &p, int mi, int j, 
   if (p.col_scale) v = __fmul_rn(v, cs);
   if (p.bias) v = __fadd_rn(v, bias);
   if (p.beta_f != 0.0f) v = __fadd_rn(__fmul_rn(p.beta_f, load_c_f32(p.tc, p.c, o)), v);
+  if (p.activation)
+    v = activation_value(p.activation, p.act_param, v, p.activation == SKL_ACT_SWIGLU ? load_c_f32(p.tc, p.c, o) : 0.0f);
   store_c_f32(p.tc, p.c, o, v);
   return (v == v) ? v : -INFINITY;
 }
@@ -350,6 +354,8 @@ extern "C" int skl_b200_launch_gemv_i8(const skl_b200_gemm_args *g, uint32_t *de
   p.col_scale = g->col_scale;
   p.bias = g->bias;
   p.global_max = g->global_max;
+  p.activation = g->activation;
+  p.act_param = g->act_param;
   p.status = dev_status;
   int mp = 1;
   while (mp < p.m) mp <<= 1;

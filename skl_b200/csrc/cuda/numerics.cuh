@@ -235,6 +235,41 @@ __device__ __forceinline__ float epilogue_value(float acc, float alpha, const fl
   return v;
 }
 
+// Activations of the float epilogue, after the reference's scalar definitions (ref/sigmoid/sigmoid_f32.c:10-28:
+// logistic o = 1/(1+exp(-beta*x)), then o *= y for the linear unit, then o *= (up + delta) for the gate;
+// ref/gelu/gelu_f32.c:12-22: relu(x) + (-|x|/2) * erfc(|x|/sqrt 2)).  The reference evaluates them in double and
+// rounds once; here they are fp32 with the accurate expf / erfcf, the product -p*v carried as a rounded part
+// plus its exact remainder so that a large exponent argument does not magnify the product's rounding.
+__device__ __forceinline__ float logistic_f32(float p, float v) {
+  const float hi = __fmul_rn(-p, v);
+  const float lo = __fmaf_rn(-p, v, -hi);  // exact: -p*v = hi + lo
+  if (hi > 20.0f) {
+    // 1 + e^a = e^a to within 2^-28 here, so the result is e^-a: no overflow of e^a, and the tail runs
+    // through the subnormals down to zero as the double-precision definition does
+    const float t = expf(-hi);
+    return __fmaf_rn(t, -lo, t);
+  }
+  float t = expf(hi);
+  t = __fmaf_rn(t, lo, t);  // exp(hi + lo) ~ exp(hi) * (1 + lo)
+  return __fdiv_rn(1.0f, __fadd_rn(1.0f, t));
+}
+__device__ __forceinline__ float gelu_f32(float v) {
+  const float b = v > 0.0f ? v : -0.0f;
+  const float h = __fmul_rn(-0.5f, fabsf(v));
+  const float e = erfcf(__fmul_rn(-1.41421356237309504880f, h));
+  return __fmaf_rn(h, e, b);
+}
+// `old` is C's previous value (read only for SKL_ACT_SWIGLU).
+__device__ __forceinline__ float activation_value(int act, float p, float v, float old) {
+  switch (act) {
+    case SKL_ACT_LOGISTIC: return logistic_f32(p, v);
+    case SKL_ACT_SWISH: return __fmul_rn(logistic_f32(p, v), v);
+    case SKL_ACT_GELU: return gelu_f32(v);
+    case SKL_ACT_SWIGLU: return __fmul_rn(__fmul_rn(logistic_f32(1.0f, v), v), __fadd_rn(old, p));
+    default: return v;
+  }
+}
+
 // *addr = max(*addr, v) for floats (NaN never wins): the IEEE ordering of non-negative floats equals the
 // ordering of their bit patterns as signed integers, that of negative floats the reverse as unsigned.
 __device__ __forceinline__ void atomic_max_f32(float *addr, float v) {

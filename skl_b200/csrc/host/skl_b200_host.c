@@ -367,6 +367,12 @@ static int widen_fp8_operand(skl_b200_gemm_args *g) {
 }
 
 /* Chooses the kernel family for a device-resident problem and enqueues it on the library stream. */
+/* Does the epilogue read C's previous contents (so that a host C has to be copied in first)? */
+static int reads_old_c(const skl_b200_gemm_args *g) {
+  if (g->epilogue == SKL_EPI_INT) return g->beta_i != 0;
+  return g->beta_f != 0.0f || g->activation == SKL_ACT_SWIGLU;
+}
+
 static int dispatch_launch(const skl_b200_gemm_args *gin) {
   skl_b200_gemm_args local = *gin, *g = &local;
   const uint64_t M = g->m0 * g->m1, N = g->n0 * g->n1, K = g->k0 * g->k1;
@@ -485,7 +491,7 @@ static int run_gemm_pipelined(skl_b200_gemm_args *g, int a_host, int c_host, int
   if (chunks > PIPE_MAX_CHUNKS) chunks = PIPE_MAX_CHUNKS;
   if (chunks < 2) chunks = 2;
   const uint64_t rows_per = ((M + chunks - 1) / chunks + 255) / 256 * 256; /* whole 256-row tiles */
-  const int need_old = (g->epilogue == SKL_EPI_INT) ? (g->beta_i != 0) : (g->beta_f != 0.0f);
+  const int need_old = reads_old_c(g);
   int c_idx = 0;
   for (uint64_t i0 = 0; i0 < M; i0 += rows_per, ++c_idx) {
     const uint64_t rows = (M - i0) < rows_per ? (M - i0) : rows_per;
@@ -594,7 +600,7 @@ static void run_gemm(skl_b200_gemm_args *g) {
   if (c_host) {
     host_any = 1;
     size_t span = span4(g->m0, g->n0, g->m1, g->n1, g->rsc0, g->csc0, g->rsc1, g->csc1) * ec;
-    int need_old = (g->epilogue == SKL_EPI_INT) ? (g->beta_i != 0) : (g->beta_f != 0.0f);
+    int need_old = reads_old_c(g);
     size_t width = 0, height = 0, pitch = 0;
     if (g->m1 == 1 && g->n1 == 1) {
       if (g->csc0 == 1 && (uint64_t)g->rsc0 >= g->n0) {
@@ -627,7 +633,7 @@ static void gemm_plain(int ta, int tb, int tc, int epi, size_t m, size_t n, size
                        size_t rsa, size_t csa, const void *b, size_t rsb, size_t csb, void *c,
                        size_t rsc, size_t csc, int32_t alpha_i, int32_t beta_i, float alpha_f,
                        float beta_f, const float *row_scale, const float *col_scale, const float *bias,
-                       float *global_max) {
+                       float *global_max, int activation, float act_param) {
   skl_b200_gemm_args g;
   memset(&g, 0, sizeof g);
   g.m0 = m; g.n0 = n; g.k0 = k;
@@ -642,6 +648,7 @@ static void gemm_plain(int ta, int tb, int tc, int epi, size_t m, size_t n, size
   g.alpha_f = alpha_f; g.beta_f = beta_f;
   g.row_scale = row_scale; g.col_scale = col_scale;
   g.bias = bias; g.global_max = global_max;
+  g.activation = activation; g.act_param = act_param;
   run_gemm(&g);
 }
 
@@ -672,14 +679,14 @@ void skl_gemm_i8rc_i8rc_i32rc_sm100a(size_t m, size_t n, size_t k, int32_t alpha
                                      size_t rsa, size_t csa, const int8_t *b, size_t rsb, size_t csb,
                                      int32_t beta, int32_t *c, size_t rsc, size_t csc) {
   gemm_plain(SKL_DT_I8, SKL_DT_I8, SKL_DT_I32, SKL_EPI_INT, m, n, k, a, rsa, csa, b, rsb, csb, c, rsc, csc,
-             alpha, beta, 0.0f, 0.0f, 0, 0, 0, 0);
+             alpha, beta, 0.0f, 0.0f, 0, 0, 0, 0, SKL_ACT_NONE, 0.0f);
 }
 
 #define SKL_B200_DEF_GEMM_RC_F32(NAME, TYPE, DT)                                                      \
   void NAME(size_t m, size_t n, size_t k, float alpha, const TYPE *a, size_t rsa, size_t csa,         \
             const TYPE *b, size_t rsb, size_t csb, float beta, float *c, size_t rsc, size_t csc) {    \
     gemm_plain(DT, DT, SKL_DT_F32, SKL_EPI_FLOAT, m, n, k, a, rsa, csa, b, rsb, csb, c, rsc, csc, 0, 0, \
-               alpha, beta, 0, 0, 0, 0);                                                              \
+               alpha, beta, 0, 0, 0, 0, SKL_ACT_NONE, 0.0f);                                          \
   }
 SKL_B200_DEF_GEMM_RC_F32(skl_gemm_bf16rc_bf16rc_f32rc_sm100a, skl_bf16_t, SKL_DT_BF16)
 SKL_B200_DEF_GEMM_RC_F32(skl_gemm_f16rc_f16rc_f32rc_sm100a, skl_f16_t, SKL_DT_F16)
@@ -760,8 +767,14 @@ void skl_gemm_fused_sm100a(size_t m, size_t n, size_t k, skl_b200_dtype_t ta, co
     g_ctx.cuda_err[0] = 0;
     return;
   }
+  if (f->activation < SKL_ACT_NONE || f->activation > SKL_ACT_SWIGLU ||
+      (f->activation == SKL_ACT_SWIGLU && f->beta != 0.0f)) {
+    g_ctx.status = SKL_B200_ERR_INVALID_ARGUMENT;
+    g_ctx.cuda_err[0] = 0;
+    return;
+  }
   gemm_plain((int)ta, (int)tb, (int)tc, SKL_EPI_FLOAT, m, n, k, a, rsa, csa, b, rsb, csb, c, rsc, csc, 0, 0,
-             f->alpha, f->beta, f->row_scale, f->col_scale, f->bias, f->global_max);
+             f->alpha, f->beta, f->row_scale, f->col_scale, f->bias, f->global_max, f->activation, f->act_param);
 }
 
 void skl_gemm_ex_sm100a(size_t m, size_t n, size_t k, skl_b200_dtype_t ta, const void *a, size_t rsa,
@@ -775,6 +788,8 @@ void skl_gemm_ex_sm100a(size_t m, size_t n, size_t k, skl_b200_dtype_t ta, const
   f.col_scale = col_scale;
   f.bias = 0;
   f.global_max = 0;
+  f.activation = SKL_B200_ACT_NONE;
+  f.act_param = 0.0f;
   skl_gemm_fused_sm100a(m, n, k, ta, a, rsa, csa, tb, b, rsb, csb, &f, tc, c, rsc, csc);
 }
 

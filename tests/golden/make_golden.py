@@ -162,6 +162,30 @@ def main():
             case += 1
     store["pack_count"] = np.array([case])
 
+    # ---- activations the fused GEMM epilogue follows: skl_sigmoid_f32_ref (logistic / silu / swish / swiglu
+    # through its beta, y, up, delta arguments) and skl_gelu_f32_ref, on the input ranges of the reference's
+    # own tests (test/sigmoid/sigmoid_f32_zve32f.c:27-39, test/gelu/skl_gelu_f32_zve32f.c:23-24) plus specials
+    g = H.rng(77)
+    specials = np.array([0.0, -0.0, 1.0, -1.0, np.inf, -np.inf, np.nan, 1e-30, -1e-30, 88.0, -88.0, 104.0, -104.0],
+                        dtype=np.float32)
+    for name, lo, hi in (("logistic", -104.0, 18.0), ("silu", -110.0, 18.0), ("swish2", -110.0, 18.0),
+                         ("swiglu", -55.0, 18.0), ("gelu", -14.356, 5.348)):
+        x = np.concatenate([g.uniform(lo, hi, 4096).astype(np.float32), g.normal(0, 2, 2048).astype(np.float32),
+                            specials])
+        up = g.normal(0, 3, x.size).astype(np.float32)
+        out = np.zeros_like(x)
+        if name == "logistic":
+            ref.skl_sigmoid_f32_ref(P(out), 1.0, P(x), None, None, 0.0, x.size)
+        elif name == "silu":
+            ref.skl_sigmoid_f32_ref(P(out), 1.0, P(x), P(x), None, 0.0, x.size)
+        elif name == "swish2":
+            ref.skl_sigmoid_f32_ref(P(out), 2.0, P(x), P(x), None, 0.0, x.size)
+        elif name == "swiglu":
+            ref.skl_sigmoid_f32_ref(P(out), 1.0, P(x), P(x), P(up), 0.5, x.size)
+        else:
+            ref.skl_gelu_f32_ref(P(out), P(x), x.size)
+        store[f"act_{name}_x"], store[f"act_{name}_up"], store[f"act_{name}_out"] = x, up, out
+
     path = os.path.join(HERE, "skl_ref_golden.npz")
     np.savez_compressed(path, **store)
     print(path, os.path.getsize(path), "bytes,", len(store), "arrays")

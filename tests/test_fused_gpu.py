@@ -15,7 +15,7 @@ from oracle import pyoracle as orc
 pytestmark = pytest.mark.gpu
 
 
-def run_case(skl, m, n, k, ta, tb, tc, layout, beta, where, force, seed):
+def run_case(skl, m, n, k, ta, tb, tc, layout, beta, where, force, seed, alpha=1.25, act=0, act_param=0.0):
     g = H.rng(seed)
     (rsa, csa), (rsb, csb), (rsc, csc) = layout_strides(layout, m, n, k, 16)
     A = H.Strided(ta, m, k, rsa, csa, g, all_codes=False)
@@ -26,14 +26,14 @@ def run_case(skl, m, n, k, ta, tb, tc, layout, beta, where, force, seed):
     bias = g.uniform(-3, 3, n).astype(np.float32)
     want = Cm.copy()
     gmax_want = np.array([-np.inf], np.float32)
-    orc.port_gemm_fused(m, n, k, ta, A.view, rsa, csa, tb, B.view, rsb, csb, 1.25, rs, cs, bias, gmax_want, beta, tc,
-                        want.view, rsc, csc)
+    orc.port_gemm_fused(m, n, k, ta, A.view, rsa, csa, tb, B.view, rsb, csb, alpha, rs, cs, bias, gmax_want, beta, tc,
+                        want.view, rsc, csc, activation=act, act_param=act_param)
     before = Cm.copy()
     gmax = np.array([-np.inf], np.float32)
     skl.skl_b200_force_path(force)
     try:
         if where == "host":
-            f = S.Fused(1.25, beta, S.ptr(rs), S.ptr(cs), S.ptr(bias), S.ptr(gmax))
+            f = S.Fused(alpha, beta, S.ptr(rs), S.ptr(cs), S.ptr(bias), S.ptr(gmax), act, act_param)
             skl.skl_gemm_fused_sm100a(m, n, k, ta, S.ptr(A.view), rsa, csa, tb, S.ptr(B.view), rsb, csb, C.byref(f), tc,
                                       S.ptr(Cm.view), rsc, csc)
             S.check()
@@ -44,7 +44,7 @@ def run_case(skl, m, n, k, ta, tb, tc, layout, beta, where, force, seed):
             da, db, dc = DeviceBuf(A.buf), DeviceBuf(B.buf), DeviceBuf(Cm.buf)
             drs, dcs, dbias = (torch.from_numpy(x).cuda() for x in (rs, cs, bias))
             dg = torch.from_numpy(gmax).cuda()
-            f = S.Fused(1.25, beta, drs.data_ptr(), dcs.data_ptr(), dbias.data_ptr(), dg.data_ptr())
+            f = S.Fused(alpha, beta, drs.data_ptr(), dcs.data_ptr(), dbias.data_ptr(), dg.data_ptr(), act, act_param)
             skl.skl_gemm_fused_sm100a(m, n, k, ta, da.ptr(A.off), rsa, csa, tb, db.ptr(B.off), rsb, csb, C.byref(f), tc,
                                       dc.ptr(Cm.off), rsc, csc)
             S.check()
@@ -89,3 +89,82 @@ def test_float_pairs_with_bias_and_global_max(skl, pair, tc):
         tol = bound + ulp * np.abs(ref) + 1e-30
         assert np.all(np.abs(out - ref) <= tol)
         assert abs(gg - gw) <= float(np.max(bound)) + 2.0 ** -20 * abs(gw)
+
+
+# ---------------------------------------------------------------------------------------------- activations
+def ulp_error_f32(x, r):
+    """Distance between x and r in units of ulp(r): the measure of the reference's own activation tests
+    (test/skl-test-driver.h:568-581)."""
+    x, r = x.astype(np.float32), r.astype(np.float32)
+    same = (x == r) | (np.isnan(x) & np.isnan(r))
+    bad = np.isinf(r) | np.isnan(x) | np.isnan(r)
+    with np.errstate(invalid="ignore", over="ignore"):
+        d = np.abs(x - r).astype(np.float64)
+    _, e = np.frexp(r)
+    e = np.where((e < -125) | (r == 0), -125 - 24, e - 24)
+    err = np.ldexp(d, -e)
+    return np.where(same, 0.0, np.where(bad, np.inf, err))
+
+
+# bounds from the reference's tests of its own kernels: test/sigmoid/sigmoid_f32_zve32f.c:66-76 (logistic 3 ulp,
+# silu / swish / swiglu 52 ulp) and, for GELU by input class (v < -2, [-2,-1), [-1,0), >= 0), the bounds of its most
+# accurate variant in test/gelu/skl_gelu_f32_zve32f.c:44
+ACT_CASES = [("logistic", S.ACT_LOGISTIC, 1.0), ("silu", S.ACT_SWISH, 1.0), ("swish2", S.ACT_SWISH, 2.0),
+             ("gelu", S.ACT_GELU, 0.0), ("swiglu", S.ACT_SWIGLU, 0.5)]
+GELU_BOUNDS = [(-np.inf, -2.0, 1.7e7), (-2.0, -1.0, 62.0), (-1.0, 0.0, 5.0), (0.0, np.inf, 4.0)]
+
+
+@pytest.mark.parametrize("name,act,p", ACT_CASES)
+@pytest.mark.parametrize("m,n,k,expect", [(1, 1000, 512, S.PATH_GEMV), (16, 2000, 512, S.PATH_TCGEN05),
+                                          (257, 520, 256, S.PATH_TCGEN05), (33, 17, 48, S.PATH_GENERIC)])
+def test_activation_epilogue_within_reference_ulp_bounds(skl, name, act, p, m, n, k, expect):
+    """int8 operands: the value entering the activation is exact, so the whole difference to the oracle is the
+    activation's own fp32 evaluation.  alpha spreads the pre-activation values over about [-25, 25]."""
+    alpha = 8.0 / (5476.0 * np.sqrt(k) * 1e-2)
+    where = "host" if (act == S.ACT_SWIGLU and m == 257) else "device"
+    _, _, before, want, got, gw, gg, _, _ = run_case(skl, m, n, k, H.I8, H.I8, H.F32, "rkr", 0.0, where, 0, 7 * m + n,
+                                                     alpha=alpha, act=act, act_param=p)
+    assert skl.skl_b200_last_path() == expect
+    err = ulp_error_f32(got, want)
+    if act == S.ACT_GELU:
+        # recover the pre-activation value's class from the oracle without the activation
+        _, _, _, pre, _, _, _, _, _ = run_case(skl, m, n, k, H.I8, H.I8, H.F32, "rkr", 0.0, "device", 0, 7 * m + n,
+                                               alpha=alpha)
+        for lo, hi, bound in GELU_BOUNDS:
+            sel = (pre >= lo) & (pre < hi)
+            assert sel.sum() == 0 or err[sel].max() <= bound, (name, lo, hi, float(err[sel].max()))
+    else:
+        bound = 3.0 if act == S.ACT_LOGISTIC else 52.0
+        assert err.max() <= bound, (name, float(err.max()))
+    # the maximum is taken after the activation
+    assert ulp_error_f32(np.array([gg]), np.array([gw]))[0] <= 52.0
+
+
+@pytest.mark.parametrize("name,act,p", ACT_CASES)
+def test_activation_epilogue_bf16_output_and_float_operands(skl, name, act, p):
+    """bf16 x bf16 -> bf16 with an activation: within one bf16 ulp of the oracle plus the reference suite's
+    forward bound carried through the activation (all five have slope <= 1.13 in magnitude... times |up + delta|
+    for the gate)."""
+    m, n, k = 260, 384, 128
+    A, B, before, want, got, gw, gg, rs, cs = run_case(skl, m, n, k, H.BF16, H.BF16, H.BF16, "rrr", 0.0, "device", 0,
+                                                       31, alpha=40.0, act=act, act_param=p)
+    assert skl.skl_b200_last_path() == S.PATH_TCGEN05
+    ref = H.to_f32(H.BF16, want).astype(np.float64)
+    out = H.to_f32(H.BF16, got).astype(np.float64)
+    scale = np.abs(40.0 * rs[:, None].astype(np.float64) * cs[None, :].astype(np.float64))
+    bound = H.skl_forward_bound(H.BF16, A.get(), H.BF16, B.get(), 1.0, 0.0, None, k) * scale * 2
+    slope = 1.13 * (np.abs(H.to_f32(H.BF16, before.get()).astype(np.float64)).max() + 0.5 if act == S.ACT_SWIGLU else 1.0)
+    tol = bound * slope * (2.0 if act == S.ACT_SWISH and p == 2.0 else 1.0) + 2.0 ** -7 * np.abs(ref) + 1e-30
+    assert np.all(np.abs(out - ref) <= tol), float(np.max(np.abs(out - ref) - tol))
+
+
+def test_swiglu_with_beta_is_rejected(skl):
+    a = np.ones((4, 4), np.int8)
+    c = np.zeros((4, 4), np.float32)
+    f = S.Fused(1.0, 0.5, None, None, None, None, S.ACT_SWIGLU, 0.0)
+    skl.skl_gemm_fused_sm100a(4, 4, 4, S.I8, S.ptr(a), 4, 1, S.I8, S.ptr(a), 4, 1, C.byref(f), S.F32, S.ptr(c), 4, 1)
+    assert skl.skl_b200_last_status() == 1
+    f = S.Fused(1.0, 0.0, None, None, None, None, 9, 0.0)
+    skl.skl_gemm_fused_sm100a(4, 4, 4, S.I8, S.ptr(a), 4, 1, S.I8, S.ptr(a), 4, 1, C.byref(f), S.F32, S.ptr(c), 4, 1)
+    assert skl.skl_b200_last_status() == 1
+    assert np.all(c == 0)

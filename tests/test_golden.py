@@ -106,3 +106,18 @@ def test_pack_port_matches_reference_vectors(case):
     at = np.full(at_want.shape, 0xEE, dtype=at_want.dtype)
     lib.orc_transpose(e // 8, m, n, P(a), n + 2, P(at), m + 3)
     assert np.array_equal(at, at_want)
+
+
+ACTS = {"logistic": (orc.ACT_LOGISTIC, 1.0), "silu": (orc.ACT_SWISH, 1.0), "swish2": (orc.ACT_SWISH, 2.0),
+        "swiglu": (orc.ACT_SWIGLU, 0.5), "gelu": (orc.ACT_GELU, 0.0)}
+
+
+@pytest.mark.parametrize("name", sorted(ACTS))
+def test_activation_port_matches_reference_vectors(name):
+    """orc_activation against skl_sigmoid_f32_ref / skl_gelu_f32_ref outputs (both evaluate in double and
+    round once, so the results agree bit for bit)."""
+    act, p = ACTS[name]
+    fn = orc.port().orc_activation
+    x, up, want = GOLD[f"act_{name}_x"], GOLD[f"act_{name}_up"], GOLD[f"act_{name}_out"]
+    got = np.array([fn(act, p, float(v), float(u)) for v, u in zip(x, up)], dtype=np.float32)
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32)) or np.array_equal(got, want, equal_nan=True)

@@ -103,3 +103,33 @@ def test_pack_unpack_transpose(e):
         getattr(ref, f"skl_transpose_e{e}_ref")(m, n, P(a), n + 1, P(t0), m + 2)
         port.orc_transpose(e // 8, m, n, P(a), n + 1, P(t1), m + 2)
         assert np.array_equal(t0, t1)
+
+
+def test_fused_activation_equals_reference_elementwise_routine_on_the_gemm_result():
+    """orc_gemm_fused with an activation = the reference GEMM into fp32, then the reference's own element-wise
+    routine over the result (skl_sigmoid_f32_ref with its beta / y / up / delta arguments, skl_gelu_f32_ref)."""
+    ref = orc.ref()
+    if not hasattr(ref, "skl_sigmoid_f32_ref"):
+        pytest.skip("reference library built without the activation files")
+    g = H.rng(91)
+    m, n, k = 13, 21, 48
+    A = H.Strided(H.BF16, m, k, k, 1, g)
+    B = H.Strided(H.BF16, k, n, n, 1, g)
+    plain = np.zeros(m * n, np.float32)
+    orc.ref_gemm_rc(H.BF16, m, n, k, 4.0, A.view, k, 1, B.view, n, 1, 0.0, plain, n, 1)
+    up = g.normal(0, 2, m * n).astype(np.float32)
+    for act, p in ((orc.ACT_LOGISTIC, 1.0), (orc.ACT_LOGISTIC, 0.7), (orc.ACT_SWISH, 1.0), (orc.ACT_SWISH, 2.0),
+                   (orc.ACT_GELU, 0.0), (orc.ACT_SWIGLU, 0.5)):
+        want = np.zeros(m * n, np.float32)
+        if act == orc.ACT_LOGISTIC:
+            ref.skl_sigmoid_f32_ref(P(want), p, P(plain), None, None, 0.0, m * n)
+        elif act == orc.ACT_SWISH:
+            ref.skl_sigmoid_f32_ref(P(want), p, P(plain), P(plain), None, 0.0, m * n)
+        elif act == orc.ACT_SWIGLU:
+            ref.skl_sigmoid_f32_ref(P(want), 1.0, P(plain), P(plain), P(up), p, m * n)
+        else:
+            ref.skl_gelu_f32_ref(P(want), P(plain), m * n)
+        got = up.copy() if act == orc.ACT_SWIGLU else np.zeros(m * n, np.float32)
+        orc.port_gemm_fused(m, n, k, H.BF16, A.view, k, 1, H.BF16, B.view, n, 1, 4.0, None, None, None, None, 0.0,
+                            H.F32, got, n, 1, activation=act, act_param=p)
+        assert np.array_equal(got, want, equal_nan=True), (act, p)
