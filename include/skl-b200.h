@@ -212,7 +212,8 @@ SKL_FUNC void skl_gemm_f8e5m2rcprc_f8e5m2rcprc_f32rcprc_sm100a(
  *     v     = v * col_scale[j]          when col_scale != NULL   (n entries)
  *     v     = beta * (float)C[i,j] + v  when beta != 0
  *     C[i,j]= narrow(v)                 tc: F32 (none), BF16 / F16 (round to nearest even),
- *                                           F8E4M3 (SKL's saturating encoder, ref/cvt/cvt_ofp8.c:97-134)
+ *                                           F8E4M3 (SKL's saturating encoder, ref/cvt/cvt_ofp8.c:97-134),
+ *                                           I8 (requantised: nearest even, saturating to [-128, 127], NaN -> 0)
  *
  * every step one fp32 operation with its own rounding, in that order.
  * Operand pairs: I8 x I8; any two of {F8E4M3, F8E5M2}; BF16 x BF16; F16 x F16; and BF16 x F8E4M3 /

@@ -334,6 +334,9 @@ void orc_gemm_packed_fp_f32(size_t m0, size_t n0, size_t k0, size_t m1, size_t n
 
 /* ------------------------------------------------------------------ extended epilogue */
 static inline float load_c(int tc, const void *c, size_t idx) {
+  if (tc == ORC_I8) {
+    return (float)((const int8_t *)c)[idx];
+  }
   if (tc == ORC_F8E4M3) {
     return orc_f8e4m3_to_f32(((const uint8_t *)c)[idx]);
   }
@@ -351,6 +354,12 @@ static inline void store_c(int tc, void *c, size_t idx, float v) {
   case ORC_F8E4M3:
     ((uint8_t *)c)[idx] = orc_f32_to_f8e4m3(v, 1);
     break;
+  case ORC_I8: { /* requantised output: nearest even, saturating, NaN -> 0 (no reference routine) */
+    float r = nearbyintf(v);
+    int q = isnan(v) ? 0 : (r < -128.0f ? -128 : (r > 127.0f ? 127 : (int)r));
+    ((int8_t *)c)[idx] = (int8_t)q;
+    break;
+  }
   default:
     ((float *)c)[idx] = v;
     break;

@@ -89,7 +89,8 @@ void orc_gemm_packed_fp_f32(size_t m0, size_t n0, size_t k0, size_t m1, size_t n
  * rounding per operation and no fused multiply-add:
  *     v = (float)acc;  v = alpha*v;  if row_scale: v = v*row_scale[i];  if col_scale: v = v*col_scale[j];
  *     if beta != 0:    v = beta*(float)C[i,j] + v;
- *     C[i,j] = narrow(v)   tc in {ORC_F32, ORC_BF16 (RNE), ORC_F16 (RNE), ORC_F8E4M3 (saturating)}.
+ *     C[i,j] = narrow(v)   tc in {ORC_F32, ORC_BF16 (RNE), ORC_F16 (RNE), ORC_F8E4M3 (saturating),
+ *                                 ORC_I8 (requantised: nearest even, saturating to [-128,127], NaN -> 0)}.
  * ta/tb may be ORC_I8 (both), or any float pair. */
 void orc_gemm_ex(size_t m, size_t n, size_t k, int ta, const void *a, size_t rsa, size_t csa, int tb,
                  const void *b, size_t rsb, size_t csb, float alpha, const float *row_scale,

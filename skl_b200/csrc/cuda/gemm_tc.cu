@@ -461,6 +461,15 @@ __device__ __forceinline__ float epilogue_chunk(const TcParams &p, const uint32_
       uint4 *dst = reinterpret_cast<uint4 *>((uint16_t *)p.c + base);
 #pragma unroll
       for (int q = 0; q < 4; ++q) dst[q] = make_uint4(w[4 * q], w[4 * q + 1], w[4 * q + 2], w[4 * q + 3]);
+    } else if (p.tc == SKL_DT_I8) {  // requantised: round to nearest even, saturating
+      uint32_t w[8];
+#pragma unroll
+      for (int q = 0; q < 8; ++q)
+        w[q] = enc_i8_sat(v[4 * q]) | (enc_i8_sat(v[4 * q + 1]) << 8) | (enc_i8_sat(v[4 * q + 2]) << 16) |
+               (enc_i8_sat(v[4 * q + 3]) << 24);
+      uint4 *dst = reinterpret_cast<uint4 *>((uint8_t *)p.c + base);
+      dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
+      dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
     } else {  // F8E4M3, saturating
       uint32_t w[8];
 #pragma unroll
@@ -1123,7 +1132,9 @@ extern "C" int skl_b200_gemm_tc_supported(const skl_b200_gemm_args *g) {
   if (g->epilogue == SKL_EPI_INT) {
     if (kind != KIND_I8 || g->tc != SKL_DT_I32) return 0;
   } else {
-    if (!(g->tc == SKL_DT_F32 || g->tc == SKL_DT_BF16 || g->tc == SKL_DT_F16 || g->tc == SKL_DT_F8E4M3)) return 0;
+    if (!(g->tc == SKL_DT_F32 || g->tc == SKL_DT_BF16 || g->tc == SKL_DT_F16 || g->tc == SKL_DT_F8E4M3 ||
+          g->tc == SKL_DT_I8))
+      return 0;
   }
   if (encode_fn() == nullptr) return 0;
   return 1;

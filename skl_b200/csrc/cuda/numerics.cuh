@@ -205,8 +205,15 @@ __device__ __forceinline__ float load_as_f32(int dt, const void *p, int64_t idx)
 }
 
 // Read / write one C element of the float epilogue.
+// Requantised int8 output: round to nearest even, saturate to [-128, 127], NaN -> 0.
+__device__ __forceinline__ uint32_t enc_i8_sat(float v) {
+  int32_t r;
+  asm("cvt.rni.sat.s8.f32 %0, %1;" : "=r"(r) : "f"(v));
+  return (uint32_t)r & 0xFFu;
+}
 __device__ __forceinline__ float load_c_f32(int tc, const void *c, int64_t idx) {
   if (tc == SKL_DT_I32) return (float)((const int32_t *)c)[idx];
+  if (tc == SKL_DT_I8) return (float)((const int8_t *)c)[idx];
   return load_as_f32(tc, c, idx);
 }
 __device__ __forceinline__ void store_c_f32(int tc, void *c, int64_t idx, float v) {
@@ -219,6 +226,9 @@ __device__ __forceinline__ void store_c_f32(int tc, void *c, int64_t idx, float 
       break;
     case SKL_DT_F8E4M3:
       ((uint8_t *)c)[idx] = (uint8_t)enc_e4m3(v, true);
+      break;
+    case SKL_DT_I8:
+      ((uint8_t *)c)[idx] = (uint8_t)enc_i8_sat(v);
       break;
     default:
       ((float *)c)[idx] = v;

@@ -761,7 +761,8 @@ void skl_gemm_fused_sm100a(size_t m, size_t n, size_t k, skl_b200_dtype_t ta, co
   int pair_ok = (ta == SKL_B200_I8 && tb == SKL_B200_I8) || (is_f8(ta) && is_f8(tb)) ||
                 (ta == SKL_B200_BF16 && tb == SKL_B200_BF16) || (ta == SKL_B200_F16 && tb == SKL_B200_F16) ||
                 (ta == SKL_B200_BF16 && is_f8(tb));
-  int out_ok = tc == SKL_B200_F32 || tc == SKL_B200_BF16 || tc == SKL_B200_F16 || tc == SKL_B200_F8E4M3;
+  int out_ok = tc == SKL_B200_F32 || tc == SKL_B200_BF16 || tc == SKL_B200_F16 || tc == SKL_B200_F8E4M3 ||
+               tc == SKL_B200_I8;
   if (!pair_ok || !out_ok) {
     g_ctx.status = SKL_B200_ERR_UNSUPPORTED;
     g_ctx.cuda_err[0] = 0;

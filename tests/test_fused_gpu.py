@@ -168,3 +168,31 @@ def test_swiglu_with_beta_is_rejected(skl):
     skl.skl_gemm_fused_sm100a(4, 4, 4, S.I8, S.ptr(a), 4, 1, S.I8, S.ptr(a), 4, 1, C.byref(f), S.F32, S.ptr(c), 4, 1)
     assert skl.skl_b200_last_status() == 1
     assert np.all(c == 0)
+
+
+# ---------------------------------------------------------------------------------------------- requantised output
+@pytest.mark.parametrize("m,n,k,expect", [(1, 1000, 512, S.PATH_GEMV), (16, 2000, 512, S.PATH_TCGEN05),
+                                          (257, 520, 256, S.PATH_TCGEN05), (33, 17, 48, S.PATH_GENERIC)])
+@pytest.mark.parametrize("beta", [0.0, 0.5])
+def test_int8_output_is_exact_for_int8_operands(skl, m, n, k, expect, beta):
+    """Requantisation to int8 (nearest even, saturating): exact accumulator, so the codes must equal the oracle's.
+    alpha spreads the values over about [-250, 250] so that both rounding and saturation occur."""
+    alpha = 80.0 / (5476.0 * np.sqrt(k) * 1e-2)
+    for where in ("device", "host"):
+        _, _, _, want, got, gw, gg, _, _ = run_case(skl, m, n, k, H.I8, H.I8, H.I8, "rkr", beta, where, 0, 3 * m + n,
+                                                    alpha=alpha)
+        assert skl.skl_b200_last_path() == expect
+        assert np.array_equal(got, want)
+        assert (want == 127).any() and (want == -128).any() and (np.abs(want.astype(np.int32)) < 100).any()
+        assert gg == gw  # the maximum is taken before the narrowing
+
+
+def test_int8_output_from_float_operands(skl):
+    """bf16 x bf16 -> int8: the accumulator differs from the oracle's by at most the reference suite's forward
+    bound, which can move a value across a rounding boundary, so codes may differ by one step there."""
+    m, n, k = 260, 384, 128
+    A, B, _, want, got, _, _, rs, cs = run_case(skl, m, n, k, H.BF16, H.BF16, H.I8, "rrr", 0.0, "device", 0, 5, alpha=900.0)
+    assert skl.skl_b200_last_path() == S.PATH_TCGEN05
+    diff = np.abs(got.astype(np.int32) - want.astype(np.int32))
+    assert diff.max() <= 1 and (diff != 0).mean() < 0.01
+    assert np.unique(want).size > 100
