@@ -57,6 +57,7 @@ struct TcParams {
   int64_t rsc, csc;
   int tc, epilogue;
   int c_vec_ok;  // csc == 1 and rows 16-byte aligned
+  int c_tma;     // C has a tensor map: results leave through shared memory and TMA stores
   int32_t alpha_i, beta_i;
   float alpha_f, beta_f;
   const float *row_scale, *col_scale;
@@ -300,6 +301,56 @@ __device__ __forceinline__ void umma_commit_pair_both(uint32_t bar) {
                : "memory");
 }
 
+// ---- results through shared memory and TMA stores
+// Each epilogue warp owns EPI_STAGE_BYTES of staging.  A 32-row x 32-column chunk is written there one row per
+// lane in the tensor map's swizzled order (the 16-byte piece index XORed with address bits 7 and up, so the 32
+// lanes' pieces spread over all banks), then one lane hands the box to the TMA engine, which writes whole rows
+// of the box to global memory and clips at the matrix edge.  Narrow element types fit 2 or 4 boxes in the
+// staging area and rotate through them, so a store only waits for the one issued that many chunks earlier.
+constexpr int EPI_STAGE_BYTES = 4096;
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap *tm, uint32_t src, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(tm), "r"(src),
+               "r"(x), "r"(y)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void bulk_wait_read() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
+struct EpiStage {
+  const CUtensorMap *tm;  // nullptr: direct stores
+  uint32_t base;          // this warp's staging area (shared-memory address, 1024-byte aligned)
+  uint32_t count;         // chunks stored so far
+};
+
+// w: the lane's row of the chunk, 32 elements of ES bytes packed into 8 * ES words.
+template <int ES>
+__device__ __forceinline__ void tma_store_chunk(EpiStage &st, int lane, const uint32_t *w, int x, int y) {
+  constexpr int NBUF = 4 / ES;
+  constexpr int PITCH = 32 * ES;      // bytes per staged row: 128 / 64 / 32 = the map's swizzle span
+  constexpr int PIECES = PITCH / 16;  // 16-byte pieces per row
+  const uint32_t buf = st.base + (st.count % NBUF) * (32 * PITCH);
+  if (lane == 0) bulk_wait_read<NBUF - 1>();
+  __syncwarp();
+  const uint32_t rowoff = (uint32_t)lane * PITCH;
+  const uint32_t sw = (rowoff >> 7) & (PIECES - 1);
+#pragma unroll
+  for (int q = 0; q < PIECES; ++q)
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(buf + rowoff + 16u * ((uint32_t)q ^ sw)),
+                 "r"(w[4 * q]), "r"(w[4 * q + 1]), "r"(w[4 * q + 2]), "r"(w[4 * q + 3])
+                 : "memory");
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  __syncwarp();
+  if (lane == 0) {
+    tma_store_2d(st.tm, buf, x, y);
+    bulk_commit();
+  }
+  ++st.count;
+}
+
 // Per-warp shared-memory copies of the tile's column scales and column bias.  Each epilogue warp fills
 // its own copy before it waits for the accumulator, so the global loads hide behind the main loop and
 // the per-element reads are shared-memory broadcasts; only __syncwarp orders them.  Columns past N (and,
@@ -334,38 +385,55 @@ struct TcConfig {
   static constexpr int STAGES_RAW = (220 * 1024) / STAGE_BYTES;
   static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
   static constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/ + EpiVectors<BN>::BYTES;
+  static constexpr int SMEM_BYTES =
+      STAGES * STAGE_BYTES + 1024 /*align*/ + 4 * EPI_STAGE_BYTES + 256 /*barriers*/ + EpiVectors<BN>::BYTES;
+  static_assert(SMEM_BYTES <= 227 * 1024, "exceeds the shared memory one CTA can have");
 };
 
 // ------------------------------------------------------------------ epilogue for 32 accumulator columns
+// Called by every lane of an epilogue warp (lane = row of the 32-row box; `row_ok` says whether that row exists).
 // Returns the largest value written (for the optional global maximum); -INFINITY for the int epilogue.
 template <bool ACC_INT, bool ACT>
-__device__ __forceinline__ float epilogue_chunk(const TcParams &p, const uint32_t (&r)[32], int row, int col0,
-                                                const float *cs, const float *bs, float rs, float row_bias) {
+__device__ __forceinline__ float epilogue_chunk(const TcParams &p, const uint32_t (&r)[32], int row, bool row_ok,
+                                                int col0, const float *cs, const float *bs, float rs,
+                                                float row_bias, EpiStage &st, int lane) {
   const int ncols = (p.N - col0) < 32 ? (p.N - col0) : 32;
+  const int64_t base = (int64_t)row * p.rsc + (int64_t)col0 * p.csc;
   if (p.epilogue == SKL_EPI_INT) {
-    int32_t *crow = (int32_t *)p.c + (int64_t)row * p.rsc + (int64_t)col0 * p.csc;
-    if (p.c_vec_ok && ncols == 32) {
-      uint4 *dst = reinterpret_cast<uint4 *>(crow);
+    uint32_t o[32];
+    if (p.beta_i != 0 && row_ok) {
+      const int32_t *crow = (const int32_t *)p.c + base;
+      if (p.c_vec_ok && ncols == 32) {
+        const uint4 *src = reinterpret_cast<const uint4 *>(crow);
 #pragma unroll
-      for (int v = 0; v < 8; ++v) {
-        uint32_t o[4];
-        uint4 old = make_uint4(0, 0, 0, 0);
-        if (p.beta_i != 0) old = dst[v];
-        const uint32_t oldv[4] = {old.x, old.y, old.z, old.w};
+        for (int q = 0; q < 8; ++q) {
+          const uint4 old = src[q];
+          o[4 * q] = (uint32_t)p.beta_i * old.x + (uint32_t)p.alpha_i * r[4 * q];
+          o[4 * q + 1] = (uint32_t)p.beta_i * old.y + (uint32_t)p.alpha_i * r[4 * q + 1];
+          o[4 * q + 2] = (uint32_t)p.beta_i * old.z + (uint32_t)p.alpha_i * r[4 * q + 2];
+          o[4 * q + 3] = (uint32_t)p.beta_i * old.w + (uint32_t)p.alpha_i * r[4 * q + 3];
+        }
+      } else {
 #pragma unroll
-        for (int e = 0; e < 4; ++e)
-          o[e] = (uint32_t)p.beta_i * oldv[e] + (uint32_t)p.alpha_i * r[v * 4 + e];
-        dst[v] = make_uint4(o[0], o[1], o[2], o[3]);
+        for (int e = 0; e < 32; ++e)
+          o[e] = (e < ncols ? (uint32_t)p.beta_i * (uint32_t)crow[(int64_t)e * p.csc] : 0u) + (uint32_t)p.alpha_i * r[e];
       }
     } else {
 #pragma unroll
-      for (int e = 0; e < 32; ++e) {
-        if (e < ncols) {
-          int32_t *cp = crow + (int64_t)e * p.csc;
-          uint32_t old = p.beta_i != 0 ? (uint32_t)p.beta_i * (uint32_t)*cp : 0u;
-          *cp = (int32_t)(old + (uint32_t)p.alpha_i * r[e]);
-        }
+      for (int e = 0; e < 32; ++e) o[e] = (uint32_t)p.alpha_i * r[e];
+    }
+    if (st.tm) {
+      tma_store_chunk<4>(st, lane, o, col0, row - lane);
+    } else if (row_ok) {
+      int32_t *crow = (int32_t *)p.c + base;
+      if (p.c_vec_ok && ncols == 32) {
+        uint4 *dst = reinterpret_cast<uint4 *>(crow);
+#pragma unroll
+        for (int q = 0; q < 8; ++q) dst[q] = make_uint4(o[4 * q], o[4 * q + 1], o[4 * q + 2], o[4 * q + 3]);
+      } else {
+#pragma unroll
+        for (int e = 0; e < 32; ++e)
+          if (e < ncols) crow[(int64_t)e * p.csc] = (int32_t)o[e];
       }
     }
     return -INFINITY;
@@ -412,8 +480,7 @@ __device__ __forceinline__ float epilogue_chunk(const TcParams &p, const uint32_
 #pragma unroll
     for (int e = 0; e < 32; ++e) v[e] = __fadd_rn(v[e], row_bias);
   }
-  const int64_t base = (int64_t)row * p.rsc + (int64_t)col0 * p.csc;
-  if (p.beta_f != 0.0f) {
+  if (p.beta_f != 0.0f && row_ok) {
 #pragma unroll
     for (int e = 0; e < 32; ++e)
       if (e < ncols)
@@ -421,10 +488,13 @@ __device__ __forceinline__ float epilogue_chunk(const TcParams &p, const uint32_
   }
   if (ACT && p.activation) {
     if (p.activation == SKL_ACT_SWIGLU) {
+      if (row_ok) {
 #pragma unroll
-      for (int e = 0; e < 32; ++e)
-        if (e < ncols)
-          v[e] = activation_value(SKL_ACT_SWIGLU, p.act_param, v[e], load_c_f32(p.tc, p.c, base + (int64_t)e * p.csc));
+        for (int e = 0; e < 32; ++e)
+          if (e < ncols)
+            v[e] =
+                activation_value(SKL_ACT_SWIGLU, p.act_param, v[e], load_c_f32(p.tc, p.c, base + (int64_t)e * p.csc));
+      }
     } else if (p.activation == SKL_ACT_GELU) {
 #pragma unroll
       for (int e = 0; e < 32; ++e) v[e] = gelu_f32(v[e]);
@@ -438,48 +508,70 @@ __device__ __forceinline__ float epilogue_chunk(const TcParams &p, const uint32_
     }
   }
   float vmax = -INFINITY;
-  if (p.global_max) {
+  if (p.global_max && row_ok) {
 #pragma unroll
     for (int e = 0; e < 32; ++e)
       if (e < ncols && v[e] == v[e]) vmax = fmaxf(vmax, v[e]);
   }
-  if (p.c_vec_ok && ncols == 32) {
+  const bool vec = st.tm != nullptr || (p.c_vec_ok && ncols == 32);
+  if (vec) {
+    // narrow and pack the row, then either hand it to the TMA store or write it as 16-byte pieces
+    uint32_t w[32];
+    int words;
     if (p.tc == SKL_DT_F32) {
-      uint4 *dst = reinterpret_cast<uint4 *>((float *)p.c + base);
+      words = 32;
 #pragma unroll
-      for (int q = 0; q < 8; ++q)
-        dst[q] = make_uint4(__float_as_uint(v[4 * q]), __float_as_uint(v[4 * q + 1]),
-                            __float_as_uint(v[4 * q + 2]), __float_as_uint(v[4 * q + 3]));
+      for (int e = 0; e < 32; ++e) w[e] = __float_as_uint(v[e]);
     } else if (p.tc == SKL_DT_BF16 || p.tc == SKL_DT_F16) {
-      uint32_t w[16];
+      words = 16;
+      // A NaN anywhere in the row makes the sum NaN (so does inf - inf, which only costs the slow path): the
+      // hardware converter handles everything else, the bit-exact NaN encoding is kept for the rare row.
+      float t[8];
 #pragma unroll
-      for (int q = 0; q < 16; ++q) {
-        uint32_t lo = p.tc == SKL_DT_BF16 ? enc_bf16(v[2 * q]) : enc_f16(v[2 * q]);
-        uint32_t hi = p.tc == SKL_DT_BF16 ? enc_bf16(v[2 * q + 1]) : enc_f16(v[2 * q + 1]);
-        w[q] = lo | (hi << 16);
+      for (int q = 0; q < 8; ++q) t[q] = (v[4 * q] + v[4 * q + 1]) + (v[4 * q + 2] + v[4 * q + 3]);
+      const float total = ((t[0] + t[1]) + (t[2] + t[3])) + ((t[4] + t[5]) + (t[6] + t[7]));
+      if (total == total) {
+        if (p.tc == SKL_DT_BF16) {
+#pragma unroll
+          for (int q = 0; q < 16; ++q) w[q] = pack_bf16x2_no_nan(v[2 * q], v[2 * q + 1]);
+        } else {
+#pragma unroll
+          for (int q = 0; q < 16; ++q) w[q] = pack_f16x2_no_nan(v[2 * q], v[2 * q + 1]);
+        }
+      } else {
+#pragma unroll
+        for (int q = 0; q < 16; ++q) {
+          uint32_t lo = p.tc == SKL_DT_BF16 ? enc_bf16(v[2 * q]) : enc_f16(v[2 * q]);
+          uint32_t hi = p.tc == SKL_DT_BF16 ? enc_bf16(v[2 * q + 1]) : enc_f16(v[2 * q + 1]);
+          w[q] = lo | (hi << 16);
+        }
       }
-      uint4 *dst = reinterpret_cast<uint4 *>((uint16_t *)p.c + base);
-#pragma unroll
-      for (int q = 0; q < 4; ++q) dst[q] = make_uint4(w[4 * q], w[4 * q + 1], w[4 * q + 2], w[4 * q + 3]);
     } else if (p.tc == SKL_DT_I8) {  // requantised: round to nearest even, saturating
-      uint32_t w[8];
+      words = 8;
 #pragma unroll
       for (int q = 0; q < 8; ++q)
         w[q] = enc_i8_sat(v[4 * q]) | (enc_i8_sat(v[4 * q + 1]) << 8) | (enc_i8_sat(v[4 * q + 2]) << 16) |
                (enc_i8_sat(v[4 * q + 3]) << 24);
-      uint4 *dst = reinterpret_cast<uint4 *>((uint8_t *)p.c + base);
-      dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
-      dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
     } else {  // F8E4M3, saturating
-      uint32_t w[8];
+      words = 8;
 #pragma unroll
       for (int q = 0; q < 8; ++q)
         w[q] = enc_e4m3x2(v[4 * q], v[4 * q + 1], true) | (enc_e4m3x2(v[4 * q + 2], v[4 * q + 3], true) << 16);
-      uint4 *dst = reinterpret_cast<uint4 *>((uint8_t *)p.c + base);
-      dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
-      dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
     }
-  } else {
+    if (st.tm) {
+      if (words == 32)
+        tma_store_chunk<4>(st, lane, w, col0, row - lane);
+      else if (words == 16)
+        tma_store_chunk<2>(st, lane, w, col0, row - lane);
+      else
+        tma_store_chunk<1>(st, lane, w, col0, row - lane);
+    } else if (row_ok) {
+      uint4 *dst = reinterpret_cast<uint4 *>((uint8_t *)p.c + base * (words / 8));
+#pragma unroll
+      for (int q = 0; q < 8; ++q)
+        if (4 * q < words) dst[q] = make_uint4(w[4 * q], w[4 * q + 1], w[4 * q + 2], w[4 * q + 3]);
+    }
+  } else if (row_ok) {
 #pragma unroll
     for (int e = 0; e < 32; ++e)
       if (e < ncols) store_c_f32(p.tc, p.c, base + (int64_t)e * p.csc, v[e]);
@@ -491,7 +583,7 @@ __device__ __forceinline__ float epilogue_chunk(const TcParams &p, const uint32_
 template <int BN, int KIND, bool ACT>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
     gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                   const TcParams p) {
+                   const __grid_constant__ CUtensorMap tmC, const TcParams p) {
   using Cfg = TcConfig<BN>;
   constexpr int ES = (KIND == KIND_F16) ? 2 : 1;   // operand element size
   constexpr int BKE = SLAB_BYTES / ES;             // k elements per stage
@@ -505,7 +597,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t tiles = (raw + 1023u) & ~1023u;   // stage ring, 1024-byte aligned
-  const uint32_t bars = tiles + Cfg::STAGES * Cfg::STAGE_BYTES;
+  const uint32_t epi_stage = tiles + Cfg::STAGES * Cfg::STAGE_BYTES;  // 4 warps x EPI_STAGE_BYTES
+  const uint32_t bars = epi_stage + 4 * EPI_STAGE_BYTES;
   // barrier block: full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2], then tmem base + abort flag
   const uint32_t full_bar = bars, empty_bar = bars + 8 * Cfg::STAGES;
   const uint32_t tfull_bar = bars + 16 * Cfg::STAGES, tempty_bar = tfull_bar + 16;
@@ -626,6 +719,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
     float tile_max = -INFINITY;  // running maximum of this thread's results (optional global maximum)
     float *cs = EpiVectors<BN>::scale(bar_gen + 256, quad), *bs = EpiVectors<BN>::bias(bar_gen + 256, quad);
     const bool has_cs = p.col_scale != nullptr, has_bs = p.bias != nullptr && !p.bias_per_row;
+    EpiStage st = {p.c_tma ? &tmC : nullptr, epi_stage + (uint32_t)quad * EPI_STAGE_BYTES, 0u};
     TileUnit u;
     for (int it = 0; get_unit<BN>(p, it, u); ++it) {
       const int m0 = u.m0, n0 = u.n0;
@@ -644,9 +738,9 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
           tmem_ld32(taddr + c0, r);
         else
           tmem_ld16(taddr + c0, r);
-        if (row < p.M)
-          tile_max = fmaxf(tile_max, epilogue_chunk<KIND == KIND_I8, ACT>(p, r, row, n0 + c0, has_cs ? cs + c0 : nullptr,
-                                                                     has_bs ? bs + c0 : nullptr, rs, row_bias));
+        tile_max = fmaxf(tile_max, epilogue_chunk<KIND == KIND_I8, ACT>(p, r, row, row < p.M, n0 + c0,
+                                                                        has_cs ? cs + c0 : nullptr,
+                                                                        has_bs ? bs + c0 : nullptr, rs, row_bias, st, lane));
       }
       tc_fence_before();
       mbar_arrive(tempty_bar + 8 * acc);
@@ -657,6 +751,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
       tile_max = warp_max_f32(tile_max);
       if (lane == 0 && tile_max != -INFINITY) atomic_max_f32(p.global_max, tile_max);
     }
+    if (st.tm && lane == 0) bulk_wait_all();  // the staging memory must outlive the stores that read it
   }
 
   tc_fence_before();
@@ -692,13 +787,14 @@ struct Tc2Config {
   static constexpr int STAGES_RAW = (220 * 1024) / STAGE_BYTES;
   static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
   static constexpr int TMEM_COLS = 2 * BN;
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256 + EpiVectors<BN>::BYTES;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 4 * EPI_STAGE_BYTES + 256 + EpiVectors<BN>::BYTES;
+  static_assert(SMEM_BYTES <= 227 * 1024, "exceeds the shared memory one CTA can have");
 };
 
 template <int BN, int KIND, bool ACT>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
     gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                    const TcParams p) {
+                    const __grid_constant__ CUtensorMap tmC, const TcParams p) {
   using Cfg = Tc2Config<BN>;
   constexpr int ES = (KIND == KIND_F16) ? 2 : 1;
   constexpr int BKE = SLAB_BYTES / ES;
@@ -712,7 +808,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t tiles = (raw + 1023u) & ~1023u;
-  const uint32_t bars = tiles + Cfg::STAGES * Cfg::STAGE_BYTES;
+  const uint32_t epi_stage = tiles + Cfg::STAGES * Cfg::STAGE_BYTES;  // 4 warps x EPI_STAGE_BYTES
+  const uint32_t bars = epi_stage + 4 * EPI_STAGE_BYTES;
   const uint32_t full_bar = bars, empty_bar = bars + 8 * Cfg::STAGES;
   const uint32_t tfull_bar = bars + 16 * Cfg::STAGES, tempty_bar = tfull_bar + 16;
   uint8_t *bar_gen = smem_raw + (bars - raw);
@@ -838,6 +935,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
     const uint32_t leader_tempty = mapa(tempty_bar, 0);
     float *cs = EpiVectors<BN>::scale(bar_gen + 256, quad), *bs = EpiVectors<BN>::bias(bar_gen + 256, quad);
     const bool has_cs = p.col_scale != nullptr, has_bs = p.bias != nullptr && !p.bias_per_row;
+    EpiStage st = {p.c_tma ? &tmC : nullptr, epi_stage + (uint32_t)quad * EPI_STAGE_BYTES, 0u};
     for (int t = pair; t < num_tiles; t += num_pairs) {
       int mi, ni;
       tile_coords(t, p.tiles_m, p.tiles_n, p.raster_gm, mi, ni);
@@ -854,9 +952,9 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         if (n0 + c0 >= p.N) break;
         uint32_t r[32];
         tmem_ld32(taddr + c0, r);
-        if (row < p.M)
-          tile_max = fmaxf(tile_max, epilogue_chunk<KIND == KIND_I8, ACT>(p, r, row, n0 + c0, has_cs ? cs + c0 : nullptr,
-                                                                     has_bs ? bs + c0 : nullptr, rs, row_bias));
+        tile_max = fmaxf(tile_max, epilogue_chunk<KIND == KIND_I8, ACT>(p, r, row, row < p.M, n0 + c0,
+                                                                        has_cs ? cs + c0 : nullptr,
+                                                                        has_bs ? bs + c0 : nullptr, rs, row_bias, st, lane));
       }
       tc_fence_before();
       mbar_arrive_cluster(leader_tempty + 8 * acc);
@@ -867,6 +965,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
       tile_max = warp_max_f32(tile_max);
       if (lane == 0 && tile_max != -INFINITY) atomic_max_f32(p.global_max, tile_max);
     }
+    if (st.tm && lane == 0) bulk_wait_all();  // the staging memory must outlive the stores that read it
   }
 
   tc_fence_before();
@@ -965,6 +1064,26 @@ bool make_map(CUtensorMap *tm, int kind, int dt, const void *base, const Operand
   return r == CUDA_SUCCESS;
 }
 
+// Tensor map of C for the epilogue's stores: boxes of 32 rows x 32 columns, swizzled over the box's row bytes
+// (128 / 64 / 32 for 4- / 2- / 1-byte elements) to match tma_store_chunk's staging order.
+bool make_c_map(CUtensorMap *tm, void *base, int64_t M, int64_t N, int64_t ld, int es) {
+  EncodeTiledFn enc = encode_fn();
+  if (!enc) return false;
+  cuuint64_t dims[2] = {(cuuint64_t)N, (cuuint64_t)M}, strides[1];
+  cuuint32_t box[2] = {32, 32}, estr[2] = {1, 1};
+  if (M <= 1) ld = (int64_t)((N * es + 15) / 16 * 16) / es;  // stride unused; keep it legal
+  strides[0] = (cuuint64_t)ld * es;
+  const CUtensorMapDataType cdt = es == 4   ? CU_TENSOR_MAP_DATA_TYPE_UINT32
+                                  : es == 2 ? CU_TENSOR_MAP_DATA_TYPE_UINT16
+                                            : CU_TENSOR_MAP_DATA_TYPE_UINT8;
+  const CUtensorMapSwizzle sw = es == 4   ? CU_TENSOR_MAP_SWIZZLE_128B
+                                : es == 2 ? CU_TENSOR_MAP_SWIZZLE_64B
+                                          : CU_TENSOR_MAP_SWIZZLE_32B;
+  CUresult r = enc(tm, cdt, 2, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
+                   CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
 uint32_t fmt_code(int kind, int dt) {
   if (kind == KIND_F16) return dt == SKL_DT_BF16 ? 1u : 0u;
   if (kind == KIND_I8) return 1u;  // signed 8-bit
@@ -1011,7 +1130,8 @@ int pick_bn(int64_t M, int64_t N, int kind, bool b_mn_major) {
 }
 
 template <int BN, int KIND, bool ACT>
-int launch_cfg_act(const CUtensorMap &ta, const CUtensorMap &tb, const TcParams &p, cudaStream_t s) {
+int launch_cfg_act(const CUtensorMap &ta, const CUtensorMap &tb, const CUtensorMap &tc, const TcParams &p,
+                   cudaStream_t s) {
   using Cfg = TcConfig<BN>;
   static bool attr_set[64] = {};  // per device: function attributes do not carry over between devices
   const int dev = current_device();
@@ -1023,19 +1143,22 @@ int launch_cfg_act(const CUtensorMap &ta, const CUtensorMap &tb, const TcParams 
   }
   int grid = p.tiles_m * p.tiles_n;
   if (grid > sm_count()) grid = sm_count();
-  gemm_tc_kernel<BN, KIND, ACT><<<grid, NUM_THREADS, Cfg::SMEM_BYTES, s>>>(ta, tb, p);
+  gemm_tc_kernel<BN, KIND, ACT><<<grid, NUM_THREADS, Cfg::SMEM_BYTES, s>>>(ta, tb, tc, p);
   SKLB_COUNT_LAUNCH();
   return (int)cudaGetLastError();
 }
 
 // The activation code lives in instantiations of its own so that the plain epilogue carries none of it.
 template <int BN, int KIND>
-int launch_cfg(const CUtensorMap &ta, const CUtensorMap &tb, const TcParams &p, cudaStream_t s) {
-  return p.activation ? launch_cfg_act<BN, KIND, true>(ta, tb, p, s) : launch_cfg_act<BN, KIND, false>(ta, tb, p, s);
+int launch_cfg(const CUtensorMap &ta, const CUtensorMap &tb, const CUtensorMap &tc, const TcParams &p,
+               cudaStream_t s) {
+  return p.activation ? launch_cfg_act<BN, KIND, true>(ta, tb, tc, p, s)
+                      : launch_cfg_act<BN, KIND, false>(ta, tb, tc, p, s);
 }
 
 template <int BN, int KIND, bool ACT>
-int launch_cfg2_act(const CUtensorMap &ta, const CUtensorMap &tb, const TcParams &p, cudaStream_t s) {
+int launch_cfg2_act(const CUtensorMap &ta, const CUtensorMap &tb, const CUtensorMap &tc, const TcParams &p,
+                    cudaStream_t s) {
   using Cfg = Tc2Config<BN>;
   static int max_pairs_dev[64];
   static bool pairs_known[64] = {};
@@ -1081,15 +1204,17 @@ int launch_cfg2_act(const CUtensorMap &ta, const CUtensorMap &tb, const TcParams
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc2_kernel<BN, KIND, ACT>, ta, tb, p);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc2_kernel<BN, KIND, ACT>, ta, tb, tc, p);
   SKLB_COUNT_LAUNCH();
   if (e != cudaSuccess) return (int)e;
   return (int)cudaGetLastError();
 }
 
 template <int BN, int KIND>
-int launch_cfg2(const CUtensorMap &ta, const CUtensorMap &tb, const TcParams &p, cudaStream_t s) {
-  return p.activation ? launch_cfg2_act<BN, KIND, true>(ta, tb, p, s) : launch_cfg2_act<BN, KIND, false>(ta, tb, p, s);
+int launch_cfg2(const CUtensorMap &ta, const CUtensorMap &tb, const CUtensorMap &tc, const TcParams &p,
+                cudaStream_t s) {
+  return p.activation ? launch_cfg2_act<BN, KIND, true>(ta, tb, tc, p, s)
+                      : launch_cfg2_act<BN, KIND, false>(ta, tb, tc, p, s);
 }
 
 // 0 = never, 1 = when the heuristic says so (default), 2 = whenever the layout allows it
@@ -1210,6 +1335,17 @@ extern "C" int skl_b200_launch_gemm_tc(const skl_b200_gemm_args *g, uint32_t *de
                 (M <= 1 || ((g->rsc0 * cs) & 15) == 0))
                    ? 1
                    : 0;
+  // Results leave through TMA stores when C is a plain row-major matrix with 16-byte-aligned rows; any other C
+  // (column-major, strided columns, unaligned) is written with direct stores.  SKL_B200_TC_TMA_STORE=0 disables.
+  CUtensorMap tmC = tmA;  // a valid map in either case; unused unless c_tma
+  p.c_tma = 0;
+  {
+    const char *e = getenv("SKL_B200_TC_TMA_STORE");
+    // The row length must be a whole number of 16-byte units: a store box that crosses the matrix edge inside
+    // such a unit was observed to write the unit's remaining bytes.
+    if (p.c_vec_ok && (N * cs) % 16 == 0 && !(e && atoi(e) == 0) && make_c_map(&tmC, g->c, M, N, g->rsc0, cs))
+      p.c_tma = 1;
+  }
   p.alpha_i = g->alpha_i;
   p.beta_i = g->beta_i;
   p.alpha_f = g->alpha_f;
@@ -1227,16 +1363,16 @@ extern "C" int skl_b200_launch_gemm_tc(const skl_b200_gemm_args *g, uint32_t *de
 
   if (pair) {
     switch (kind) {
-      case KIND_F16: return launch_cfg2<256, KIND_F16>(tmA, tmB, p, s);
-      case KIND_F8: return launch_cfg2<256, KIND_F8>(tmA, tmB, p, s);
-      default: return launch_cfg2<256, KIND_I8>(tmA, tmB, p, s);
+      case KIND_F16: return launch_cfg2<256, KIND_F16>(tmA, tmB, tmC, p, s);
+      case KIND_F8: return launch_cfg2<256, KIND_F8>(tmA, tmB, tmC, p, s);
+      default: return launch_cfg2<256, KIND_I8>(tmA, tmB, tmC, p, s);
     }
   }
 #define TC_DISPATCH(BNV)                                                      \
   switch (kind) {                                                             \
-    case KIND_F16: return launch_cfg<BNV, KIND_F16>(tmA, tmB, p, s);          \
-    case KIND_F8: return launch_cfg<BNV, KIND_F8>(tmA, tmB, p, s);            \
-    default: return launch_cfg<BNV, KIND_I8>(tmA, tmB, p, s);                 \
+    case KIND_F16: return launch_cfg<BNV, KIND_F16>(tmA, tmB, tmC, p, s);          \
+    case KIND_F8: return launch_cfg<BNV, KIND_F8>(tmA, tmB, tmC, p, s);            \
+    default: return launch_cfg<BNV, KIND_I8>(tmA, tmB, tmC, p, s);                 \
   }
   if (bn == 256) {
     TC_DISPATCH(256)
@@ -1245,7 +1381,7 @@ extern "C" int skl_b200_launch_gemm_tc(const skl_b200_gemm_args *g, uint32_t *de
   } else if (bn == 16) {
     TC_DISPATCH(16)
   } else {
-    return launch_cfg<64, KIND_F16>(tmA, tmB, p, s);
+    return launch_cfg<64, KIND_F16>(tmA, tmB, tmC, p, s);
   }
 #undef TC_DISPATCH
 }

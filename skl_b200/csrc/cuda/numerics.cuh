@@ -138,6 +138,20 @@ __device__ __forceinline__ uint32_t enc_bf16(float x) {
   return ((u & 0x7FFFFFFFu) > 0x7F800000u) ? nan : r;
 }
 
+// Two finite-or-infinite values to packed bf16 / f16 with the hardware converter (lo in bits 0-15).  It rounds
+// to nearest even exactly like enc_bf16 / enc_f16 but canonicalises NaN, so callers use it only on values they
+// know are not NaN.
+__device__ __forceinline__ uint32_t pack_bf16x2_no_nan(float lo, float hi) {
+  uint32_t d;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
+  return d;
+}
+__device__ __forceinline__ uint32_t pack_f16x2_no_nan(float lo, float hi) {
+  uint32_t d;
+  asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
+  return d;
+}
+
 __device__ __forceinline__ float dec_f16(uint32_t bits) {
   float r;
   uint16_t h = (uint16_t)bits;

@@ -196,3 +196,32 @@ def test_int8_output_from_float_operands(skl):
     diff = np.abs(got.astype(np.int32) - want.astype(np.int32))
     assert diff.max() <= 1 and (diff != 0).mean() < 0.01
     assert np.unique(want).size > 100
+
+
+@pytest.mark.parametrize("tc", [H.BF16, H.F16, H.F32])
+def test_non_finite_scales_give_non_finite_results_in_the_same_places(skl, tc):
+    """A column scale of +inf / NaN: infinities must come out bit-exact, NaN wherever the oracle has NaN (the
+    payload of a NaN produced by an fp32 multiply is the host's or the device's own, so only the class is held)."""
+    m, n, k = 130, 260, 128
+    g = H.rng(11)
+    a = g.integers(-128, 128, size=(m, k), dtype=np.int8)
+    b = g.integers(-128, 128, size=(n, k), dtype=np.int8)  # [N][K]
+    cs = g.uniform(0.5, 1.5, n).astype(np.float32)
+    cs[5], cs[77], cs[200] = np.inf, np.nan, -np.inf
+    dt = H.NP_STORE[tc]
+    want = np.zeros((m, n), dt)
+    orc.port_gemm_fused(m, n, k, H.I8, a, k, 1, H.I8, b, 1, k, 1.0, None, cs, None, None, 0.0, tc, want, n, 1)
+    import torch
+
+    da, db, dcs = (torch.from_numpy(x).cuda() for x in (a, b, cs))
+    dc = torch.zeros((m, n * dt().itemsize), dtype=torch.uint8, device="cuda")
+    f = S.Fused(1.0, 0.0, None, dcs.data_ptr(), None, None, 0, 0.0)
+    skl.skl_gemm_fused_sm100a(m, n, k, S.I8, da.data_ptr(), k, 1, S.I8, db.data_ptr(), 1, k, C.byref(f), tc, dc.data_ptr(), n, 1)
+    S.check()
+    assert skl.skl_b200_last_path() == S.PATH_TCGEN05
+    got = dc.cpu().numpy().view(dt).reshape(m, n)
+    wf, gf = H.to_f32(tc, want), H.to_f32(tc, got)
+    assert np.array_equal(np.isnan(wf), np.isnan(gf)) and np.isnan(wf).sum() >= m
+    ok = ~np.isnan(wf)
+    assert np.array_equal(got[ok], want[ok])
+    assert np.isinf(wf).sum() >= m
