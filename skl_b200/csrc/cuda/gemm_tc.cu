@@ -51,6 +51,8 @@ struct TcParams {
   // into `tail_split` column strips each, one strip per CTA, so the last round is short instead of idle.
   int main_tiles, tail_round, tail_units, tail_split;
   uint32_t idesc_tail;  // instruction descriptor with N = BN / tail_split
+  int tail_b_atoms;     // MN-major B: boxes one strip loads per k-slab
+  uint32_t tail_b_bytes;  // bytes of B one strip loads per k-slab
   int a_mn, b_mn;  // 1: operand is MN-major in global/shared memory
   uint32_t idesc;
   void *c;
@@ -583,7 +585,8 @@ __device__ __forceinline__ float epilogue_chunk(const TcParams &p, const uint32_
 template <int BN, int KIND, bool ACT>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
     gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                   const __grid_constant__ CUtensorMap tmC, const TcParams p) {
+                   const __grid_constant__ CUtensorMap tmBs, const __grid_constant__ CUtensorMap tmC,
+                   const TcParams p) {
   using Cfg = TcConfig<BN>;
   constexpr int ES = (KIND == KIND_F16) ? 2 : 1;   // operand element size
   constexpr int BKE = SLAB_BYTES / ES;             // k elements per stage
@@ -641,7 +644,11 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
       bool ok = true;
       TileUnit u;
       for (int it = 0; ok && get_unit<BN>(p, it, u); ++it) {
-        const int m0 = u.m0, n0 = u.n0;  // a tail strip loads the full-width B box from its first column
+        const int m0 = u.m0, n0 = u.n0;
+        // a tail strip loads only its own columns of B: a narrower box (k-major, through tmBs) or fewer boxes
+        const bool strip = u.ncols != BN;
+        const uint32_t stage_tx = Cfg::A_BYTES + (strip ? p.tail_b_bytes : (uint32_t)Cfg::B_BYTES);
+        const int b_boxes = strip ? p.tail_b_atoms : B_ATOMS;
         for (int kb = 0; kb < p.num_kb; ++kb) {
           if (!mbar_wait(empty_bar + 8 * stage, phase ^ 1u, abort_flag, p.status, ERR_WAIT_EMPTY)) {
             ok = false;
@@ -649,7 +656,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
           }
           const uint32_t fb = full_bar + 8 * stage;
           const uint32_t sa = tiles + stage * Cfg::STAGE_BYTES, sb = sa + Cfg::A_BYTES;
-          mbar_expect_tx(fb, Cfg::STAGE_BYTES);
+          mbar_expect_tx(fb, stage_tx);
           const int k0 = kb * BKE;
           if (!p.a_mn) {
             tma_load_2d(sa, &tmA, fb, k0, m0);
@@ -659,11 +666,11 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
               tma_load_2d(sa + i * ATOM_BYTES, &tmA, fb, m0 + i * MN_PER_ATOM, k0);
           }
           if (!p.b_mn) {
-            tma_load_2d(sb, &tmB, fb, k0, n0);
+            tma_load_2d(sb, strip ? &tmBs : &tmB, fb, k0, n0);
           } else {
 #pragma unroll
             for (int i = 0; i < B_ATOMS; ++i)
-              tma_load_2d(sb + i * ATOM_BYTES, &tmB, fb, n0 + i * MN_PER_ATOM, k0);
+              if (i < b_boxes) tma_load_2d(sb + i * ATOM_BYTES, &tmB, fb, n0 + i * MN_PER_ATOM, k0);
           }
           if (++stage == Cfg::STAGES) {
             stage = 0;
@@ -1130,8 +1137,8 @@ int pick_bn(int64_t M, int64_t N, int kind, bool b_mn_major) {
 }
 
 template <int BN, int KIND, bool ACT>
-int launch_cfg_act(const CUtensorMap &ta, const CUtensorMap &tb, const CUtensorMap &tc, const TcParams &p,
-                   cudaStream_t s) {
+int launch_cfg_act(const CUtensorMap &ta, const CUtensorMap &tb, const CUtensorMap &tbs, const CUtensorMap &tc,
+                   const TcParams &p, cudaStream_t s) {
   using Cfg = TcConfig<BN>;
   static bool attr_set[64] = {};  // per device: function attributes do not carry over between devices
   const int dev = current_device();
@@ -1143,17 +1150,17 @@ int launch_cfg_act(const CUtensorMap &ta, const CUtensorMap &tb, const CUtensorM
   }
   int grid = p.tiles_m * p.tiles_n;
   if (grid > sm_count()) grid = sm_count();
-  gemm_tc_kernel<BN, KIND, ACT><<<grid, NUM_THREADS, Cfg::SMEM_BYTES, s>>>(ta, tb, tc, p);
+  gemm_tc_kernel<BN, KIND, ACT><<<grid, NUM_THREADS, Cfg::SMEM_BYTES, s>>>(ta, tb, tbs, tc, p);
   SKLB_COUNT_LAUNCH();
   return (int)cudaGetLastError();
 }
 
 // The activation code lives in instantiations of its own so that the plain epilogue carries none of it.
 template <int BN, int KIND>
-int launch_cfg(const CUtensorMap &ta, const CUtensorMap &tb, const CUtensorMap &tc, const TcParams &p,
-               cudaStream_t s) {
-  return p.activation ? launch_cfg_act<BN, KIND, true>(ta, tb, tc, p, s)
-                      : launch_cfg_act<BN, KIND, false>(ta, tb, tc, p, s);
+int launch_cfg(const CUtensorMap &ta, const CUtensorMap &tb, const CUtensorMap &tbs, const CUtensorMap &tc,
+               const TcParams &p, cudaStream_t s) {
+  return p.activation ? launch_cfg_act<BN, KIND, true>(ta, tb, tbs, tc, p, s)
+                      : launch_cfg_act<BN, KIND, false>(ta, tb, tbs, tc, p, s);
 }
 
 template <int BN, int KIND, bool ACT>
@@ -1324,7 +1331,14 @@ extern "C" int skl_b200_launch_gemm_tc(const skl_b200_gemm_args *g, uint32_t *de
       }
     }
     p.idesc_tail = (p.idesc & ~(0x3Fu << 17)) | ((uint32_t)((bn / p.tail_split) >> 3) << 17);
+    const int strip_cols = bn / p.tail_split, per_atom = SLAB_BYTES / es;
+    p.tail_b_atoms = (strip_cols + per_atom - 1) / per_atom;
+    p.tail_b_bytes = vb.mn_major ? (uint32_t)p.tail_b_atoms * (uint32_t)(per_atom * SLAB_BYTES)
+                                 : (uint32_t)strip_cols * SLAB_BYTES;
   }
+  CUtensorMap tmBs = tmB;  // the strips' own box of B (k-major B only; MN-major strips load fewer boxes of tmB)
+  if (p.tail_split > 1 && !vb.mn_major && !make_map(&tmBs, kind, g->tb, g->b, vb, N, K, bn / p.tail_split))
+    return (int)cudaErrorInvalidValue;
   p.c = g->c;
   p.rsc = g->rsc0;
   p.csc = g->csc0;
@@ -1370,9 +1384,9 @@ extern "C" int skl_b200_launch_gemm_tc(const skl_b200_gemm_args *g, uint32_t *de
   }
 #define TC_DISPATCH(BNV)                                                      \
   switch (kind) {                                                             \
-    case KIND_F16: return launch_cfg<BNV, KIND_F16>(tmA, tmB, tmC, p, s);          \
-    case KIND_F8: return launch_cfg<BNV, KIND_F8>(tmA, tmB, tmC, p, s);            \
-    default: return launch_cfg<BNV, KIND_I8>(tmA, tmB, tmC, p, s);                 \
+    case KIND_F16: return launch_cfg<BNV, KIND_F16>(tmA, tmB, tmBs, tmC, p, s);          \
+    case KIND_F8: return launch_cfg<BNV, KIND_F8>(tmA, tmB, tmBs, tmC, p, s);            \
+    default: return launch_cfg<BNV, KIND_I8>(tmA, tmB, tmBs, tmC, p, s);                 \
   }
   if (bn == 256) {
     TC_DISPATCH(256)
@@ -1381,7 +1395,7 @@ extern "C" int skl_b200_launch_gemm_tc(const skl_b200_gemm_args *g, uint32_t *de
   } else if (bn == 16) {
     TC_DISPATCH(16)
   } else {
-    return launch_cfg<64, KIND_F16>(tmA, tmB, tmC, p, s);
+    return launch_cfg<64, KIND_F16>(tmA, tmB, tmBs, tmC, p, s);
   }
 #undef TC_DISPATCH
 }
