@@ -255,7 +255,7 @@ def make_workloads(torch, S, lib):
             return gemm_ex(m, n, k, code, code, code, a, b, c), 2.0 * m * n * k, "tflops", 40
         return build
 
-    def gemv(mm, n=14336):
+    def gemv(mm, n=14336, static=False):
         def build():
             # config 4; rotate over weight copies totalling > 2x L2 so every pass streams from HBM
             k = 4096
@@ -270,8 +270,12 @@ def make_workloads(torch, S, lib):
             def call():
                 wi = w[idx[0] % copies]
                 idx[0] += 1
+                if static:  # weights declared static: consecutive launches overlap drain and weight prefetch
+                    lib.skl_b200_set_static_weights(1)
                 lib.skl_gemm_ex_sm100a(mm, n, k, S.I8, x.data_ptr(), k, 1, S.I8, wi.data_ptr(), 1, k, 1.0, sx.data_ptr(),
                                        sw.data_ptr(), 0.0, S.F32, y.data_ptr(), n, 1)
+                if static:
+                    lib.skl_b200_set_static_weights(0)
             return call, float(n * k + mm * k + 4 * (n + mm) + 4 * mm * n), "gbs", 60
         return build
 
@@ -323,6 +327,8 @@ def make_workloads(torch, S, lib):
     W["bf16_4096_bf16out"] = half(torch.bfloat16, S.BF16)
     W["fp16_4096_fp16out"] = half(torch.float16, S.F16)
     W["gemv_i8_m1"], W["gemv_i8_m4"], W["gemv_i8_m16"] = gemv(1), gemv(4), gemv(16)
+    W["gemv_i8_m1_static_weights"], W["gemv_i8_m2_static_weights"] = gemv(1, static=True), gemv(2, static=True)
+    W["gemv_i8_m2"] = gemv(2)
     # the same kernels at other row counts: separates the fixed cost of a launch from the streaming rate
     for rows in (1184, 4736, 28672, 57344):
         W[f"gemv_i8_m1_n{rows}"] = gemv(1, rows)

@@ -88,6 +88,11 @@ SKL_FUNC void skl_b200_set_async(int enabled);
 SKL_FUNC void skl_b200_synchronize(void);
 /* Releases the calling thread's cached device workspaces. */
 SKL_FUNC void skl_b200_release_workspace(void);
+/* Declares, for this thread's following calls, that the B operands (the weights) are static: nothing queued
+ * earlier on the stream writes them.  The skinny int8 kernel (m <= 2) then launches as a programmatic
+ * dependent of the preceding kernel: it starts streaming its weights while that kernel drains and waits for
+ * it only before reading the activations, scales, bias or C.  Off by default; results are identical. */
+SKL_FUNC void skl_b200_set_static_weights(int enabled);
 
 /* Which kernel family served the calling thread's last GEMM call (for tests and benchmarks). */
 typedef enum skl_b200_path {

@@ -40,6 +40,7 @@ SIGNATURES = {
     "skl_b200_set_async": ([_I], None),
     "skl_b200_synchronize": ([], None),
     "skl_b200_release_workspace": ([], None),
+    "skl_b200_set_static_weights": ([_I], None),
     "skl_b200_last_path": ([], _I),
     "skl_b200_last_launch_count": ([], _I),
     "skl_b200_force_path": ([_I], None),

@@ -69,6 +69,8 @@ typedef struct skl_b200_gemm_args {
   float *global_max;       /* NULL, or one device float raised to the largest result value (NaN ignored) */
   int32_t activation;      /* SKL_ACT_*: applied after bias and beta*C, before the maximum and the narrowing */
   float act_param;         /* logistic / swish: beta; swiglu: delta */
+  int32_t b_static;        /* the caller declared B (the weights) not written by earlier work on the stream: the
+                              skinny kernel may then start streaming B before the preceding kernel has finished */
 } skl_b200_gemm_args;
 
 /* Device status word written by kernels whose bounded waits expire: 0 = ok, else a stage code. */

@@ -41,6 +41,7 @@ struct GemvParams {
   float *global_max;
   int activation;
   float act_param;
+  int overlap;  // launched as a programmatic dependent: see the kernel's first lines
   uint32_t *status;
 };
 
@@ -184,11 +185,17 @@ __global__ void __launch_bounds__(GV_THREADS, 1) gemv_i8_kernel(const GemvParams
     pq += count;
   };
 
+  // Overlapped launch (the caller declared the weights static): let the next launch on the stream start on
+  // each SM as soon as this one's CTA there has left, and -- being such a dependent launch itself -- start
+  // the weight stream at once but wait for the previous kernel to finish before touching anything that
+  // kernel may have written (activations, scales, bias, C).
+  if (p.overlap) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   if (lane < S) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bars + lane * 8));
   asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   __syncwarp();
   issue(S);  // weights start streaming before the activations are staged
+  if (p.overlap) asm volatile("griddepcontrol.wait;" ::: "memory");
   for (int e = threadIdx.x; e < MP * kc; e += GV_THREADS) {
     int mi = e / kc, ch = e - mi * kc;
     uint4 v = make_uint4(0, 0, 0, 0);
@@ -356,6 +363,7 @@ extern "C" int skl_b200_launch_gemv_i8(const skl_b200_gemm_args *g, uint32_t *de
   p.global_max = g->global_max;
   p.activation = g->activation;
   p.act_param = g->act_param;
+  p.overlap = g->b_static ? 1 : 0;
   p.status = dev_status;
   int mp = 1;
   while (mp < p.m) mp <<= 1;
@@ -390,7 +398,19 @@ extern "C" int skl_b200_launch_gemv_i8(const skl_b200_gemm_args *g, uint32_t *de
                                (int)GV_SMEM_BUDGET);                                               \
       attr_set[dev] = (e == cudaSuccess);                                                          \
     }                                                                                              \
-    if (e == cudaSuccess) gemv_i8_kernel<MPV><<<grid, GV_THREADS, smem, s>>>(p);                   \
+    if (e == cudaSuccess) {                                                                        \
+      cudaLaunchConfig_t cfg = {};                                                                 \
+      cfg.gridDim = dim3((unsigned)grid);                                                          \
+      cfg.blockDim = dim3(GV_THREADS);                                                             \
+      cfg.dynamicSmemBytes = smem;                                                                 \
+      cfg.stream = s;                                                                              \
+      cudaLaunchAttribute attr[1];                                                                 \
+      attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;                             \
+      attr[0].val.programmaticStreamSerializationAllowed = 1;                                      \
+      cfg.attrs = attr;                                                                            \
+      cfg.numAttrs = p.overlap ? 1 : 0;                                                            \
+      e = cudaLaunchKernelEx(&cfg, gemv_i8_kernel<MPV>, p);                                        \
+    }                                                                                              \
   } while (0)
   switch (mp) {
     case 1: GV_LAUNCH(1); break;

@@ -36,6 +36,7 @@ typedef struct {
 typedef struct {
   void *stream;
   int async;
+  int static_weights; /* skl_b200_set_static_weights */
   skl_b200_status_t status;
   char cuda_err[192];
   skl_b200_path_t last_path;
@@ -53,7 +54,7 @@ typedef struct {
   cudaEvent_t ev_in[PIPE_MAX_CHUNKS], ev_done[PIPE_MAX_CHUNKS], ev_ready;
 } ctx_t;
 
-static __thread ctx_t g_ctx = {0, 0, SKL_B200_OK, {0}, SKL_B200_PATH_NONE, 0, 0, -1, 0, {{0, 0}}, 0, 0, 0, 0, 0, 0, {0}, {0}, 0};
+static __thread ctx_t g_ctx = {.status = SKL_B200_OK, .last_path = SKL_B200_PATH_NONE, .device = -1};
 
 static void set_err(skl_b200_status_t s) {
   if (g_ctx.status == SKL_B200_OK) g_ctx.status = s;
@@ -200,6 +201,7 @@ const char *skl_b200_last_cuda_error(void) { return g_ctx.cuda_err; }
 void skl_b200_set_stream(void *cuda_stream) { g_ctx.stream = cuda_stream; }
 void *skl_b200_get_stream(void) { return g_ctx.stream; }
 void skl_b200_set_async(int enabled) { g_ctx.async = enabled != 0; }
+void skl_b200_set_static_weights(int enabled) { g_ctx.static_weights = enabled != 0; }
 skl_b200_path_t skl_b200_last_path(void) { return g_ctx.last_path; }
 int skl_b200_last_launch_count(void) { return g_ctx.last_launches; }
 void skl_b200_force_path(int path) { g_ctx.force_path = path; }
@@ -548,6 +550,9 @@ static void run_gemm(skl_b200_gemm_args *g) {
   int host_any = 0;
   const int a_host = K != 0 && !on_device(g->a);
   const int c_host = !on_device(g->c);
+
+  /* a B that this call stages itself is written on the stream just before the kernel: never "static" */
+  g->b_static = (g_ctx.static_weights && K != 0 && on_device(g->b)) ? 1 : 0;
 
   /* B and the scale vectors are staged whole in either route */
   if (K != 0 && !on_device(g->b)) {

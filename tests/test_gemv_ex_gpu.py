@@ -101,3 +101,41 @@ def test_extended_epilogue_all_pairs_and_outputs(skl, pair, tc):
         err = np.where(out == ref, 0.0, np.abs(out - ref))  # equal infinities count as agreement
         tol = np.where(np.isfinite(tol), tol, np.inf)
         assert np.all(err <= tol), float(np.nanmax(err - tol))
+
+
+@pytest.mark.parametrize("m", [1, 2])
+def test_overlapped_launches_with_static_weights_keep_stream_order(skl, m):
+    """With skl_b200_set_static_weights(1) each skinny launch may start streaming weights before its predecessor has
+    finished, but must still see everything the predecessor wrote.  A chain of launches accumulates into the same C
+    (beta = 1), each from new activations written just before it on the same stream; the sum must be exact."""
+    import torch
+
+    n, k, steps = 3000, 2048, 24
+    g = H.rng(500 + m)
+    w = g.integers(-128, 128, size=(n, k), dtype=np.int8)
+    xs = g.integers(-128, 128, size=(steps, m, k), dtype=np.int8)
+    want = np.zeros((m, n), np.int64)
+    for s_ in range(steps):
+        want += xs[s_].astype(np.int64) @ w.astype(np.int64).T
+    dw = torch.from_numpy(w).cuda()
+    dxs = torch.from_numpy(xs).cuda()
+    dx = torch.zeros((m, k), dtype=torch.int8, device="cuda")
+    dc = torch.zeros((m, n), dtype=torch.int32, device="cuda")
+    stream = torch.cuda.Stream()
+    skl.skl_b200_set_stream(stream.cuda_stream)
+    skl.skl_b200_set_async(1)
+    skl.skl_b200_set_static_weights(1)
+    try:
+        with torch.cuda.stream(stream):
+            for s_ in range(steps):
+                dx.copy_(dxs[s_])  # the activations change between launches, on the same stream
+                skl.skl_gemm_i8rc_i8rc_i32rc_sm100a(m, n, k, 1, dx.data_ptr(), k, 1, dw.data_ptr(), 1, k, 1, dc.data_ptr(), n, 1)
+                assert skl.skl_b200_last_path() == S.PATH_GEMV
+        skl.skl_b200_synchronize()
+        S.check()
+    finally:
+        skl.skl_b200_set_static_weights(0)
+        skl.skl_b200_set_async(0)
+        skl.skl_b200_set_stream(None)
+        torch.cuda.synchronize()
+    assert np.array_equal(dc.cpu().numpy().astype(np.int64), want)
