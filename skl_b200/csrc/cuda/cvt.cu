@@ -89,96 +89,99 @@ __device__ __forceinline__ uint32_t f8_to_bf16_bits(uint32_t code) {
   return f2u(f) >> 16;
 }
 
-__device__ __forceinline__ bool has_zero_byte(uint32_t v) {
-  return ((v - 0x01010101u) & ~v & 0x80808080u) != 0u;
+// Two fp8 codes (low 16 bits of `two`, lower byte first) -> two bf16 patterns, without a branch: the hardware
+// decoder to f16x2 (exact for every code, subnormals included), f16 -> f32 -> bf16x2 (exact: at most 4
+// significant bits), then the one place where the converters and the reference differ: they produce the NaN
+// pattern 0x7FFF (sign kept), the reference's decode-then-cast produces +qNaN 0x7FC0 for every NaN code
+// (ref/cvt/cvt_ofp8.c:18-52, 230-242).  No finite or infinite value has the low 15 bits 0x7FFF.
+template <int FMT>
+__device__ __forceinline__ uint32_t f8x2_to_bf16x2(uint32_t two) {
+  const uint16_t in = (uint16_t)two;
+  uint32_t h2;
+  if (FMT == SKL_DT_F8E4M3)
+    asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(h2) : "h"(in));
+  else
+    asm("cvt.rn.f16x2.e5m2x2 %0, %1;" : "=r"(h2) : "h"(in));
+  float f0, f1;
+  asm("{\n\t.reg .f16 a, b;\n\tmov.b32 {a, b}, %2;\n\tcvt.f32.f16 %0, a;\n\tcvt.f32.f16 %1, b;\n\t}"
+      : "=f"(f0), "=f"(f1)
+      : "r"(h2));
+  uint32_t r;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(f1), "f"(f0));
+  const uint32_t t = r & 0x7FFF7FFFu;
+  const uint32_t nan1 = ((t + 0x00010001u) >> 15) & 0x00010001u;  // 1 in each half that holds 0x7FFF
+  const uint32_t mask = nan1 * 0xFFFFu;
+  return (r & ~mask) | (0x7FC07FC0u & mask);
 }
 
 // Four fp8 codes (one 32-bit word, lowest byte first) -> four bf16 patterns in two words.
-// Normal codes are widened with packed integer arithmetic, two per word:
-//     E4M3: bf16 = sign<<8 | ((code & 0x7F) << 4) + (120 << 7)      E5M2: ... << 5) + (112 << 7)
-// A word that holds any code with a zero exponent field (zero, subnormal) or an all-ones one
-// (E4M3 NaN, E5M2 Inf / NaN) takes the per-element decoder instead.
 template <int FMT>
 __device__ __forceinline__ void f8x4_to_bf16x4(uint32_t w, uint32_t &lo, uint32_t &hi) {
-  constexpr uint32_t EXPF = FMT == SKL_DT_F8E4M3 ? 0x78787878u : 0x7C7C7C7Cu;
-  const uint32_t e = w & EXPF;
-  // E4M3's only non-finite code is exponent and mantissa all ones; E5M2's are every all-ones exponent
-  const uint32_t top = FMT == SKL_DT_F8E4M3 ? ((w & 0x7F7F7F7Fu) ^ 0x7F7F7F7Fu) : (e ^ EXPF);
-  if (has_zero_byte(e) || has_zero_byte(top)) {
-    lo = f8_to_bf16_bits<FMT>(w & 0xFFu) | (f8_to_bf16_bits<FMT>((w >> 8) & 0xFFu) << 16);
-    hi = f8_to_bf16_bits<FMT>((w >> 16) & 0xFFu) | (f8_to_bf16_bits<FMT>(w >> 24) << 16);
-    return;
-  }
-  constexpr int SH = FMT == SKL_DT_F8E4M3 ? 4 : 5;
-  constexpr uint32_t BIAS = FMT == SKL_DT_F8E4M3 ? 0x3C003C00u : 0x38003800u;
-  const uint32_t x0 = __byte_perm(w, 0u, 0x4140);  // 0x00b1_00b0
-  const uint32_t x1 = __byte_perm(w, 0u, 0x4342);  // 0x00b3_00b2
-  lo = (((x0 & 0x007F007Fu) << SH) + BIAS) | ((x0 & 0x00800080u) << 8);
-  hi = (((x1 & 0x007F007Fu) << SH) + BIAS) | ((x1 & 0x00800080u) << 8);
+  lo = f8x2_to_bf16x2<FMT>(w);
+  hi = f8x2_to_bf16x2<FMT>(w >> 16);
 }
 
+// Widening: the unit of work is 8 codes = one 8-byte load and one 16-byte store, consecutive lanes taking
+// consecutive units, so that every warp-level load covers 256 contiguous bytes and every store 512 (a thread
+// that converted 16 codes would write its 32 bytes as two 16-byte halves, and each warp-level store would
+// then touch 32 sectors half-way).  Eight units per thread are in flight to cover the HBM latency.
 template <int FMT>
 __global__ void __launch_bounds__(CVT_THREADS)
     cvt_f8_to_bf16_kernel(uint16_t *__restrict__ dst, const uint8_t *__restrict__ src, size_t n,
                           bool vec_ok) {
+  constexpr int U = 8;
   const size_t stride = (size_t)gridDim.x * blockDim.x;
   const size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-  const size_t nvec = vec_ok ? n / 16 : 0;
-  // four independent 16-byte loads per thread per step: enough bytes in flight to cover HBM latency
-  for (size_t v0 = tid; v0 < nvec; v0 += 4 * stride) {
-    uint4 q[4];
+  const size_t nvec = vec_ok ? n / 8 : 0;
+  for (size_t v0 = tid; v0 < nvec; v0 += U * stride) {
+    uint2 q[U];
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {
+    for (int u = 0; u < U; ++u) {
       const size_t v = v0 + u * stride;
-      q[u] = v < nvec ? __ldg(reinterpret_cast<const uint4 *>(src) + v) : make_uint4(0, 0, 0, 0);
+      q[u] = v < nvec ? __ldg(reinterpret_cast<const uint2 *>(src) + v) : make_uint2(0, 0);
     }
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {
+    for (int u = 0; u < U; ++u) {
       const size_t v = v0 + u * stride;
       if (v >= nvec) break;
-      uint32_t w[4] = {q[u].x, q[u].y, q[u].z, q[u].w};
-      uint32_t o[8];
-#pragma unroll
-      for (int i = 0; i < 4; ++i) f8x4_to_bf16x4<FMT>(w[i], o[2 * i], o[2 * i + 1]);
-      uint4 *d = reinterpret_cast<uint4 *>(dst) + v * 2;
-      d[0] = make_uint4(o[0], o[1], o[2], o[3]);
-      d[1] = make_uint4(o[4], o[5], o[6], o[7]);
+      uint32_t o[4];
+      f8x4_to_bf16x4<FMT>(q[u].x, o[0], o[1]);
+      f8x4_to_bf16x4<FMT>(q[u].y, o[2], o[3]);
+      reinterpret_cast<uint4 *>(dst)[v] = make_uint4(o[0], o[1], o[2], o[3]);
     }
   }
-  for (size_t i = nvec * 16 + tid; i < n; i += stride) dst[i] = (uint16_t)f8_to_bf16_bits<FMT>(src[i]);
+  for (size_t i = nvec * 8 + tid; i < n; i += stride) dst[i] = (uint16_t)f8_to_bf16_bits<FMT>(src[i]);
 }
 
-// rows x cols matrix, unit stride along cols, separate leading dimensions; cols % 16 == 0 and
-// 16-byte aligned rows take the vector path.
+// rows x cols matrix, unit stride along cols, separate leading dimensions; cols % 8 == 0 and rows aligned
+// to 8 (source) / 16 (destination) bytes take the vector path.
 template <int FMT>
 __global__ void __launch_bounds__(CVT_THREADS)
     cvt_f8_to_bf16_2d_kernel(uint16_t *__restrict__ dst, size_t ld_dst, const uint8_t *__restrict__ src,
                              size_t ld_src, size_t rows, size_t cols, bool vec_ok) {
+  constexpr int U = 8;
   const size_t stride = (size_t)gridDim.x * blockDim.x;
   const size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (vec_ok) {
-    const size_t cvec = cols / 16;
+    const size_t cvec = cols / 8;
     const size_t total = rows * cvec;
-    for (size_t v0 = tid; v0 < total; v0 += 4 * stride) {
-      uint4 q[4];
-      size_t rr[4], cc[4];
+    for (size_t v0 = tid; v0 < total; v0 += U * stride) {
+      uint2 q[U];
+      size_t doff[U];  // destination offset in 16-byte units
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
+      for (int u = 0; u < U; ++u) {
         const size_t v = v0 + u * stride;
-        rr[u] = v / cvec;
-        cc[u] = v - rr[u] * cvec;
-        q[u] = v < total ? __ldg(reinterpret_cast<const uint4 *>(src + rr[u] * ld_src) + cc[u]) : make_uint4(0, 0, 0, 0);
+        const size_t r = v / cvec, c = v - r * cvec;
+        doff[u] = r * (ld_dst / 8) + c;
+        q[u] = v < total ? __ldg(reinterpret_cast<const uint2 *>(src + r * ld_src) + c) : make_uint2(0, 0);
       }
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
+      for (int u = 0; u < U; ++u) {
         if (v0 + u * stride >= total) break;
-        uint32_t w[4] = {q[u].x, q[u].y, q[u].z, q[u].w};
-        uint32_t o[8];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) f8x4_to_bf16x4<FMT>(w[i], o[2 * i], o[2 * i + 1]);
-        uint4 *d = reinterpret_cast<uint4 *>(dst + rr[u] * ld_dst) + cc[u] * 2;
-        d[0] = make_uint4(o[0], o[1], o[2], o[3]);
-        d[1] = make_uint4(o[4], o[5], o[6], o[7]);
+        uint32_t o[4];
+        f8x4_to_bf16x4<FMT>(q[u].x, o[0], o[1]);
+        f8x4_to_bf16x4<FMT>(q[u].y, o[2], o[3]);
+        reinterpret_cast<uint4 *>(dst)[doff[u]] = make_uint4(o[0], o[1], o[2], o[3]);
       }
     }
   } else {
@@ -256,7 +259,7 @@ extern "C" int skl_b200_launch_cvt_f8_to_bf16(void *dst, const void *src, int sr
   if (n == 0) return 0;
   cudaStream_t s = (cudaStream_t)stream;
   const bool vec = aligned16(dst) && aligned16(src);
-  const int grid = cvt_grid(n, 16);
+  const int grid = cvt_grid(n, 8 * 8);
   if (src_fmt == SKL_DT_F8E4M3)
     cvt_f8_to_bf16_kernel<SKL_DT_F8E4M3>
         <<<grid, CVT_THREADS, 0, s>>>((uint16_t *)dst, (const uint8_t *)src, n, vec);
@@ -272,9 +275,8 @@ extern "C" int skl_b200_launch_cvt_f8_to_bf16_2d(void *dst, size_t ld_dst, const
                                                  size_t cols, void *stream) {
   if (rows == 0 || cols == 0) return 0;
   cudaStream_t s = (cudaStream_t)stream;
-  const bool vec = aligned16(dst) && aligned16(src) && (cols % 16 == 0) && (ld_src % 16 == 0) &&
-                   (ld_dst % 8 == 0);
-  const int grid = cvt_grid(rows * cols, 16);
+  const bool vec = aligned16(dst) && aligned16(src) && (cols % 8 == 0) && (ld_src % 8 == 0) && (ld_dst % 8 == 0);
+  const int grid = cvt_grid(rows * cols, 8 * 8);
   if (src_fmt == SKL_DT_F8E4M3)
     cvt_f8_to_bf16_2d_kernel<SKL_DT_F8E4M3><<<grid, CVT_THREADS, 0, s>>>(
         (uint16_t *)dst, ld_dst, (const uint8_t *)src, ld_src, rows, cols, vec);
