@@ -635,6 +635,11 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // Launched as a programmatic dependent of the kernel before it on the stream: the set-up above ran while
+  // that kernel was still draining; nothing it may have written is read before this point.  The next such
+  // launch may likewise begin its own set-up as this kernel's CTAs leave.
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
   if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer
@@ -852,6 +857,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
   cluster_sync_all();  // both CTAs' barriers are initialised before either touches the other's
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  asm volatile("griddepcontrol.wait;" ::: "memory");  // see gemm_tc_kernel
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
   const int num_tiles = p.tiles_m * p.tiles_n;  // tiles of 256 rows
 
@@ -1136,6 +1143,17 @@ int pick_bn(int64_t M, int64_t N, int kind, bool b_mn_major) {
   return best;
 }
 
+// Launch as a programmatic dependent of the preceding kernel (its set-up overlaps that kernel's tail; see the
+// griddepcontrol.wait in the kernels).  SKL_B200_TC_OVERLAP=0 turns it off.
+bool overlap_launch() {
+  static int on = -1;
+  if (on < 0) {
+    const char *e = getenv("SKL_B200_TC_OVERLAP");
+    on = (e && atoi(e) == 0) ? 0 : 1;
+  }
+  return on != 0;
+}
+
 template <int BN, int KIND, bool ACT>
 int launch_cfg_act(const CUtensorMap &ta, const CUtensorMap &tb, const CUtensorMap &tbs, const CUtensorMap &tc,
                    const TcParams &p, cudaStream_t s) {
@@ -1150,8 +1168,19 @@ int launch_cfg_act(const CUtensorMap &ta, const CUtensorMap &tb, const CUtensorM
   }
   int grid = p.tiles_m * p.tiles_n;
   if (grid > sm_count()) grid = sm_count();
-  gemm_tc_kernel<BN, KIND, ACT><<<grid, NUM_THREADS, Cfg::SMEM_BYTES, s>>>(ta, tb, tbs, tc, p);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)grid);
+  cfg.blockDim = dim3(NUM_THREADS);
+  cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = overlap_launch() ? 1 : 0;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BN, KIND, ACT>, ta, tb, tbs, tc, p);
   SKLB_COUNT_LAUNCH();
+  if (e != cudaSuccess) return (int)e;
   return (int)cudaGetLastError();
 }
 
@@ -1204,13 +1233,15 @@ int launch_cfg2_act(const CUtensorMap &ta, const CUtensorMap &tb, const CUtensor
   cfg.blockDim = dim3(NUM_THREADS);
   cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
   cfg.stream = s;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = 2;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = overlap_launch() ? 2 : 1;
   cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc2_kernel<BN, KIND, ACT>, ta, tb, tc, p);
   SKLB_COUNT_LAUNCH();
   if (e != cudaSuccess) return (int)e;
