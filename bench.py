@@ -237,6 +237,27 @@ def make_workloads(torch, S, lib):
             lib.skl_gemm_i8_i8_i32_sm100a(m, n, k, 1, a.data_ptr(), k, b.data_ptr(), n, 0, c.data_ptr(), n)
         return call, 2.0 * m * n * k, "tflops", 20
 
+    def int8_packed(force_simt):
+        def build():
+            # SKL's packed entry point on an mmt4d-style layout: A [m1][k1][16][8], B [n1][k1][16][8], C [m1][n1][16][16]
+            m = n = k = 4096 if not force_simt else 1024
+            m0, n0, k0 = 16, 16, 8
+            m1, n1, k1 = m // m0, n // n0, k // k0
+            a = torch.randint(-128, 128, (m * k,), dtype=torch.int8, device=dev, generator=g)
+            b = torch.randint(-128, 128, (k * n,), dtype=torch.int8, device=dev, generator=g)
+            c = torch.empty((m * n,), dtype=torch.int32, device=dev)
+
+            def call():
+                if force_simt:
+                    lib.skl_b200_force_path(S.PATH_GENERIC)
+                lib.skl_gemm_i8rcprc_i8rcprc_i32rcprc_sm100a(
+                    m0, n0, k0, m1, n1, k1, 1, a.data_ptr(), k0, 1, k1 * m0 * k0, m0 * k0, b.data_ptr(), 1, k0, n0 * k0,
+                    k1 * n0 * k0, 0, c.data_ptr(), n0, 1, n1 * m0 * n0, m0 * n0)
+                if force_simt:
+                    lib.skl_b200_force_path(0)
+            return call, 2.0 * m * n * k, "tflops", 10
+        return build
+
     def fp8(ta, alpha):
         def build():
             m = n = k = 8192  # config 3; finite codes only
@@ -322,6 +343,8 @@ def make_workloads(torch, S, lib):
         return call, 4.0 * m * n, "gbs", 10
 
     W["int8_8192_i32out"] = int8_8192
+    W["int8_4096_packed_i32out"] = int8_packed(False)
+    W["int8_1024_packed_i32out_simt_kernel"] = int8_packed(True)
     W["fp8_e4m3xe4m3_8192_bf16out"] = fp8(S.F8E4M3, 1e-3)
     W["fp8_e5m2xe4m3_8192_bf16out"] = fp8(S.F8E5M2, 1e-6)
     W["bf16_4096_bf16out"] = half(torch.bfloat16, S.BF16)

@@ -19,7 +19,7 @@
 
 /* ------------------------------------------------------------------ per-thread context */
 
-enum { WS_A = 0, WS_B, WS_C, WS_ROW, WS_COL, WS_WIDEN, WS_BIAS, WS_GMAX, WS_COUNT };
+enum { WS_A = 0, WS_B, WS_C, WS_ROW, WS_COL, WS_WIDEN, WS_BIAS, WS_GMAX, WS_PLAIN_A, WS_PLAIN_B, WS_PLAIN_C, WS_COUNT };
 
 #define PIPE_MAX_CHUNKS 16
 
@@ -534,6 +534,68 @@ static int run_gemm_pipelined(skl_b200_gemm_args *g, int a_host, int c_host, int
   return 1;
 }
 
+/* Blocked (packed) operands on the tensor cores.  The any-stride kernel serves every blocked description, but
+ * for a large problem one pass of the re-layout kernel over each operand (O(MK + KN + MN) bytes at HBM speed) is
+ * far cheaper than running O(MNK) work on the CUDA cores: A and B are unblocked into k-major plain workspaces,
+ * C (when it is read) into a row-major one, the problem runs as a plain GEMM, and C is blocked back.  The
+ * packed GEMM's matrices are exactly m0*m1 x n0*n1 (ref/gemm/gemm_i8rcprc_i8rcprc_i32rcprc.c:10-37), so the
+ * way back writes every element of C's blocks and nothing else.  Device pointers only (staged by the caller). */
+typedef struct {
+  int active;
+  skl_b200_gemm_args packed; /* the caller's description, for the way back */
+  size_t ldc;
+} unblock_t;
+
+static int unblock_operands(skl_b200_gemm_args *g, unblock_t *u) {
+  u->active = 0;
+  if (g->m1 == 1 && g->n1 == 1 && g->k1 == 1) return 1;
+  const uint64_t M = g->m0 * g->m1, N = g->n0 * g->n1, K = g->k0 * g->k1;
+  double threshold = 16777216.0; /* 2^24 multiply-adds */
+  {
+    const char *e = getenv("SKL_B200_UNBLOCK_MIN_MNK"); /* tuning / test override */
+    if (e) threshold = atof(e);
+  }
+  if (K == 0 || (double)M * (double)N * (double)K < threshold) return 1;
+  if (g_ctx.force_path == SKL_B200_PATH_GENERIC) return 1;
+  if (K > 65536 && g->ta == SKL_DT_I8) return 1; /* the tensor path's int8 limit */
+  const size_t ea = dt_size(g->ta), eb = dt_size(g->tb), ec = dt_size(g->tc);
+  const size_t ldk_a = (size_t)((K * ea + 15) / 16 * 16) / ea, ldk_b = (size_t)((K * eb + 15) / 16 * 16) / eb;
+  const size_t ldc = (size_t)((N * ec + 15) / 16 * 16) / ec;
+  void *pa = workspace(WS_PLAIN_A, (size_t)M * ldk_a * ea);
+  void *pb = pa ? workspace(WS_PLAIN_B, (size_t)N * ldk_b * eb) : 0;
+  void *pc = pb ? workspace(WS_PLAIN_C, (size_t)M * ldc * ec) : 0;
+  if (!pc) return 0;
+  /* A: blocks m0 x k0 -> [M][ldk]; B: blocks k0 x n0 -> [N][ldk] (k contiguous) */
+  if (!cuda_ok((cudaError_t)skl_b200_launch_unpack(ea, g->m0, g->k0, g->a, (size_t)g->rsa0, (size_t)g->csa0,
+                                                   (size_t)g->rsa1, (size_t)g->csa1, M, K, pa, ldk_a, 1, g_ctx.stream)))
+    return 0;
+  if (!cuda_ok((cudaError_t)skl_b200_launch_unpack(eb, g->k0, g->n0, g->b, (size_t)g->rsb0, (size_t)g->csb0,
+                                                   (size_t)g->rsb1, (size_t)g->csb1, K, N, pb, 1, ldk_b, g_ctx.stream)))
+    return 0;
+  if (reads_old_c(g) &&
+      !cuda_ok((cudaError_t)skl_b200_launch_unpack(ec, g->m0, g->n0, g->c, (size_t)g->rsc0, (size_t)g->csc0,
+                                                   (size_t)g->rsc1, (size_t)g->csc1, M, N, pc, ldc, 1, g_ctx.stream)))
+    return 0;
+  u->active = 1;
+  u->packed = *g;
+  u->ldc = ldc;
+  g->m0 = M; g->n0 = N; g->k0 = K;
+  g->m1 = g->n1 = g->k1 = 1;
+  g->a = pa; g->rsa0 = (int64_t)ldk_a; g->csa0 = 1; g->rsa1 = g->csa1 = 0;
+  g->b = pb; g->rsb0 = 1; g->csb0 = (int64_t)ldk_b; g->rsb1 = g->csb1 = 0;
+  g->c = pc; g->rsc0 = (int64_t)ldc; g->csc0 = 1; g->rsc1 = g->csc1 = 0;
+  g->b_static = 0; /* B was just written on this stream */
+  return 1;
+}
+
+static int reblock_result(const skl_b200_gemm_args *plain, const unblock_t *u) {
+  if (!u->active) return 1;
+  const skl_b200_gemm_args *q = &u->packed;
+  return cuda_ok((cudaError_t)skl_b200_launch_pack(dt_size(q->tc), (size_t)plain->m0, (size_t)plain->n0, plain->c, u->ldc,
+                                                   1, q->m0, q->n0, q->c, (size_t)q->rsc0, (size_t)q->csc0,
+                                                   (size_t)q->rsc1, (size_t)q->csc1, 0, g_ctx.stream));
+}
+
 static void run_gemm(skl_b200_gemm_args *g) {
   if (!begin_call()) return;
   g_ctx.last_path = SKL_B200_PATH_NONE;
@@ -623,8 +685,11 @@ static void run_gemm(skl_b200_gemm_args *g) {
     g->c = out.dev;
   }
 
+  unblock_t unblocked;
+  if (!unblock_operands(g, &unblocked)) return;
   if (!widen_fp8_operand(g)) return;
   if (!dispatch_launch(g)) return;
+  if (!reblock_result(g, &unblocked)) return;
 
   if (c_host && !stage_out_end(&out)) return;
   if (host_gmax &&

@@ -154,6 +154,58 @@ def test_packed_operands(skl, t):
 
 
 @pytest.mark.parametrize("t", ALL_T)
+@pytest.mark.parametrize("where", ["device", "host"])
+def test_large_packed_operands_run_unblocked_on_the_tensor_cores(skl, t, where):
+    """A blocked problem above 2^24 multiply-adds is unblocked into plain workspaces, run on the tensor-core
+    kernel and blocked back (IREE mmt4d-like layout here: A [m1][k1][m0][k0], B [n1][k1][n0][k0], C [m1][n1][m0][n0]).
+    int8 is exact; floats are held to the reference suite's forward bound; the guard elements must survive."""
+    from oracle import pyoracle as orc
+    from gpu_common import DeviceBuf
+
+    P = orc._p
+    name = {H.I8: "i8", H.BF16: "bf16", H.F16: "f16", H.F8E4M3: "f8e4m3", H.F8E5M2: "f8e5m2"}[t]
+    tc = H.I32 if t == H.I8 else H.F32
+    fn = getattr(skl, f"skl_gemm_{name}rcprc_{name}rcprc_{'i32' if t == H.I8 else 'f32'}rcprc_sm100a")
+    g = H.rng(23)
+    m0, n0, k0, m1, n1, k1 = 16, 8, 4, 20, 36, 72  # M = 320, N = 288, K = 288: 2.65e7 multiply-adds
+    M, N, K = m0 * m1, n0 * n1, k0 * k1
+    a = H.random_operand(t, (M * K,), g)
+    b = H.random_operand(t, (K * N,), g)
+    c = H.random_operand(tc, (M * N + 9,), g)
+    sa = (k0, 1, k1 * m0 * k0, m0 * k0)              # rs0, cs0, rs1, cs1 of A[m][k]
+    sb = (1, k0, n0 * k0, k1 * n0 * k0)              # B[k][n]: k within block unit stride, blocks [n1][k1]
+    sc = (n0, 1, n1 * m0 * n0, m0 * n0)
+    want = c.copy()
+    if t == H.I8:
+        orc.port().orc_gemm_packed_i8_i32(m0, n0, k0, m1, n1, k1, 2, P(a), *sa, P(b), *sb, 3, P(want), *sc)
+    else:
+        orc.port().orc_gemm_packed_fp_f32(m0, n0, k0, m1, n1, k1, 2.0, t, P(a), *sa, t, P(b), *sb, 3.0, P(want), *sc)
+    if where == "host":
+        got = c.copy()
+        fn(m0, n0, k0, m1, n1, k1, 2, S.ptr(a), *sa, S.ptr(b), *sb, 3, S.ptr(got), *sc)
+        S.check()
+    else:
+        da, db, dc = DeviceBuf(a), DeviceBuf(b), DeviceBuf(c)
+        fn(m0, n0, k0, m1, n1, k1, 2, da.ptr(0), *sa, db.ptr(0), *sb, 3, dc.ptr(0), *sc)
+        S.check()
+        got = dc.back()
+    assert skl.skl_b200_last_path() == S.PATH_TCGEN05
+    assert np.array_equal(got[-9:], want[-9:])
+    if t == H.I8:
+        assert np.array_equal(got, want)
+    else:
+        # logical views for the bound
+        A = H.to_f32(t, a).reshape(m1, k1, m0, k0).transpose(0, 2, 1, 3).reshape(M, K)
+        B = H.to_f32(t, b).reshape(n1, k1, n0, k0).transpose(1, 3, 0, 2).reshape(K, N)
+        Cold = c[:M * N].reshape(m1, n1, m0, n0).transpose(0, 2, 1, 3).reshape(M, N)
+        u = 2.0 ** -24
+        bound = 2 * ((1 + u) ** (K + 2) - 1) * (2.0 * np.abs(A).astype(np.float64) @ np.abs(B).astype(np.float64) + 3.0 * np.abs(Cold))
+        diff = np.abs(got[:M * N].astype(np.float64) - want[:M * N].astype(np.float64))
+        diff = diff.reshape(m1, n1, m0, n0).transpose(0, 2, 1, 3).reshape(M, N)
+        assert np.all(diff <= bound + 1e-30)
+
+
+@pytest.mark.parametrize("t", ALL_T)
 @pytest.mark.parametrize("layout", ["rkr", "rrr"])
 def test_tail_round_is_split_into_strips(skl, t, layout, monkeypatch):
     """Tile counts that leave a short last round on a 148-SM part (150 and 160 tiles of 128 x 256): the
