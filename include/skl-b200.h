@@ -206,6 +206,27 @@ SKL_FUNC void skl_gemm_f8e5m2rcprc_f8e5m2rcprc_f32rcprc_sm100a(
     size_t rsb1, size_t csb1, float beta, float *c, size_t rsc0, size_t csc0, size_t rsc1,
     size_t csc1);
 
+/* ------------------------------------------------------------------ GEMM, fp32 and fp64
+ * Same parameter lists as skl_gemm_f32rc_f32rc_f32rc_ref / skl_gemm_f64rc_f64rc_f64rc_ref
+ * (ref/gemm/gemm_f32rc_f32rc_f32rc.h, gemm_f64rc_f64rc_f64rc.h) and their packed forms
+ * (gemm_f32rcprc_f32rcprc_f32rcprc.h, gemm_f64rcprc_f64rcprc_f64rcprc.h).  They run on the CUDA cores
+ * (no TF32: that would change the results): one accumulator per output, k ascending, product and sum each
+ * rounded once, which reproduces the reference compiled without floating-point contraction bit for bit. */
+SKL_FUNC void skl_gemm_f32rc_f32rc_f32rc_sm100a(size_t m, size_t n, size_t k, float alpha, const float *a,
+                                                size_t rsa, size_t csa, const float *b, size_t rsb, size_t csb,
+                                                float beta, float *c, size_t rsc, size_t csc);
+SKL_FUNC void skl_gemm_f32rcprc_f32rcprc_f32rcprc_sm100a(
+    size_t m0, size_t n0, size_t k0, size_t m1, size_t n1, size_t k1, float alpha, const float *a, size_t rsa0,
+    size_t csa0, size_t rsa1, size_t csa1, const float *b, size_t rsb0, size_t csb0, size_t rsb1, size_t csb1,
+    float beta, float *c, size_t rsc0, size_t csc0, size_t rsc1, size_t csc1);
+SKL_FUNC void skl_gemm_f64rc_f64rc_f64rc_sm100a(size_t m, size_t n, size_t k, double alpha, const double *a,
+                                                size_t rsa, size_t csa, const double *b, size_t rsb, size_t csb,
+                                                double beta, double *c, size_t rsc, size_t csc);
+SKL_FUNC void skl_gemm_f64rcprc_f64rcprc_f64rcprc_sm100a(
+    size_t m0, size_t n0, size_t k0, size_t m1, size_t n1, size_t k1, double alpha, const double *a, size_t rsa0,
+    size_t csa0, size_t rsa1, size_t csa1, const double *b, size_t rsb0, size_t csb0, size_t rsb1, size_t csb1,
+    double beta, double *c, size_t rsc0, size_t csc0, size_t rsc1, size_t csc1);
+
 /* ------------------------------------------------------------------ GEMM with the extended epilogue
  * No SKL counterpart: SKL's outputs are always int32 / fp32 with scalar alpha and beta
  * (src/gemm/README.md:41-47).  This entry adds per-row and per-column fp32 scale vectors, mixed

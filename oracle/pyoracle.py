@@ -22,6 +22,7 @@ import numpy as np
 _DIR = os.path.dirname(os.path.abspath(__file__))
 
 I8, BF16, F16, F8E4M3, F8E5M2, F32, I32 = range(7)
+F64 = 7
 _SZ = C.c_size_t
 _VP = C.c_void_p
 _F = C.c_float
@@ -84,6 +85,8 @@ def port():
                                     _F, _I, _VP, _SZ, _SZ]
         lib.orc_gemm_fused.argtypes = [_SZ, _SZ, _SZ, _I, _VP, _SZ, _SZ, _I, _VP, _SZ, _SZ, _F, _VP, _VP, _VP, _VP,
                                        _F, _I, _F, _I, _VP, _SZ, _SZ]
+        lib.orc_gemm_f64.argtypes = [_SZ] * 6 + [C.c_double, _VP] + [_SZ] * 4 + [_VP] + [_SZ] * 4 + \
+            [C.c_double, _VP] + [_SZ] * 4
         lib.orc_activation.argtypes = [_I, _F, _F, _F]
         lib.orc_activation.restype = _F
         lib.orc_pack.argtypes = [_SZ, _SZ, _SZ, _VP, _SZ, _SZ, _SZ, _SZ, _VP, _SZ, _SZ, _SZ, _SZ,
@@ -137,6 +140,14 @@ def ref():
             getattr(lib, f"skl_transpose_e{e}_ref").argtypes = [_SZ, _SZ, _VP, _SZ, _VP, _SZ]
         lib.skl_unpack_e8rcprc_e8rc_ref.argtypes = [_SZ, _SZ, _VP, _SZ, _SZ, _SZ, _SZ, _SZ, _SZ, _VP,
                                                     _SZ, _SZ]
+        lib.skl_gemm_f32rc_f32rc_f32rc_ref.argtypes = [_SZ, _SZ, _SZ, _F, _VP, _SZ, _SZ, _VP, _SZ, _SZ, _F, _VP, _SZ,
+                                                       _SZ]
+        lib.skl_gemm_f64rc_f64rc_f64rc_ref.argtypes = [_SZ, _SZ, _SZ, C.c_double, _VP, _SZ, _SZ, _VP, _SZ, _SZ,
+                                                       C.c_double, _VP, _SZ, _SZ]
+        lib.skl_gemm_f32rcprc_f32rcprc_f32rcprc_ref.argtypes = [_SZ] * 6 + [_F, _VP] + [_SZ] * 4 + [_VP] + \
+            [_SZ] * 4 + [_F, _VP] + [_SZ] * 4
+        lib.skl_gemm_f64rcprc_f64rcprc_f64rcprc_ref.argtypes = [_SZ] * 6 + [C.c_double, _VP] + [_SZ] * 4 + [_VP] + \
+            [_SZ] * 4 + [C.c_double, _VP] + [_SZ] * 4
         if hasattr(lib, "skl_sigmoid_f32_ref"):  # a library built before the activation files were added lacks them
             lib.skl_sigmoid_f32_ref.argtypes = [_VP, _F, _VP, _VP, _VP, _F, _SZ]
             lib.skl_gelu_f32_ref.argtypes = [_VP, _VP, _SZ]

@@ -332,6 +332,34 @@ void orc_gemm_packed_fp_f32(size_t m0, size_t n0, size_t k0, size_t m1, size_t n
   }
 }
 
+/* ref/gemm/gemm_f64rcprc_f64rcprc_f64rcprc.c (and, with one block per dimension, gemm_f64rc_f64rc_f64rc.c:9-22) */
+void orc_gemm_f64(size_t m0, size_t n0, size_t k0, size_t m1, size_t n1, size_t k1, double alpha, const double *a,
+                  size_t rsa0, size_t csa0, size_t rsa1, size_t csa1, const double *b, size_t rsb0, size_t csb0,
+                  size_t rsb1, size_t csb1, double beta, double *c, size_t rsc0, size_t csc0, size_t rsc1,
+                  size_t csc1) {
+  for (size_t bi = 0; bi < m1; ++bi) {
+    for (size_t bj = 0; bj < n1; ++bj) {
+      for (size_t i = 0; i < m0; ++i) {
+        for (size_t j = 0; j < n0; ++j) {
+          double acc = 0.0;
+          for (size_t bp = 0; bp < k1; ++bp) {
+            size_t abase = bi * rsa1 + bp * csa1 + i * rsa0;
+            size_t bbase = bp * rsb1 + bj * csb1 + j * csb0;
+            for (size_t p = 0; p < k0; ++p) {
+              double prod = a[abase + p * csa0] * b[bbase + p * rsb0];
+              acc = acc + prod;
+            }
+          }
+          double *cp = c + bi * rsc1 + bj * csc1 + i * rsc0 + j * csc0;
+          double left = beta * *cp;
+          double right = alpha * acc;
+          *cp = left + right;
+        }
+      }
+    }
+  }
+}
+
 /* ------------------------------------------------------------------ extended epilogue */
 static inline float load_c(int tc, const void *c, size_t idx) {
   if (tc == ORC_I8) {

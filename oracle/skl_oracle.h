@@ -70,6 +70,13 @@ void orc_gemm_fp_f32(size_t m, size_t n, size_t k, float alpha, int ta, const vo
                      size_t csa, int tb, const void *b, size_t rsb, size_t csb, float beta, float *c,
                      size_t rsc, size_t csc);
 
+/* fp64: ref/gemm/gemm_f64rc_f64rc_f64rc.c:9-22 and, packed, gemm_f64rcprc_f64rcprc_f64rcprc.c; fp32 operands
+ * go through orc_gemm_fp_f32 with ta = tb = ORC_F32 (ref/gemm/gemm_f32rc_f32rc_f32rc.c:9-22). */
+void orc_gemm_f64(size_t m0, size_t n0, size_t k0, size_t m1, size_t n1, size_t k1, double alpha, const double *a,
+                  size_t rsa0, size_t csa0, size_t rsa1, size_t csa1, const double *b, size_t rsb0, size_t csb0,
+                  size_t rsb1, size_t csb1, double beta, double *c, size_t rsc0, size_t csc0, size_t rsc1,
+                  size_t csc1);
+
 /* ---- GEMM, packed (blocked 4-D) operands ----
  * int8: ref/gemm/gemm_i8rcprc_i8rcprc_i32rcprc.c:10-37;
  * float: gemm_bf16rcprc_bf16rcprc_f32rcprc.c:9-36 and its f16 / f8 siblings. */

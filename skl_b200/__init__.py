@@ -18,6 +18,7 @@ LIB_PATH = os.path.join(_PKG, "lib", "libskl_b200.so")
 
 # skl_b200_dtype_t
 I8, BF16, F16, F8E4M3, F8E5M2, F32, I32 = range(7)
+F64 = 7
 # skl_b200_path_t
 PATH_NONE, PATH_GENERIC, PATH_TCGEN05, PATH_GEMV = range(4)
 
@@ -60,6 +61,12 @@ SIGNATURES = {
     "skl_gemm_f16c_f16_f32_sm100a": (_GEMM_R_F, None),
     "skl_gemm_f8e4m3c_f8e4m3_f32_sm100a": (_GEMM_R_F, None),
     "skl_gemm_f8e5m2c_f8e5m2_f32_sm100a": (_GEMM_R_F, None),
+    "skl_gemm_f32rc_f32rc_f32rc_sm100a": (_GEMM_RC_F, None),
+    "skl_gemm_f64rc_f64rc_f64rc_sm100a": ([_SZ, _SZ, _SZ, C.c_double, _VP, _SZ, _SZ, _VP, _SZ, _SZ, C.c_double, _VP,
+                                           _SZ, _SZ], None),
+    "skl_gemm_f32rcprc_f32rcprc_f32rcprc_sm100a": (_GEMM_P_F, None),
+    "skl_gemm_f64rcprc_f64rcprc_f64rcprc_sm100a": ([_SZ] * 6 + [C.c_double, _VP] + [_SZ] * 4 + [_VP] + [_SZ] * 4 +
+                                                   [C.c_double, _VP] + [_SZ] * 4, None),
     "skl_gemm_i8rcprc_i8rcprc_i32rcprc_sm100a": (_GEMM_P_I, None),
     "skl_gemm_bf16rcprc_bf16rcprc_f32rcprc_sm100a": (_GEMM_P_F, None),
     "skl_gemm_f16rcprc_f16rcprc_f32rcprc_sm100a": (_GEMM_P_F, None),

@@ -24,7 +24,8 @@ enum {
   SKL_DT_F8E4M3 = 3,
   SKL_DT_F8E5M2 = 4,
   SKL_DT_F32 = 5,
-  SKL_DT_I32 = 6
+  SKL_DT_I32 = 6,
+  SKL_DT_F64 = 7
 };
 
 /* How the accumulator becomes C. */
@@ -32,7 +33,9 @@ enum {
   /* C = beta*C + alpha*acc in int32 two's-complement arithmetic (ref/gemm/gemm_i8rc_i8rc_i32rc.c:23) */
   SKL_EPI_INT = 0,
   /* v = alpha*(float)acc; *row_scale[i]; *col_scale[j]; (+ beta*C when beta != 0); narrow to tc */
-  SKL_EPI_FLOAT = 1
+  SKL_EPI_FLOAT = 1,
+  /* C = beta*C + alpha*acc in double, one rounding per operation (ref/gemm/gemm_f64rc_f64rc_f64rc.c:9-22) */
+  SKL_EPI_F64 = 2
 };
 
 /* Activation applied to the float epilogue's value v (same numbering as skl_b200_activation_t); the
@@ -59,6 +62,7 @@ typedef struct skl_b200_gemm_args {
   int64_t rsc0, csc0, rsc1, csc1;
   int32_t alpha_i, beta_i; /* SKL_EPI_INT   */
   float alpha_f, beta_f;   /* SKL_EPI_FLOAT */
+  double alpha_d, beta_d;  /* SKL_EPI_F64   */
   const float *row_scale;  /* m entries or NULL (SKL_EPI_FLOAT) */
   const float *col_scale;  /* n entries or NULL (SKL_EPI_FLOAT) */
   int32_t col_scale_first; /* 0: v*row_scale then *col_scale (the defined order); 1: the reverse, used

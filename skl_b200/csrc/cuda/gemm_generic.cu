@@ -35,9 +35,11 @@ __device__ __forceinline__ int64_t offs(int64_t r, int64_t c, int64_t r0, int64_
   return (r / r0) * rs1 + (r % r0) * rs0 + (c / c0) * cs1 + (c % c0) * cs0;
 }
 
-template <bool IS_INT, bool BLOCKED>
+// ACC: 0 = int32 (int8 operands), 1 = fp32 (bf16 / f16 / fp8 / f32 operands), 2 = fp64 (f64 operands)
+template <int ACC, bool BLOCKED>
 __global__ void __launch_bounds__(256) gemm_generic_kernel(const GenericParams p) {
-  using acc_t = typename std::conditional<IS_INT, int32_t, float>::type;
+  constexpr bool IS_INT = ACC == 0;
+  using acc_t = typename std::conditional<ACC == 0, int32_t, typename std::conditional<ACC == 1, float, double>::type>::type;
   __shared__ acc_t As[TK][TM + 1];
   __shared__ acc_t Bs[TK][TN + 1];
 
@@ -75,6 +77,8 @@ __global__ void __launch_bounds__(256) gemm_generic_kernel(const GenericParams p
         int64_t o = offs<BLOCKED>(i, kidx, g.m0, g.k0, g.rsa0, g.csa0, g.rsa1, g.csa1);
         if (IS_INT)
           v = (acc_t)((const int8_t *)g.a)[o];
+        else if (ACC == 2)
+          v = (acc_t)((const double *)g.a)[o];
         else
           v = (acc_t)load_as_f32(g.ta, g.a, o);
       }
@@ -97,6 +101,8 @@ __global__ void __launch_bounds__(256) gemm_generic_kernel(const GenericParams p
         int64_t o = offs<BLOCKED>(kidx, j, g.k0, g.n0, g.rsb0, g.csb0, g.rsb1, g.csb1);
         if (IS_INT)
           v = (acc_t)((const int8_t *)g.b)[o];
+        else if (ACC == 2)
+          v = (acc_t)((const double *)g.b)[o];
         else
           v = (acc_t)load_as_f32(g.tb, g.b, o);
       }
@@ -116,6 +122,8 @@ __global__ void __launch_bounds__(256) gemm_generic_kernel(const GenericParams p
         for (int c = 0; c < 4; ++c) {
           if (IS_INT)
             acc[r][c] = (acc_t)((uint32_t)acc[r][c] + (uint32_t)((int32_t)av[r] * (int32_t)bv[c]));
+          else if (ACC == 2)
+            acc[r][c] = (acc_t)__dadd_rn((double)acc[r][c], __dmul_rn((double)av[r], (double)bv[c]));
           else
             acc[r][c] = (acc_t)__fadd_rn((float)acc[r][c], __fmul_rn((float)av[r], (float)bv[c]));
         }
@@ -138,6 +146,10 @@ __global__ void __launch_bounds__(256) gemm_generic_kernel(const GenericParams p
         uint32_t prod = (uint32_t)g.alpha_i * (uint32_t)(int32_t)acc[r][c];
         uint32_t old = (g.beta_i != 0) ? (uint32_t)g.beta_i * (uint32_t)*cp : 0u;
         *cp = (int32_t)(old + prod);
+      } else if (g.epilogue == SKL_EPI_F64) {
+        double *cp = (double *)g.c + o;
+        const double prod = __dmul_rn(g.alpha_d, (double)acc[r][c]);
+        *cp = (g.beta_d != 0.0) ? __dadd_rn(__dmul_rn(g.beta_d, *cp), prod) : prod;
       } else {
         float v = epilogue_value((float)acc[r][c], g.alpha_f, g.row_scale, g.col_scale, i, j);
         if (g.bias) v = __fadd_rn(v, g.bias[g.bias_per_row ? i : j]);
@@ -176,19 +188,25 @@ extern "C" int skl_b200_launch_gemm_generic(const skl_b200_gemm_args *args, void
   if (p.M == 0 || p.N == 0) return 0;
   const bool blocked = !(args->m1 == 1 && args->n1 == 1 && args->k1 == 1);
   const bool is_int = (args->ta == SKL_DT_I8);
+  const bool is_f64 = (args->ta == SKL_DT_F64);
   dim3 grid((unsigned)((p.N + TN - 1) / TN), (unsigned)((p.M + TM - 1) / TM));
   if (grid.y > 65535u) return (int)cudaErrorInvalidConfiguration;
   cudaStream_t s = (cudaStream_t)stream;
   if (is_int) {
     if (blocked)
-      gemm_generic_kernel<true, true><<<grid, 256, 0, s>>>(p);
+      gemm_generic_kernel<0, true><<<grid, 256, 0, s>>>(p);
     else
-      gemm_generic_kernel<true, false><<<grid, 256, 0, s>>>(p);
+      gemm_generic_kernel<0, false><<<grid, 256, 0, s>>>(p);
+  } else if (is_f64) {
+    if (blocked)
+      gemm_generic_kernel<2, true><<<grid, 256, 0, s>>>(p);
+    else
+      gemm_generic_kernel<2, false><<<grid, 256, 0, s>>>(p);
   } else {
     if (blocked)
-      gemm_generic_kernel<false, true><<<grid, 256, 0, s>>>(p);
+      gemm_generic_kernel<1, true><<<grid, 256, 0, s>>>(p);
     else
-      gemm_generic_kernel<false, false><<<grid, 256, 0, s>>>(p);
+      gemm_generic_kernel<1, false><<<grid, 256, 0, s>>>(p);
   }
   SKLB_COUNT_LAUNCH();
   return (int)cudaGetLastError();

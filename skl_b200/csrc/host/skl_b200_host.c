@@ -280,6 +280,7 @@ void skl_b200_shard_columns(size_t n, size_t parts, size_t index, size_t align, 
 /* ------------------------------------------------------------------ staging helpers */
 
 static size_t dt_size(int dt) {
+  if (dt == SKL_DT_F64) return 8;
   return (dt == SKL_DT_F32 || dt == SKL_DT_I32) ? 4 : ((dt == SKL_DT_BF16 || dt == SKL_DT_F16) ? 2 : 1);
 }
 
@@ -372,6 +373,7 @@ static int widen_fp8_operand(skl_b200_gemm_args *g) {
 /* Does the epilogue read C's previous contents (so that a host C has to be copied in first)? */
 static int reads_old_c(const skl_b200_gemm_args *g) {
   if (g->epilogue == SKL_EPI_INT) return g->beta_i != 0;
+  if (g->epilogue == SKL_EPI_F64) return g->beta_d != 0.0;
   return g->beta_f != 0.0f || g->activation == SKL_ACT_SWIGLU;
 }
 
@@ -547,7 +549,7 @@ typedef struct {
 } unblock_t;
 
 static int unblock_operands(skl_b200_gemm_args *g, unblock_t *u) {
-  u->active = 0;
+  memset(u, 0, sizeof *u);
   if (g->m1 == 1 && g->n1 == 1 && g->k1 == 1) return 1;
   const uint64_t M = g->m0 * g->m1, N = g->n0 * g->n1, K = g->k0 * g->k1;
   double threshold = 16777216.0; /* 2^24 multiply-adds */
@@ -558,6 +560,7 @@ static int unblock_operands(skl_b200_gemm_args *g, unblock_t *u) {
   if (K == 0 || (double)M * (double)N * (double)K < threshold) return 1;
   if (g_ctx.force_path == SKL_B200_PATH_GENERIC) return 1;
   if (K > 65536 && g->ta == SKL_DT_I8) return 1; /* the tensor path's int8 limit */
+  if (g->ta == SKL_DT_F32 || g->ta == SKL_DT_F64) return 1; /* no tensor-core kernel for these */
   const size_t ea = dt_size(g->ta), eb = dt_size(g->tb), ec = dt_size(g->tc);
   const size_t ldk_a = (size_t)((K * ea + 15) / 16 * 16) / ea, ldk_b = (size_t)((K * eb + 15) / 16 * 16) / eb;
   const size_t ldc = (size_t)((N * ec + 15) / 16 * 16) / ec;
@@ -816,6 +819,47 @@ SKL_B200_DEF_GEMM_PACKED_F32(skl_gemm_bf16rcprc_bf16rcprc_f32rcprc_sm100a, skl_b
 SKL_B200_DEF_GEMM_PACKED_F32(skl_gemm_f16rcprc_f16rcprc_f32rcprc_sm100a, skl_f16_t, SKL_DT_F16)
 SKL_B200_DEF_GEMM_PACKED_F32(skl_gemm_f8e4m3rcprc_f8e4m3rcprc_f32rcprc_sm100a, uint8_t, SKL_DT_F8E4M3)
 SKL_B200_DEF_GEMM_PACKED_F32(skl_gemm_f8e5m2rcprc_f8e5m2rcprc_f32rcprc_sm100a, uint8_t, SKL_DT_F8E5M2)
+
+/* fp32 and fp64 GEMMs (ref/gemm/gemm_f32rc_f32rc_f32rc.c:9-22, gemm_f64rc_f64rc_f64rc.c:9-22 and the packed forms):
+ * on the any-stride kernel, one accumulator per output, k ascending, product and sum rounded separately. */
+void skl_gemm_f32rc_f32rc_f32rc_sm100a(size_t m, size_t n, size_t k, float alpha, const float *a, size_t rsa,
+                                       size_t csa, const float *b, size_t rsb, size_t csb, float beta, float *c,
+                                       size_t rsc, size_t csc) {
+  gemm_plain(SKL_DT_F32, SKL_DT_F32, SKL_DT_F32, SKL_EPI_FLOAT, m, n, k, a, rsa, csa, b, rsb, csb, c, rsc, csc, 0, 0,
+             alpha, beta, 0, 0, 0, 0, SKL_ACT_NONE, 0.0f);
+}
+void skl_gemm_f32rcprc_f32rcprc_f32rcprc_sm100a(size_t m0, size_t n0, size_t k0, size_t m1, size_t n1, size_t k1,
+                                                float alpha, const float *a, size_t rsa0, size_t csa0, size_t rsa1,
+                                                size_t csa1, const float *b, size_t rsb0, size_t csb0, size_t rsb1,
+                                                size_t csb1, float beta, float *c, size_t rsc0, size_t csc0,
+                                                size_t rsc1, size_t csc1) {
+  gemm_packed(SKL_DT_F32, SKL_DT_F32, SKL_EPI_FLOAT, m0, n0, k0, m1, n1, k1, a, rsa0, csa0, rsa1, csa1, b, rsb0, csb0,
+              rsb1, csb1, c, rsc0, csc0, rsc1, csc1, 0, 0, alpha, beta);
+}
+void skl_gemm_f64rcprc_f64rcprc_f64rcprc_sm100a(size_t m0, size_t n0, size_t k0, size_t m1, size_t n1, size_t k1,
+                                                double alpha, const double *a, size_t rsa0, size_t csa0,
+                                                size_t rsa1, size_t csa1, const double *b, size_t rsb0,
+                                                size_t csb0, size_t rsb1, size_t csb1, double beta, double *c,
+                                                size_t rsc0, size_t csc0, size_t rsc1, size_t csc1) {
+  skl_b200_gemm_args g;
+  memset(&g, 0, sizeof g);
+  g.m0 = m0; g.n0 = n0; g.k0 = k0;
+  g.m1 = m1; g.n1 = n1; g.k1 = k1;
+  g.ta = SKL_DT_F64; g.tb = SKL_DT_F64; g.tc = SKL_DT_F64;
+  g.epilogue = SKL_EPI_F64;
+  g.a = a; g.b = b; g.c = c;
+  g.rsa0 = (int64_t)rsa0; g.csa0 = (int64_t)csa0; g.rsa1 = (int64_t)rsa1; g.csa1 = (int64_t)csa1;
+  g.rsb0 = (int64_t)rsb0; g.csb0 = (int64_t)csb0; g.rsb1 = (int64_t)rsb1; g.csb1 = (int64_t)csb1;
+  g.rsc0 = (int64_t)rsc0; g.csc0 = (int64_t)csc0; g.rsc1 = (int64_t)rsc1; g.csc1 = (int64_t)csc1;
+  g.alpha_d = alpha; g.beta_d = beta;
+  run_gemm(&g);
+}
+void skl_gemm_f64rc_f64rc_f64rc_sm100a(size_t m, size_t n, size_t k, double alpha, const double *a, size_t rsa,
+                                       size_t csa, const double *b, size_t rsb, size_t csb, double beta, double *c,
+                                       size_t rsc, size_t csc) {
+  skl_gemm_f64rcprc_f64rcprc_f64rcprc_sm100a(m, n, k, 1, 1, 1, alpha, a, rsa, csa, 0, 0, b, rsb, csb, 0, 0, beta, c, rsc,
+                                             csc, 0, 0);
+}
 
 /* extended epilogue */
 static int is_f8(int t) { return t == SKL_DT_F8E4M3 || t == SKL_DT_F8E5M2; }

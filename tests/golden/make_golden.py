@@ -186,6 +186,17 @@ def main():
             ref.skl_gelu_f32_ref(P(out), P(x), x.size)
         store[f"act_{name}_x"], store[f"act_{name}_up"], store[f"act_{name}_out"] = x, up, out
 
+    # ---- fp32 / fp64 GEMM (plain strides), skl_gemm_f32rc_f32rc_f32rc_ref / skl_gemm_f64rc_f64rc_f64rc_ref
+    g = H.rng(88)
+    for name, dt in (("f32", np.float32), ("f64", np.float64)):
+        m, n, k = 9, 11, 23
+        a = g.normal(0, 1, (m, k)).astype(dt)
+        b = g.normal(0, 1, (k, n)).astype(dt)
+        c = g.normal(0, 1, (m, n)).astype(dt)
+        out = c.copy()
+        getattr(ref, f"skl_gemm_{name}rc_{name}rc_{name}rc_ref")(m, n, k, 1.25, P(a), k, 1, P(b), n, 1, -0.5, P(out), n, 1)
+        store[f"gemm_{name}_a"], store[f"gemm_{name}_b"], store[f"gemm_{name}_c"], store[f"gemm_{name}_out"] = a, b, c, out
+
     path = os.path.join(HERE, "skl_ref_golden.npz")
     np.savez_compressed(path, **store)
     print(path, os.path.getsize(path), "bytes,", len(store), "arrays")

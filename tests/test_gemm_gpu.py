@@ -247,3 +247,57 @@ def test_large_host_operands_take_the_row_chunk_pipeline(skl, beta, monkeypatch)
         orc.port_gemm_rc(H.BF16, H.BF16, 1, n, k, 1.5, a[r:], k, 1, b, n, 1, beta, want, n, 1)
         bound = H.skl_forward_bound(H.BF16, a[r:r + 1], H.BF16, b, 1.5, beta, c0[r:r + 1, :n], k)
         assert np.all(np.abs(outs[0][r:r + 1, :n].astype(np.float64) - want) <= bound)
+
+
+@pytest.mark.parametrize("name,dt", [("f32", np.float32), ("f64", np.float64)])
+@pytest.mark.parametrize("where", ["device", "host"])
+def test_f32_and_f64_gemm_are_bit_exact(skl, name, dt, where):
+    """ref/gemm/gemm_f32rc_f32rc_f32rc.c:9-22 and gemm_f64rc_f64rc_f64rc.c:9-22 (+ packed): one accumulator per
+    output, k ascending, separately rounded product and sum -- the any-stride kernel reproduces the oracle exactly
+    (beta != 0 so that C is read on both sides)."""
+    from oracle import pyoracle as orc
+    from gpu_common import DeviceBuf
+
+    P = orc._p
+    port = orc.port()
+    g = H.rng(61)
+    rc = getattr(skl, f"skl_gemm_{name}rc_{name}rc_{name}rc_sm100a")
+    pk = getattr(skl, f"skl_gemm_{name}rcprc_{name}rcprc_{name}rcprc_sm100a")
+    for (m, n, k, col_major_b) in [(1, 1, 1, 0), (17, 33, 65, 0), (130, 70, 257, 1), (5, 9, 0, 0)]:
+        kk = max(k, 1)
+        a = g.normal(0, 1, (m, kk)).astype(dt)
+        b = g.normal(0, 1, (n, kk) if col_major_b else (kk, n)).astype(dt)
+        rsb, csb = (1, kk) if col_major_b else (n, 1)
+        c = g.normal(0, 1, m * (n + 3) + 5).astype(dt)  # padded rows and a tail the call must not touch
+        want = c.copy()
+        if name == "f32":
+            port.orc_gemm_fp_f32(m, n, k, 1.5, H.F32, P(a), kk, 1, H.F32, P(b), rsb, csb, 0.75, P(want), n + 3, 1)
+        else:
+            port.orc_gemm_f64(m, n, k, 1, 1, 1, 1.5, P(a), kk, 1, 0, 0, P(b), rsb, csb, 0, 0, 0.75, P(want), n + 3, 1, 0, 0)
+        if where == "host":
+            got = c.copy()
+            rc(m, n, k, 1.5, S.ptr(a), kk, 1, S.ptr(b), rsb, csb, 0.75, S.ptr(got), n + 3, 1)
+            S.check()
+        else:
+            da, db, dc = DeviceBuf(a), DeviceBuf(b), DeviceBuf(c)
+            rc(m, n, k, 1.5, da.ptr(0), kk, 1, db.ptr(0), rsb, csb, 0.75, dc.ptr(0), n + 3, 1)
+            S.check()
+            got = dc.back()
+        assert skl.skl_b200_last_path() == S.PATH_GENERIC
+        assert np.array_equal(got, want)
+    m0, n0, k0, m1, n1, k1 = 4, 3, 2, 5, 7, 9
+    sa = (k0, 1, k1 * m0 * k0, m0 * k0)
+    sb = (1, k0, n1 * k0 * n0, k0 * n0)
+    sc = (1, m0, m0 * n0, m1 * m0 * n0)
+    a = g.normal(0, 1, m1 * k1 * m0 * k0).astype(dt)
+    b = g.normal(0, 1, k1 * n1 * k0 * n0).astype(dt)
+    c = g.normal(0, 1, m1 * n1 * m0 * n0 + 7).astype(dt)
+    want = c.copy()
+    if name == "f32":
+        port.orc_gemm_packed_fp_f32(m0, n0, k0, m1, n1, k1, 2.0, H.F32, P(a), *sa, H.F32, P(b), *sb, 3.0, P(want), *sc)
+    else:
+        port.orc_gemm_f64(m0, n0, k0, m1, n1, k1, 2.0, P(a), *sa, P(b), *sb, 3.0, P(want), *sc)
+    got = c.copy()
+    pk(m0, n0, k0, m1, n1, k1, 2.0, S.ptr(a), *sa, S.ptr(b), *sb, 3.0, S.ptr(got), *sc)
+    S.check()
+    assert np.array_equal(got, want)

@@ -121,3 +121,17 @@ def test_activation_port_matches_reference_vectors(name):
     x, up, want = GOLD[f"act_{name}_x"], GOLD[f"act_{name}_up"], GOLD[f"act_{name}_out"]
     got = np.array([fn(act, p, float(v), float(u)) for v, u in zip(x, up)], dtype=np.float32)
     assert np.array_equal(got.view(np.uint32), want.view(np.uint32)) or np.array_equal(got, want, equal_nan=True)
+
+
+def test_f32_f64_gemm_port_matches_reference_vectors():
+    port = orc.port()
+    for name in ("f32", "f64"):
+        a, b, c, want = (GOLD[f"gemm_{name}_{x}"] for x in ("a", "b", "c", "out"))
+        m, k = a.shape
+        n = b.shape[1]
+        got = c.copy()
+        if name == "f32":
+            port.orc_gemm_fp_f32(m, n, k, 1.25, H.F32, P(a), k, 1, H.F32, P(b), n, 1, -0.5, P(got), n, 1)
+        else:
+            port.orc_gemm_f64(m, n, k, 1, 1, 1, 1.25, P(a), k, 1, 0, 0, P(b), n, 1, 0, 0, -0.5, P(got), n, 1, 0, 0)
+        assert np.array_equal(got, want)

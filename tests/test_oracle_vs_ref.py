@@ -133,3 +133,41 @@ def test_fused_activation_equals_reference_elementwise_routine_on_the_gemm_resul
         orc.port_gemm_fused(m, n, k, H.BF16, A.view, k, 1, H.BF16, B.view, n, 1, 4.0, None, None, None, None, 0.0,
                             H.F32, got, n, 1, activation=act, act_param=p)
         assert np.array_equal(got, want, equal_nan=True), (act, p)
+
+
+def test_f32_and_f64_gemm_port_equals_reference():
+    """fp32 operands through orc_gemm_fp_f32 and fp64 through orc_gemm_f64 against skl_gemm_f32rc_f32rc_f32rc_ref /
+    skl_gemm_f64rc_f64rc_f64rc_ref and the packed forms: bit for bit (same order, no contraction on either side)."""
+    ref, port = orc.ref(), orc.port()
+    g = H.rng(5)
+    for (m, n, k) in [(1, 1, 1), (7, 5, 9), (33, 17, 40), (4, 6, 0)]:
+        for dt in (np.float32, np.float64):
+            a = g.normal(0, 1, (m, max(k, 1))).astype(dt)
+            b = g.normal(0, 1, (max(k, 1), n)).astype(dt)
+            c0 = g.normal(0, 1, (m, n)).astype(dt)
+            c1 = c0.copy()
+            ld = max(k, 1)
+            if dt is np.float32:
+                ref.skl_gemm_f32rc_f32rc_f32rc_ref(m, n, k, 1.5, P(a), ld, 1, P(b), n, 1, 0.5, P(c0), n, 1)
+                port.orc_gemm_fp_f32(m, n, k, 1.5, H.F32, P(a), ld, 1, H.F32, P(b), n, 1, 0.5, P(c1), n, 1)
+            else:
+                ref.skl_gemm_f64rc_f64rc_f64rc_ref(m, n, k, 1.5, P(a), ld, 1, P(b), n, 1, 0.5, P(c0), n, 1)
+                port.orc_gemm_f64(m, n, k, 1, 1, 1, 1.5, P(a), ld, 1, 0, 0, P(b), n, 1, 0, 0, 0.5, P(c1), n, 1, 0, 0)
+            assert np.array_equal(c0, c1)
+    # packed: blocks 4 x 3 x 2, counts 3 x 2 x 5, column-major inside C's blocks
+    m0, n0, k0, m1, n1, k1 = 4, 3, 2, 3, 2, 5
+    sa = (k0, 1, k1 * m0 * k0, m0 * k0)
+    sb = (1, k0, n1 * k0 * n0, k0 * n0)
+    sc = (1, m0, m0 * n0, m1 * m0 * n0)
+    for dt in (np.float32, np.float64):
+        a = g.normal(0, 1, m1 * k1 * m0 * k0).astype(dt)
+        b = g.normal(0, 1, k1 * n1 * k0 * n0).astype(dt)
+        c0 = g.normal(0, 1, m1 * n1 * m0 * n0).astype(dt)
+        c1 = c0.copy()
+        if dt is np.float32:
+            ref.skl_gemm_f32rcprc_f32rcprc_f32rcprc_ref(m0, n0, k0, m1, n1, k1, 2.0, P(a), *sa, P(b), *sb, 3.0, P(c0), *sc)
+            port.orc_gemm_packed_fp_f32(m0, n0, k0, m1, n1, k1, 2.0, H.F32, P(a), *sa, H.F32, P(b), *sb, 3.0, P(c1), *sc)
+        else:
+            ref.skl_gemm_f64rcprc_f64rcprc_f64rcprc_ref(m0, n0, k0, m1, n1, k1, 2.0, P(a), *sa, P(b), *sb, 3.0, P(c0), *sc)
+            port.orc_gemm_f64(m0, n0, k0, m1, n1, k1, 2.0, P(a), *sa, P(b), *sb, 3.0, P(c1), *sc)
+        assert np.array_equal(c0, c1)
