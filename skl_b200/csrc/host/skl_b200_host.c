@@ -491,14 +491,31 @@ static int run_gemm_pipelined(skl_b200_gemm_args *g, int a_host, int c_host, int
   if (!cuda_ok(cudaEventRecord(g_ctx.ev_ready, main_s))) return 1;
   if (!cuda_ok(cudaStreamWaitEvent(g_ctx.s_out, g_ctx.ev_ready, 0))) return 1;
 
-  int chunks = (int)(M / 2048);
-  if (chunks > PIPE_MAX_CHUNKS) chunks = PIPE_MAX_CHUNKS;
-  if (chunks < 2) chunks = 2;
-  const uint64_t rows_per = ((M + chunks - 1) / chunks + 255) / 256 * 256; /* whole 256-row tiles */
+  /* Chunk schedule (whole 256-row tiles): 256, 512, 1024 rows first, so that the device->host direction -- the
+   * longer one -- starts as early as possible and then never waits for a chunk, then equal chunks of about
+   * 2048 rows. */
+  uint64_t sizes[PIPE_MAX_CHUNKS];
+  int n_chunks = 0;
+  {
+    uint64_t left = M;
+    for (uint64_t ramp = 256; ramp <= 1024 && left > 4096; ramp *= 2) {
+      sizes[n_chunks++] = ramp;
+      left -= ramp;
+    }
+    int rest = (int)((left + 2047) / 2048);
+    if (rest > PIPE_MAX_CHUNKS - n_chunks) rest = PIPE_MAX_CHUNKS - n_chunks;
+    if (rest < 1) rest = 1;
+    const uint64_t rows_per = ((left + rest - 1) / rest + 255) / 256 * 256;
+    while (left > 0) {
+      const uint64_t r = left < rows_per ? left : rows_per;
+      sizes[n_chunks++] = r;
+      left -= r;
+    }
+  }
   const int need_old = reads_old_c(g);
-  int c_idx = 0;
-  for (uint64_t i0 = 0; i0 < M; i0 += rows_per, ++c_idx) {
-    const uint64_t rows = (M - i0) < rows_per ? (M - i0) : rows_per;
+  uint64_t i0 = 0;
+  for (int c_idx = 0; c_idx < n_chunks; i0 += sizes[c_idx], ++c_idx) {
+    const uint64_t rows = sizes[c_idx];
     const size_t a_off = (size_t)(i0 * (uint64_t)g->rsa0) * ea, c_off = (size_t)(i0 * (uint64_t)g->rsc0) * ec;
     if (a_host) {
       if (!cuda_ok(cudaMemcpy2DAsync(dev_a + a_off, (size_t)g->rsa0 * ea, (const uint8_t *)host_a + a_off,

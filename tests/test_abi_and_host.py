@@ -96,3 +96,20 @@ def test_no_device_means_error_not_fallback(skl):
     assert np.all(c == 7)
     with pytest.raises(S.SklB200Error):
         S.check()
+
+
+def test_fused_struct_layout_matches_the_header(tmp_path):
+    """The ctypes mirror of skl_b200_fused_t must have the C compiler's size and field offsets."""
+    import ctypes
+    import subprocess
+
+    fields = [name for name, _ in S.Fused._fields_]
+    src = tmp_path / "layout.c"
+    prints = "\n".join(f'  printf("%zu\\n", offsetof(skl_b200_fused_t, {f}));' for f in fields)
+    src.write_text('#include <stdio.h>\n#include <stddef.h>\n#include "skl-b200.h"\nint main(void) {\n'
+                   '  printf("%zu\\n", sizeof(skl_b200_fused_t));\n' + prints + "\n  return 0;\n}\n")
+    exe = tmp_path / "layout"
+    subprocess.check_call(["gcc", "-std=c99", "-I", os.path.join(ROOT, "include"), str(src), "-o", str(exe)])
+    out = [int(x) for x in subprocess.check_output([str(exe)]).split()]
+    assert out[0] == ctypes.sizeof(S.Fused)
+    assert out[1:] == [getattr(S.Fused, f).offset for f in fields]
