@@ -6,14 +6,20 @@
 // and the epilogue warps apply alpha/beta, scale vectors and the output narrowing on the way out.
 //
 // One CTA = one 128 x BN output tile at a time, persistent over a static tile schedule
-// (tile = blockIdx.x + i*gridDim.x).  192 threads in three roles:
+// (unit = blockIdx.x + i*gridDim.x; tiles are visited in L2-sized groups of m-tiles, and the tiles left
+// after the last full round are cut into column strips, one per CTA).  192 threads in three roles:
 //   warp 0      TMA producer: one lane issues cp.async.bulk.tensor loads of the A and B k-slabs
 //               (128 bytes of K per slab, 128-byte swizzle) into a ring of shared-memory stages;
 //   warp 1      MMA issuer: allocates TMEM, and one lane issues 4 tcgen05.mma (K = 32 bytes each) per
 //               stage, then tcgen05.commit to hand the stage back / to publish the finished tile;
-//   warps 2..5  epilogue: tcgen05.ld 32 columns at a time from the finished accumulator
-//               (two accumulators in TMEM, so tile i+1's MMAs overlap tile i's epilogue), apply the
-//               epilogue and store C with 16-byte stores where alignment allows.
+//   warps 2..5  epilogue: each warp first copies the tile's column scales / bias into its own
+//               shared-memory slice, then reads the finished accumulator with tcgen05.ld 32 columns at
+//               a time (two accumulators in TMEM, so tile i+1's MMAs overlap tile i's epilogue),
+//               applies alpha/beta, scales, bias, activation and narrowing, and writes the 32 x 32
+//               chunk through swizzled shared-memory staging and a TMA store (16-byte or element
+//               stores when C is not a row-major matrix with 16-byte rows).
+// The kernel is launched as a programmatic dependent of the kernel before it on the stream and waits
+// for that kernel (griddepcontrol.wait) only after its own set-up.
 // Operands may be K-major (k contiguous) or MN-major (m or n contiguous) in global memory; the
 // shared-memory matrix descriptors and the instruction descriptor carry the difference, no
 // transposing pre-pass is needed.  Edges in M, N and K rely on TMA zero fill.
@@ -1262,18 +1268,21 @@ int pair_mode() {
   return atoi(e);
 }
 
-// Is the two-CTA kernel usable / worthwhile for this problem?  Measured on B200 against the one-CTA
-// kernel at equal data: it moves a third less data from L2 to the SMs and runs at a higher clock under
-// the power cap, but keeps the tensor pipe slightly less busy; the net effect is a few percent gain
-// for int8 and a few percent loss for bf16 / fp8, so the default uses it for int8 only.
+// Is the two-CTA kernel usable / worthwhile for this problem?  Measured on B200 against the one-CTA kernel at
+// equal data: it moves a third less data from L2 to the SMs and runs at a higher clock under the power cap;
+// the net effect is +2-7 % for int8, +2 % for fp8 and under 1 % for bf16.  It has no tail strips, so it is
+// chosen for the 8-bit kinds only and only when its last round of 256 x 256 tiles is nearly full.
 bool use_pair_kernel(int kind, int64_t M, int64_t N, const OperandView &vb) {
   const int mode = pair_mode();
   if (mode == 0) return false;
   (void)vb;
   if (mode == 2) return N > 16;
-  // needs at least two 128-row slabs per tile to be useful and enough tiles to fill the machine
-  const int64_t tiles = ((M + 255) / 256) * ((N + 255) / 256);
-  return kind == KIND_I8 && M > 128 && tiles >= sm_count() / 2;
+  if (kind == KIND_F16 || M <= 128) return false;
+  const int64_t tiles = ((M + 255) / 256) * ((N + 255) / 256), pairs = sm_count() / 2;
+  if (tiles < pairs) return false;
+  const int64_t rounds = (tiles + pairs - 1) / pairs;
+  const double fill = (double)tiles / (double)(rounds * pairs);
+  return kind == KIND_I8 ? fill >= 0.85 : fill >= 0.95;
 }
 
 }  // namespace
