@@ -526,14 +526,29 @@ def main() -> None:
 
     # ---------------- end to end: pinned host buffers through the same call
     lib.skl_b200_set_async(0)
-    xh = x.cpu().pin_memory()
     w8h = w8.cpu().pin_memory()
     sh = scale.cpu().pin_memory()
     ch = torch.empty((m, ncols), dtype=torch.bfloat16).pin_memory()
+    gather_x = bool(dist) and world > 1 and m % world == 0
+    if gather_x:
+        # X is replicated on the devices but need not cross PCIe N times: each rank uploads its own m/N rows and
+        # the ranks all-gather them over NVLink (NCCL); W, the scales and C stay host buffers of the library call.
+        rows = m // world
+        xh = x[rank * rows:(rank + 1) * rows].cpu().pin_memory()
+        x_part = torch.empty((rows, k), dtype=torch.bfloat16, device="cuda")
+        x_all = torch.empty((m, k), dtype=torch.bfloat16, device="cuda")
 
-    def step_host():
-        lib.skl_gemm_ex_sm100a(m, ncols, k, S.BF16, xh.data_ptr(), k, 1, S.F8E4M3, w8h.data_ptr(), ncols, 1, 1.0, None,
-                               sh.data_ptr(), 0.0, S.BF16, ch.data_ptr(), ncols, 1)
+        def step_host():
+            x_part.copy_(xh, non_blocking=True)
+            dist.all_gather_into_tensor(x_all, x_part)
+            lib.skl_gemm_ex_sm100a(m, ncols, k, S.BF16, x_all.data_ptr(), k, 1, S.F8E4M3, w8h.data_ptr(), ncols, 1, 1.0,
+                                   None, sh.data_ptr(), 0.0, S.BF16, ch.data_ptr(), ncols, 1)
+    else:
+        xh = x.cpu().pin_memory()
+
+        def step_host():
+            lib.skl_gemm_ex_sm100a(m, ncols, k, S.BF16, xh.data_ptr(), k, 1, S.F8E4M3, w8h.data_ptr(), ncols, 1, 1.0,
+                                   None, sh.data_ptr(), 0.0, S.BF16, ch.data_ptr(), ncols, 1)
 
     e2e_steps = max(3, min(args.steps, 8))
     for _ in range(2):
@@ -569,7 +584,10 @@ def main() -> None:
         "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": workload_config(world),
         "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                "ms_per_step": ms_e2e, "steps": e2e_steps, "matches_device_run": same},
+                "ms_per_step": ms_e2e, "steps": e2e_steps, "matches_device_run": same,
+                "bytes_are": "per rank",
+                "x_distribution": ("each rank uploads m/N rows, all-gather over NVLink (NCCL)" if gather_x
+                                   else "uploaded whole by the library call")},
         "gpu_launches": launches_per_step * args.steps,
         "launches_per_step": launches_per_step,
         "clocks": clk.summary(),
