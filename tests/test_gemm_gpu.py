@@ -301,3 +301,29 @@ def test_f32_and_f64_gemm_are_bit_exact(skl, name, dt, where):
     pk(m0, n0, k0, m1, n1, k1, 2.0, S.ptr(a), *sa, S.ptr(b), *sb, 3.0, S.ptr(got), *sc)
     S.check()
     assert np.array_equal(got, want)
+
+
+@pytest.mark.parametrize("m,n,k,expect", [(1, 300, 512, S.PATH_GEMV), (200, 300, 512, S.PATH_TCGEN05),
+                                          (33, 17, 48, S.PATH_GENERIC)])
+def test_int32_wrap_around_in_alpha_and_beta(skl, m, n, k, expect):
+    """C = beta*C + alpha*acc in two's-complement int32 (ref/gemm/gemm_i8rc_i8rc_i32rc.c:23): factors large enough
+    that both products wrap many times; every kernel family must reproduce the reference's wrapped values."""
+    from oracle import pyoracle as orc
+    from gpu_common import DeviceBuf
+
+    P = orc._p
+    g = H.rng(m + n)
+    a = g.integers(-128, 128, size=(m, k), dtype=np.int8)
+    b = g.integers(-128, 128, size=(n, k), dtype=np.int8)  # [N][K]
+    c = g.integers(-2**31, 2**31, size=(m, n), dtype=np.int64).astype(np.int32)
+    alpha, beta = 0x01000001, -0x7FFFFFF
+    want = c.copy()
+    orc.port().orc_gemm_i8_i32(m, n, k, alpha, P(a), k, 1, P(b), 1, k, beta, P(want), n, 1)
+    da, db, dc = DeviceBuf(a), DeviceBuf(b), DeviceBuf(c)
+    skl.skl_gemm_i8rc_i8rc_i32rc_sm100a(m, n, k, alpha, da.ptr(0), k, 1, db.ptr(0), 1, k, beta, dc.ptr(0), n, 1)
+    S.check()
+    assert skl.skl_b200_last_path() == expect
+    assert np.array_equal(dc.back(), want)
+    # the accumulator really wrapped in the reference arithmetic
+    exact = beta * c.astype(object) + alpha * (a.astype(np.int64) @ b.astype(np.int64).T).astype(object)
+    assert any(abs(int(v)) >= 2**31 for v in exact.ravel()[:64])

@@ -171,3 +171,19 @@ def test_f32_and_f64_gemm_port_equals_reference():
             ref.skl_gemm_f64rcprc_f64rcprc_f64rcprc_ref(m0, n0, k0, m1, n1, k1, 2.0, P(a), *sa, P(b), *sb, 3.0, P(c0), *sc)
             port.orc_gemm_f64(m0, n0, k0, m1, n1, k1, 2.0, P(a), *sa, P(b), *sb, 3.0, P(c1), *sc)
         assert np.array_equal(c0, c1)
+
+
+def test_int8_wrap_around_equals_reference():
+    """alpha and beta large enough that beta*C and alpha*acc wrap in int32: the port's unsigned arithmetic must
+    give what the reference's signed expression gives on this target."""
+    ref, port = orc.ref(), orc.port()
+    g = H.rng(17)
+    m, n, k = 9, 13, 96
+    a = g.integers(-128, 128, size=(m, k), dtype=np.int8)
+    b = g.integers(-128, 128, size=(k, n), dtype=np.int8)
+    c0 = g.integers(-2**31, 2**31, size=(m, n), dtype=np.int64).astype(np.int32)
+    c1 = c0.copy()
+    alpha, beta = 0x01000001, -0x7FFFFFF
+    ref.skl_gemm_i8rc_i8rc_i32rc_ref(m, n, k, alpha, P(a), k, 1, P(b), n, 1, beta, P(c0), n, 1)
+    port.orc_gemm_i8_i32(m, n, k, alpha, P(a), k, 1, P(b), n, 1, beta, P(c1), n, 1)
+    assert np.array_equal(c0, c1)
