@@ -237,6 +237,21 @@ def make_workloads(torch, S, lib):
             lib.skl_gemm_i8_i8_i32_sm100a(m, n, k, 1, a.data_ptr(), k, b.data_ptr(), n, 0, c.data_ptr(), n)
         return call, 2.0 * m * n * k, "tflops", 20
 
+    def c5_static():
+        # the headline shape with the weights declared static: W is widened by the first call only
+        m, k, n = M_C5, K_C5, N_C5
+        x = (torch.randn((m, k), device=dev, generator=g)).to(torch.bfloat16)
+        w = torch.randint(0, 256, (k, n), dtype=torch.uint8, device=dev, generator=g) & 0x77
+        sc = torch.rand((n,), device=dev, generator=g) * 1e-2 + 1e-3
+        c = torch.empty((m, n), dtype=torch.bfloat16, device=dev)
+
+        def call():
+            lib.skl_b200_set_static_weights(1)
+            lib.skl_gemm_ex_sm100a(m, n, k, S.BF16, x.data_ptr(), k, 1, S.F8E4M3, w.data_ptr(), n, 1, 1.0, None,
+                                   sc.data_ptr(), 0.0, S.BF16, c.data_ptr(), n, 1)
+            lib.skl_b200_set_static_weights(0)
+        return call, 2.0 * m * n * k, "tflops", 20
+
     def int8_packed(force_simt):
         def build():
             # SKL's packed entry point on an mmt4d-style layout: A [m1][k1][16][8], B [n1][k1][16][8], C [m1][n1][16][16]
@@ -343,6 +358,7 @@ def make_workloads(torch, S, lib):
         return call, 4.0 * m * n, "gbs", 10
 
     W["int8_8192_i32out"] = int8_8192
+    W["c5_static_weights"] = c5_static
     W["int8_4096_packed_i32out"] = int8_packed(False)
     W["int8_1024_packed_i32out_simt_kernel"] = int8_packed(True)
     W["fp8_e4m3xe4m3_8192_bf16out"] = fp8(S.F8E4M3, 1e-3)

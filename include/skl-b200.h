@@ -91,7 +91,9 @@ SKL_FUNC void skl_b200_release_workspace(void);
 /* Declares, for this thread's following calls, that the B operands (the weights) are static: nothing queued
  * earlier on the stream writes them.  The skinny int8 kernel (m <= 2) then launches as a programmatic
  * dependent of the preceding kernel: it starts streaming its weights while that kernel drains and waits for
- * it only before reading the activations, scales, bias or C.  Off by default; results are identical. */
+ * it only before reading the activations, scales, bias or C.  A static fp8 B of a bf16 x fp8 GEMM is widened to
+ * bf16 by the first call only; later calls with the same matrix reuse that copy.  Off by default; results are
+ * identical. */
 SKL_FUNC void skl_b200_set_static_weights(int enabled);
 
 /* Which kernel family served the calling thread's last GEMM call (for tests and benchmarks). */

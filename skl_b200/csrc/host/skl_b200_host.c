@@ -37,6 +37,11 @@ typedef struct {
   void *stream;
   int async;
   int static_weights; /* skl_b200_set_static_weights */
+  /* widened copy of a static fp8 B kept from the previous call: source, geometry, format, where it lives */
+  const void *wide_src;
+  size_t wide_rows, wide_cols, wide_ld;
+  int wide_fmt;
+  void *wide_ptr; /* 0 = nothing cached */
   skl_b200_status_t status;
   char cuda_err[192];
   skl_b200_path_t last_path;
@@ -75,6 +80,7 @@ static void release_resources(void) {
     if (g_ctx.ws[i].ptr) (void)cudaFree(g_ctx.ws[i].ptr);
     g_ctx.ws[i].ptr = 0;
     g_ctx.ws[i].cap = 0;
+    g_ctx.wide_ptr = 0;
   }
   if (g_ctx.dev_status) (void)cudaFreeHost(g_ctx.dev_status);
   g_ctx.dev_status = 0;
@@ -140,6 +146,7 @@ static void *workspace(int slot, size_t bytes) {
       (void)cudaFree(w->ptr);
       w->ptr = 0;
       w->cap = 0;
+      if (slot == WS_WIDEN) g_ctx.wide_ptr = 0;
     }
     size_t want = bytes + bytes / 8 + 256;
     void *p = 0;
@@ -198,7 +205,10 @@ const char *skl_b200_status_string(skl_b200_status_t s) {
 }
 
 const char *skl_b200_last_cuda_error(void) { return g_ctx.cuda_err; }
-void skl_b200_set_stream(void *cuda_stream) { g_ctx.stream = cuda_stream; }
+void skl_b200_set_stream(void *cuda_stream) {
+  if (cuda_stream != g_ctx.stream) g_ctx.wide_ptr = 0; /* the cached widened B was produced in the old stream's order */
+  g_ctx.stream = cuda_stream;
+}
 void *skl_b200_get_stream(void) { return g_ctx.stream; }
 void skl_b200_set_async(int enabled) { g_ctx.async = enabled != 0; }
 void skl_b200_set_static_weights(int enabled) { g_ctx.static_weights = enabled != 0; }
@@ -355,8 +365,24 @@ static int widen_fp8_operand(skl_b200_gemm_args *g) {
   size_t ld_dst = (cols + 7) & ~(size_t)7; /* 16-byte aligned rows */
   void *wide = workspace(WS_WIDEN, rows * ld_dst * 2);
   if (!wide) return 0;
-  if (!cuda_ok((cudaError_t)skl_b200_launch_cvt_f8_to_bf16_2d(wide, ld_dst, g->b, ld_src, g->tb, rows, cols, g_ctx.stream)))
-    return 0;
+  /* Weights declared static (skl_b200_set_static_weights) are widened once: the copy made by the previous call is
+   * reused while the same matrix keeps arriving.  Anything else is widened afresh, which also drops the cached copy. */
+  const int cached = g->b_static && g_ctx.wide_ptr == wide && g_ctx.wide_src == g->b && g_ctx.wide_rows == rows &&
+                     g_ctx.wide_cols == cols && g_ctx.wide_ld == ld_src && g_ctx.wide_fmt == g->tb;
+  if (!cached) {
+    g_ctx.wide_ptr = 0;
+    if (!cuda_ok((cudaError_t)skl_b200_launch_cvt_f8_to_bf16_2d(wide, ld_dst, g->b, ld_src, g->tb, rows, cols,
+                                                                g_ctx.stream)))
+      return 0;
+    if (g->b_static) {
+      g_ctx.wide_ptr = wide;
+      g_ctx.wide_src = g->b;
+      g_ctx.wide_rows = rows;
+      g_ctx.wide_cols = cols;
+      g_ctx.wide_ld = ld_src;
+      g_ctx.wide_fmt = g->tb;
+    }
+  }
   g->b = wide;
   g->tb = SKL_DT_BF16;
   if (k_major) {

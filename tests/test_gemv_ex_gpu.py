@@ -139,3 +139,41 @@ def test_overlapped_launches_with_static_weights_keep_stream_order(skl, m):
         skl.skl_b200_set_stream(None)
         torch.cuda.synchronize()
     assert np.array_equal(dc.cpu().numpy().astype(np.int64), want)
+
+
+def test_static_fp8_weights_are_widened_once(skl):
+    """bf16 x fp8 with skl_b200_set_static_weights(1): the first call widens W (2 launches), repeats reuse the copy
+    (1 launch), another W or switching the declaration off widens again; every result equals the plain call's."""
+    import torch
+
+    m, n, k = 256, 512, 256
+    g = H.rng(321)
+    x = torch.from_numpy(H.random_operand(H.BF16, (m, k), g).view(np.int16)).cuda()
+    w1 = torch.from_numpy(H.random_operand(H.F8E4M3, (k, n), g)).cuda()
+    w2 = torch.from_numpy(H.random_operand(H.F8E4M3, (k, n), g)).cuda()
+    cs = torch.from_numpy(g.uniform(0.5, 1.5, n).astype(np.float32)).cuda()
+
+    def run(w):
+        c = torch.zeros((m, n), dtype=torch.int16, device="cuda")
+        skl.skl_gemm_ex_sm100a(m, n, k, S.BF16, x.data_ptr(), k, 1, S.F8E4M3, w.data_ptr(), n, 1, 1.0, None, cs.data_ptr(),
+                               0.0, S.BF16, c.data_ptr(), n, 1)
+        S.check()
+        return c, skl.skl_b200_last_launch_count()
+
+    ref1, l0 = run(w1)
+    ref2, _ = run(w2)
+    assert l0 == 2
+    skl.skl_b200_set_static_weights(1)
+    try:
+        a, la = run(w1)
+        b, lb = run(w1)
+        c2, lc = run(w2)
+        d, ld = run(w2)
+        e, le = run(w1)
+    finally:
+        skl.skl_b200_set_static_weights(0)
+    assert (la, lb, lc, ld, le) == (2, 1, 2, 1, 2)
+    for got, want in ((a, ref1), (b, ref1), (c2, ref2), (d, ref2), (e, ref1)):
+        assert torch.equal(got, want)
+    f, lf = run(w1)
+    assert lf == 2 and torch.equal(f, ref1)
