@@ -103,10 +103,11 @@ def test_extended_epilogue_all_pairs_and_outputs(skl, pair, tc):
         assert np.all(err <= tol), float(np.nanmax(err - tol))
 
 
-@pytest.mark.parametrize("m", [1, 2])
+@pytest.mark.parametrize("m", [1, 2, 4, 16])
 def test_overlapped_launches_with_static_weights_keep_stream_order(skl, m):
-    """With skl_b200_set_static_weights(1) each skinny launch may start streaming weights before its predecessor has
-    finished, but must still see everything the predecessor wrote.  A chain of launches accumulates into the same C
+    """With skl_b200_set_static_weights(1) each skinny launch (the dp4a kernel for m <= 2, the transposed tensor-core
+    tile above) may start streaming weights before its predecessor has finished, but must still see everything the
+    predecessor wrote.  A chain of launches accumulates into the same C
     (beta = 1), each from new activations written just before it on the same stream; the sum must be exact."""
     import torch
 
@@ -130,7 +131,7 @@ def test_overlapped_launches_with_static_weights_keep_stream_order(skl, m):
             for s_ in range(steps):
                 dx.copy_(dxs[s_])  # the activations change between launches, on the same stream
                 skl.skl_gemm_i8rc_i8rc_i32rc_sm100a(m, n, k, 1, dx.data_ptr(), k, 1, dw.data_ptr(), 1, k, 1, dc.data_ptr(), n, 1)
-                assert skl.skl_b200_last_path() == S.PATH_GEMV
+                assert skl.skl_b200_last_path() == (S.PATH_GEMV if m <= 2 else S.PATH_TCGEN05)
         skl.skl_b200_synchronize()
         S.check()
     finally:
