@@ -313,8 +313,8 @@ __device__ __forceinline__ void umma_commit_pair_both(uint32_t bar) {
 // Each epilogue warp owns EPI_STAGE_BYTES of staging.  A 32-row x 32-column chunk is written there one row per
 // lane in the tensor map's swizzled order (the 16-byte piece index XORed with address bits 7 and up, so the 32
 // lanes' pieces spread over all banks), then one lane hands the box to the TMA engine, which writes whole rows
-// of the box to global memory and clips at the matrix edge.  Narrow element types fit 2 or 4 boxes in the
-// staging area and rotate through them, so a store only waits for the one issued that many chunks earlier.
+// of the box to global memory and clips at the matrix edge.  A box is 2 KiB (1 KiB for 1-byte elements), so 2 or
+// 4 boxes rotate through the staging area and a store only waits for the one issued that many boxes earlier.
 constexpr int EPI_STAGE_BYTES = 4096;
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap *tm, uint32_t src, int x, int y) {
   asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(tm), "r"(src),
@@ -334,12 +334,12 @@ struct EpiStage {
   uint32_t count;         // chunks stored so far
 };
 
-// w: the lane's row of the chunk, 32 elements of ES bytes packed into 8 * ES words.
-template <int ES>
-__device__ __forceinline__ void tma_store_chunk(EpiStage &st, int lane, const uint32_t *w, int x, int y) {
-  constexpr int NBUF = 4 / ES;
-  constexpr int PITCH = 32 * ES;      // bytes per staged row: 128 / 64 / 32 = the map's swizzle span
+// One box: PITCH bytes per row (64 or 32 = the map's swizzle span), 32 rows, NBUF boxes rotating through the
+// staging area.  w: the lane's row of the box, PITCH / 4 words.
+template <int PITCH, int NBUF>
+__device__ __forceinline__ void tma_store_box(EpiStage &st, int lane, const uint32_t *w, int x, int y) {
   constexpr int PIECES = PITCH / 16;  // 16-byte pieces per row
+  static_assert(NBUF * 32 * PITCH <= EPI_STAGE_BYTES, "boxes exceed the staging area");
   const uint32_t buf = st.base + (st.count % NBUF) * (32 * PITCH);
   if (lane == 0) bulk_wait_read<NBUF - 1>();
   __syncwarp();
@@ -357,6 +357,21 @@ __device__ __forceinline__ void tma_store_chunk(EpiStage &st, int lane, const ui
     bulk_commit();
   }
   ++st.count;
+}
+
+// w: the lane's row of a 32-column chunk, 32 elements of ES bytes packed into 8 * ES words.  4-byte elements go
+// out as two boxes of 16 columns so that, like the narrower types, one store is always in flight while the
+// next box is being filled.
+template <int ES>
+__device__ __forceinline__ void tma_store_chunk(EpiStage &st, int lane, const uint32_t *w, int x, int y) {
+  if (ES == 4) {
+    tma_store_box<64, 2>(st, lane, w, x, y);
+    tma_store_box<64, 2>(st, lane, w + 16, x + 16, y);
+  } else if (ES == 2) {
+    tma_store_box<64, 2>(st, lane, w, x, y);
+  } else {
+    tma_store_box<32, 4>(st, lane, w, x, y);
+  }
 }
 
 // Per-warp shared-memory copies of the tile's column scales and column bias.  Each epilogue warp fills
@@ -1084,21 +1099,19 @@ bool make_map(CUtensorMap *tm, int kind, int dt, const void *base, const Operand
   return r == CUDA_SUCCESS;
 }
 
-// Tensor map of C for the epilogue's stores: boxes of 32 rows x 32 columns, swizzled over the box's row bytes
-// (128 / 64 / 32 for 4- / 2- / 1-byte elements) to match tma_store_chunk's staging order.
+// Tensor map of C for the epilogue's stores: boxes of 32 rows x 32 columns (16 columns for 4-byte elements),
+// swizzled over the box's row bytes (64 / 64 / 32 for 4- / 2- / 1-byte elements) to match tma_store_box.
 bool make_c_map(CUtensorMap *tm, void *base, int64_t M, int64_t N, int64_t ld, int es) {
   EncodeTiledFn enc = encode_fn();
   if (!enc) return false;
   cuuint64_t dims[2] = {(cuuint64_t)N, (cuuint64_t)M}, strides[1];
-  cuuint32_t box[2] = {32, 32}, estr[2] = {1, 1};
+  cuuint32_t box[2] = {es == 4 ? 16u : 32u, 32}, estr[2] = {1, 1};
   if (M <= 1) ld = (int64_t)((N * es + 15) / 16 * 16) / es;  // stride unused; keep it legal
   strides[0] = (cuuint64_t)ld * es;
   const CUtensorMapDataType cdt = es == 4   ? CU_TENSOR_MAP_DATA_TYPE_UINT32
                                   : es == 2 ? CU_TENSOR_MAP_DATA_TYPE_UINT16
                                             : CU_TENSOR_MAP_DATA_TYPE_UINT8;
-  const CUtensorMapSwizzle sw = es == 4   ? CU_TENSOR_MAP_SWIZZLE_128B
-                                : es == 2 ? CU_TENSOR_MAP_SWIZZLE_64B
-                                          : CU_TENSOR_MAP_SWIZZLE_32B;
+  const CUtensorMapSwizzle sw = es == 1 ? CU_TENSOR_MAP_SWIZZLE_32B : CU_TENSOR_MAP_SWIZZLE_64B;
   CUresult r = enc(tm, cdt, 2, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
                    CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS;
