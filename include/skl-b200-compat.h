@@ -22,6 +22,7 @@
 
 /* column-major-A GEMMs: src/gemm/gemm_i8c_i8_i32_xsfmm32a8i.h:57-60 and siblings */
 #define skl_gemm_i8c_i8_i32_xsfmm32a8i skl_gemm_i8c_i8_i32_sm100a
+#define skl_gemm_i8rcp1x4_i8p4x1c_i32_xsfvqdotq skl_gemm_i8rcp1x4_i8p4x1c_i32_sm100a
 #define skl_gemm_bf16c_bf16_f32_xsfmm32a16f skl_gemm_bf16c_bf16_f32_sm100a
 #define skl_gemm_f16c_f16_f32_xsfmm32a16f skl_gemm_f16c_f16_f32_sm100a
 #define skl_gemm_f8e4m3c_f8e4m3_f32_xsfmm32a8f skl_gemm_f8e4m3c_f8e4m3_f32_sm100a

@@ -208,6 +208,16 @@ SKL_FUNC void skl_gemm_f8e5m2rcprc_f8e5m2rcprc_f32rcprc_sm100a(
     size_t rsb1, size_t csb1, float beta, float *c, size_t rsc0, size_t csc0, size_t rsc1,
     size_t csc1);
 
+/* ------------------------------------------------------------------ GEMM, int8 with 4-deep k blocks
+ * Same parameter list as skl_gemm_i8rcp1x4_i8p4x1c_i32_xsfvqdotq
+ * (src/gemm/gemm_i8rcp1x4_i8p4x1c_i32_xsfvqdotq.h:70-75): A in 1 x 4 blocks (element (i, k) at
+ * i*rsa1 + (k/4)*csa1 + k%4), B in 4 x 1 blocks, column blocks 4 elements apart (element (k, j) at
+ * (k/4)*rsb1 + 4*j + k%4), C row-major; K = 4*k1.  Equivalent to the general packed entry with
+ * m0 = n0 = 1, k0 = 4, as that header states. */
+SKL_FUNC void skl_gemm_i8rcp1x4_i8p4x1c_i32_sm100a(size_t m, size_t n, size_t k1, int32_t alpha, const int8_t *a,
+                                                   size_t rsa1, size_t csa1, const int8_t *b, size_t rsb1,
+                                                   int32_t beta, int32_t *c, size_t rsc);
+
 /* ------------------------------------------------------------------ GEMM, fp32 and fp64
  * Same parameter lists as skl_gemm_f32rc_f32rc_f32rc_ref / skl_gemm_f64rc_f64rc_f64rc_ref
  * (ref/gemm/gemm_f32rc_f32rc_f32rc.h, gemm_f64rc_f64rc_f64rc.h) and their packed forms

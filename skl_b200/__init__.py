@@ -61,6 +61,7 @@ SIGNATURES = {
     "skl_gemm_f16c_f16_f32_sm100a": (_GEMM_R_F, None),
     "skl_gemm_f8e4m3c_f8e4m3_f32_sm100a": (_GEMM_R_F, None),
     "skl_gemm_f8e5m2c_f8e5m2_f32_sm100a": (_GEMM_R_F, None),
+    "skl_gemm_i8rcp1x4_i8p4x1c_i32_sm100a": ([_SZ, _SZ, _SZ, _I32, _VP, _SZ, _SZ, _VP, _SZ, _I32, _VP, _SZ], None),
     "skl_gemm_f32rc_f32rc_f32rc_sm100a": (_GEMM_RC_F, None),
     "skl_gemm_f64rc_f64rc_f64rc_sm100a": ([_SZ, _SZ, _SZ, C.c_double, _VP, _SZ, _SZ, _VP, _SZ, _SZ, C.c_double, _VP,
                                            _SZ, _SZ], None),

@@ -863,6 +863,14 @@ SKL_B200_DEF_GEMM_PACKED_F32(skl_gemm_f16rcprc_f16rcprc_f32rcprc_sm100a, skl_f16
 SKL_B200_DEF_GEMM_PACKED_F32(skl_gemm_f8e4m3rcprc_f8e4m3rcprc_f32rcprc_sm100a, uint8_t, SKL_DT_F8E4M3)
 SKL_B200_DEF_GEMM_PACKED_F32(skl_gemm_f8e5m2rcprc_f8e5m2rcprc_f32rcprc_sm100a, uint8_t, SKL_DT_F8E5M2)
 
+/* src/gemm/gemm_i8rcp1x4_i8p4x1c_i32_xsfvqdotq.h:43-52: the general packed GEMM with m0 = n0 = 1, k0 = 4 */
+void skl_gemm_i8rcp1x4_i8p4x1c_i32_sm100a(size_t m, size_t n, size_t k1, int32_t alpha, const int8_t *a, size_t rsa1,
+                                          size_t csa1, const int8_t *b, size_t rsb1, int32_t beta, int32_t *c,
+                                          size_t rsc) {
+  skl_gemm_i8rcprc_i8rcprc_i32rcprc_sm100a(1, 1, 4, m, n, k1, alpha, a, 0, 1, rsa1, csa1, b, 1, 0, rsb1, 4, beta, c, 0, 0,
+                                           rsc, 1);
+}
+
 /* fp32 and fp64 GEMMs (ref/gemm/gemm_f32rc_f32rc_f32rc.c:9-22, gemm_f64rc_f64rc_f64rc.c:9-22 and the packed forms):
  * on the any-stride kernel, one accumulator per output, k ascending, product and sum rounded separately. */
 void skl_gemm_f32rc_f32rc_f32rc_sm100a(size_t m, size_t n, size_t k, float alpha, const float *a, size_t rsa,

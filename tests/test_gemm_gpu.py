@@ -327,3 +327,31 @@ def test_int32_wrap_around_in_alpha_and_beta(skl, m, n, k, expect):
     # the accumulator really wrapped in the reference arithmetic
     exact = beta * c.astype(object) + alpha * (a.astype(np.int64) @ b.astype(np.int64).T).astype(object)
     assert any(abs(int(v)) >= 2**31 for v in exact.ravel()[:64])
+
+
+@pytest.mark.parametrize("m,n,k1,expect", [(5, 7, 3, S.PATH_GENERIC), (320, 288, 80, S.PATH_TCGEN05)])
+def test_int8_1x4_4x1_blocked_entry_point(skl, m, n, k1, expect):
+    """skl_gemm_i8rcp1x4_i8p4x1c_i32 (src/gemm/gemm_i8rcp1x4_i8p4x1c_i32_xsfvqdotq.h:43-75): A rows padded to a
+    multiple of 4, B interleaved 4 deep; exact against the packed oracle called as that header prescribes."""
+    from oracle import pyoracle as orc
+
+    P = orc._p
+    g = H.rng(m)
+    k = 4 * k1
+    rsa1 = k + 8  # padded rows, still a multiple of 4
+    a = g.integers(-128, 128, size=m * rsa1, dtype=np.int8)
+    rsb1 = 4 * n + 4
+    b = g.integers(-128, 128, size=k1 * rsb1, dtype=np.int8)
+    c = g.integers(-1000, 1000, size=m * (n + 2) + 3, dtype=np.int32)
+    want = c.copy()
+    orc.port().orc_gemm_packed_i8_i32(1, 1, 4, m, n, k1, 2, P(a), 0, 1, rsa1, 4, P(b), 1, 0, rsb1, 4, 3, P(want), 0, 0, n + 2, 1)
+    got = c.copy()
+    skl.skl_gemm_i8rcp1x4_i8p4x1c_i32_sm100a(m, n, k1, 2, S.ptr(a), rsa1, 4, S.ptr(b), rsb1, 3, S.ptr(got), n + 2)
+    S.check()
+    assert skl.skl_b200_last_path() == expect
+    assert np.array_equal(got, want)
+    # and against plain matrices rebuilt from the blocked ones
+    A = a.reshape(m, rsa1)[:, :k].astype(np.int64)
+    B = b.reshape(k1, rsb1)[:, :4 * n].reshape(k1, n, 4).transpose(0, 2, 1).reshape(k, n).astype(np.int64)
+    C0 = c[:m * (n + 2)].reshape(m, n + 2)[:, :n].astype(np.int64)
+    assert np.array_equal(got[:m * (n + 2)].reshape(m, n + 2)[:, :n], (3 * C0 + 2 * (A @ B)).astype(np.int32))
