@@ -36,7 +36,7 @@ if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
 M_C5, K_C5, N_C5 = 16384, 4096, 14336
-C5_DRAM_BYTES_PER_LAUNCH_1GPU = 620.9e6 + 449.1e6
+C5_DRAM_BYTES_PER_LAUNCH_1GPU = 697.0e6 + 452.0e6
 
 
 def measured_peaks():

@@ -165,15 +165,23 @@ __global__ void __launch_bounds__(CVT_THREADS)
   if (vec_ok) {
     const size_t cvec = cols / 8;
     const size_t total = rows * cvec;
+    // (row, unit-in-row) of this thread's next unit, advanced by one grid stride at a time without dividing
+    const size_t dr = stride / cvec, dc = stride - dr * cvec;
+    size_t r = tid / cvec, c = tid - r * cvec;
     for (size_t v0 = tid; v0 < total; v0 += U * stride) {
       uint2 q[U];
       size_t doff[U];  // destination offset in 16-byte units
 #pragma unroll
       for (int u = 0; u < U; ++u) {
         const size_t v = v0 + u * stride;
-        const size_t r = v / cvec, c = v - r * cvec;
         doff[u] = r * (ld_dst / 8) + c;
         q[u] = v < total ? __ldg(reinterpret_cast<const uint2 *>(src + r * ld_src) + c) : make_uint2(0, 0);
+        r += dr;
+        c += dc;
+        if (c >= cvec) {
+          c -= cvec;
+          ++r;
+        }
       }
 #pragma unroll
       for (int u = 0; u < U; ++u) {
