@@ -106,6 +106,11 @@ int skl_b200_launch_cvt_f8_to_bf16_2d(void *dst, size_t ld_dst, const void *src,
 int skl_b200_launch_cvt_f4_to_f8e4m3(void *dst, const void *src, size_t n, void *stream);
 /* Device-side self check: counts inputs in [first, first+count) (fp32 bit patterns) for which the
  * hardware-assisted encoder and the integer encoder disagree; *mismatches is a device uint64. */
+/* dst[c][r] = widen(src[r][c]): rows x cols fp8 (unit stride along cols) into cols x rows bf16 (unit stride along
+ * rows).  Needs a 4-byte aligned src with ld_src % 4 == 0 and a 16-byte aligned dst with ld_dst % 8 == 0
+ * (cudaErrorInvalidValue otherwise). */
+int skl_b200_launch_cvt_f8_to_bf16_2d_transposed(void *dst, size_t ld_dst, const void *src, size_t ld_src,
+                                                 int src_fmt, size_t rows, size_t cols, void *stream);
 int skl_b200_launch_cvt_selfcheck(int dst_fmt, int saturate, uint64_t first, uint64_t count,
                                   unsigned long long *mismatches, void *stream);
 

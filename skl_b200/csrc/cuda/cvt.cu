@@ -201,6 +201,65 @@ __global__ void __launch_bounds__(CVT_THREADS)
   }
 }
 
+// Widening with a transpose: src is rows x cols fp8 with unit stride along cols, dst is cols x rows bf16 with unit
+// stride along rows (dst[c][r] = widen(src[r][c])).  Used for the fp8 operand of a bf16 x fp8 GEMM whose B arrives
+// n-contiguous: the tensor-core kernel runs several percent faster on a k-contiguous B, and since the widened copy
+// has to be written anyway it is written in that orientation.
+// Tile: 128 rows x 64 cols.  A thread takes 4 rows x 4 cols as four 4-byte loads, transposes the 4 x 4 bytes in
+// registers, widens each column's 4 codes (consecutive along dst's unit stride) to 8 bytes and puts them into a
+// shared-memory tile laid out like dst; the tile then leaves as 16-byte stores, 256 contiguous bytes per dst row.
+constexpr int WT_R = 128, WT_C = 64, WT_PITCH = 2 * WT_R + 8;  // pitch in bytes, 8-byte aligned, odd in 8-byte units
+template <int FMT>
+__global__ void __launch_bounds__(256)
+    cvt_f8_to_bf16_transpose_kernel(uint16_t *__restrict__ dst, size_t ld_dst, const uint8_t *__restrict__ src,
+                                    size_t ld_src, uint32_t rows, uint32_t cols, uint32_t tiles_r, uint32_t tiles_c) {
+  __shared__ __align__(16) uint8_t tile[WT_C * WT_PITCH];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const uint32_t num_tiles = tiles_r * tiles_c;
+  for (uint32_t t = blockIdx.x; t < num_tiles; t += gridDim.x) {
+    const uint32_t r0 = (t / tiles_c) * WT_R, c0 = (t % tiles_c) * WT_C;
+    const bool full = r0 + WT_R <= rows && c0 + WT_C <= cols;
+    if (full) {
+      // 32 x 16 micro-tiles of 4 rows x 4 cols; a warp step covers 4 (rows) x 8 (cols) of them
+#pragma unroll
+      for (int w = warp; w < 16; w += 8) {
+        const int cx = (w & 1) * 8 + (lane & 7);   // micro-tile column 0..15
+        const int ry = (w >> 1) * 4 + (lane >> 3);  // micro-tile row 0..31
+        uint32_t r[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q)
+          r[q] = __ldg(reinterpret_cast<const uint32_t *>(src + (size_t)(r0 + 4 * ry + q) * ld_src + c0 + 4 * cx));
+        const uint32_t a0 = __byte_perm(r[0], r[1], 0x5140), a1 = __byte_perm(r[0], r[1], 0x7362);
+        const uint32_t b0 = __byte_perm(r[2], r[3], 0x5140), b1 = __byte_perm(r[2], r[3], 0x7362);
+        const uint32_t col[4] = {__byte_perm(a0, b0, 0x5410), __byte_perm(a0, b0, 0x7632), __byte_perm(a1, b1, 0x5410),
+                                 __byte_perm(a1, b1, 0x7632)};  // col[b] = codes of rows 4ry..4ry+3 in column 4cx+b
+#pragma unroll
+        for (int b = 0; b < 4; ++b) {
+          uint32_t lo, hi;
+          f8x4_to_bf16x4<FMT>(col[b], lo, hi);
+          *reinterpret_cast<uint2 *>(tile + (4 * cx + b) * WT_PITCH + 8 * ry) = make_uint2(lo, hi);
+        }
+      }
+      __syncthreads();
+      // 64 dst rows of 256 bytes = 16 pieces of 16 bytes each
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int e = threadIdx.x + 256 * i, row = e >> 4, piece = e & 15;
+        const uint2 x = *reinterpret_cast<const uint2 *>(tile + row * WT_PITCH + 16 * piece);
+        const uint2 y = *reinterpret_cast<const uint2 *>(tile + row * WT_PITCH + 16 * piece + 8);
+        *reinterpret_cast<uint4 *>(dst + (size_t)(c0 + row) * ld_dst + r0 + 8 * piece) = make_uint4(x.x, x.y, y.x, y.y);
+      }
+      __syncthreads();
+    } else {
+      // ragged edge tile: one element at a time
+      for (int e = threadIdx.x; e < WT_R * WT_C; e += 256) {
+        const uint32_t rr = r0 + e / WT_C, cc = c0 + e % WT_C;
+        if (rr < rows && cc < cols) dst[(size_t)cc * ld_dst + rr] = (uint16_t)f8_to_bf16_bits<FMT>(src[(size_t)rr * ld_src + cc]);
+      }
+    }
+  }
+}
+
 // E2M1 nibble -> E4M3 byte: all eight magnitudes are exact in E4M3 (ref/cvt/cvt_ofp4.c:18-60).
 __device__ __forceinline__ uint32_t f4_to_e4m3(uint32_t nib) {
   // magnitudes 0, .5, 1, 1.5, 2, 3, 4, 6 -> 0x00 0x30 0x38 0x3C 0x40 0x44 0x48 0x4C
@@ -291,6 +350,29 @@ extern "C" int skl_b200_launch_cvt_f8_to_bf16_2d(void *dst, size_t ld_dst, const
   else
     cvt_f8_to_bf16_2d_kernel<SKL_DT_F8E5M2><<<grid, CVT_THREADS, 0, s>>>(
         (uint16_t *)dst, ld_dst, (const uint8_t *)src, ld_src, rows, cols, vec);
+  SKLB_COUNT_LAUNCH();
+  return (int)cudaGetLastError();
+}
+
+extern "C" int skl_b200_launch_cvt_f8_to_bf16_2d_transposed(void *dst, size_t ld_dst, const void *src,
+                                                            size_t ld_src, int src_fmt, size_t rows,
+                                                            size_t cols, void *stream) {
+  if (rows == 0 || cols == 0) return 0;
+  // word loads along src rows, 16-byte stores along dst rows
+  if (!aligned16(dst) || (reinterpret_cast<uintptr_t>(src) & 3u) != 0 || ld_src % 4 != 0 || ld_dst % 8 != 0 ||
+      rows >= (1ull << 31) || cols >= (1ull << 31))
+    return (int)cudaErrorInvalidValue;
+  const uint32_t tr = (uint32_t)((rows + WT_R - 1) / WT_R), tc = (uint32_t)((cols + WT_C - 1) / WT_C);
+  const uint64_t tiles = (uint64_t)tr * tc;
+  const uint64_t cap = (uint64_t)cvt_grid(~(size_t)0 >> 8, 1);  // 8 CTAs per SM
+  const int grid = (int)(tiles < cap ? tiles : cap);
+  cudaStream_t s = (cudaStream_t)stream;
+  if (src_fmt == SKL_DT_F8E4M3)
+    cvt_f8_to_bf16_transpose_kernel<SKL_DT_F8E4M3><<<grid, 256, 0, s>>>((uint16_t *)dst, ld_dst, (const uint8_t *)src,
+                                                                         ld_src, (uint32_t)rows, (uint32_t)cols, tr, tc);
+  else
+    cvt_f8_to_bf16_transpose_kernel<SKL_DT_F8E5M2><<<grid, 256, 0, s>>>((uint16_t *)dst, ld_dst, (const uint8_t *)src,
+                                                                         ld_src, (uint32_t)rows, (uint32_t)cols, tr, tc);
   SKLB_COUNT_LAUNCH();
   return (int)cudaGetLastError();
 }
