@@ -178,3 +178,30 @@ def test_static_fp8_weights_are_widened_once(skl):
         assert torch.equal(got, want)
     f, lf = run(w1)
     assert lf == 2 and torch.equal(f, ref1)
+
+
+@pytest.mark.parametrize("tb", [H.F8E4M3, H.F8E5M2])
+@pytest.mark.parametrize("where", ["device", "host"])
+def test_bf16_x_fp8_with_reoriented_widening(skl, tb, where, monkeypatch):
+    """m >= 512 and an n-contiguous fp8 B: the widened copy is written k-contiguous by the transposing kernel.
+    Shapes ragged against its 128 x 64 tiles; the result must equal what the layout-keeping route gives, bit for
+    bit (both feed exactly the same bf16 values to the same kernel family), and stay within the oracle's bound."""
+    for (m, n, k) in [(520, 300, 200), (640, 257, 136), (512, 64, 128)]:
+        outs = []
+        for keep in ("", "1"):
+            if keep:
+                monkeypatch.setenv("SKL_B200_WIDEN_KEEP_LAYOUT", keep)
+            else:
+                monkeypatch.delenv("SKL_B200_WIDEN_KEEP_LAYOUT", raising=False)
+            A, B, before, want, got, rs, cs = ex_case(skl, m, n, k, H.BF16, tb, H.F32, "rrr", 1.5, 0.0, False, True,
+                                                      where, m + n, 0, amp=1.0)
+            assert skl.skl_b200_last_path() == S.PATH_TCGEN05
+            outs.append(got.copy())
+        monkeypatch.delenv("SKL_B200_WIDEN_KEEP_LAYOUT", raising=False)
+        ref = H.to_f32(H.F32, want.get()).astype(np.float64)
+        scale = np.abs(1.5 * cs[None, :].astype(np.float64))
+        bound = H.skl_forward_bound(H.BF16, A.get(), tb, B.get(), 1.0, 0.0, None, k) * scale * 2
+        err = np.abs(outs[0].astype(np.float64) - ref)
+        assert np.all(err <= bound + 2.0 ** -23 * np.abs(ref) + 1e-30)
+        # k-order inside the MMA is the same for both orientations of B, so the two routes agree exactly
+        assert np.array_equal(outs[0].view(np.uint32), outs[1].view(np.uint32))
