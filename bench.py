@@ -55,6 +55,7 @@ class ClockSampler:
 
     def __init__(self, index: int, period_s: float = 0.004):
         self.index, self.period, self.samples, self.reasons = index, period_s, [], set()
+        self.power_w = []
         self.max_mhz = None
         self._stop = threading.Event()
         self._thread = None
@@ -80,6 +81,7 @@ class ClockSampler:
         while not self._stop.is_set():
             try:
                 self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                self.power_w.append(nv.nvmlDeviceGetPowerUsage(self.h) / 1000.0)
                 mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
                 for bit, name in names.items():
                     if mask & bit:
@@ -101,8 +103,10 @@ class ClockSampler:
 
     def summary(self):
         s = sorted(self.samples)
+        pw = sorted(self.power_w)
         return {"sm_mhz": (s[len(s) // 2] if s else None), "sm_max_mhz": self.max_mhz,
-                "reasons": sorted(self.reasons), "samples": len(s)}
+                "reasons": sorted(self.reasons), "samples": len(s),
+                "power_w": (round(pw[len(pw) // 2], 1) if pw else None)}
 
 
 # ----------------------------------------------------------------------------- CPU baseline (checker only)
