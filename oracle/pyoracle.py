@@ -87,6 +87,7 @@ def port():
                                        _F, _I, _F, _I, _VP, _SZ, _SZ]
         lib.orc_gemm_f64.argtypes = [_SZ] * 6 + [C.c_double, _VP] + [_SZ] * 4 + [_VP] + [_SZ] * 4 + \
             [C.c_double, _VP] + [_SZ] * 4
+        lib.orc_gemm_f16acc.argtypes = [_SZ] * 6 + [_F, _VP] + [_SZ] * 4 + [_VP] + [_SZ] * 4 + [_F, _VP] + [_SZ] * 4
         lib.orc_activation.argtypes = [_I, _F, _F, _F]
         lib.orc_activation.restype = _F
         lib.orc_pack.argtypes = [_SZ, _SZ, _SZ, _VP, _SZ, _SZ, _SZ, _SZ, _VP, _SZ, _SZ, _SZ, _SZ,
@@ -140,6 +141,9 @@ def ref():
             getattr(lib, f"skl_transpose_e{e}_ref").argtypes = [_SZ, _SZ, _VP, _SZ, _VP, _SZ]
         lib.skl_unpack_e8rcprc_e8rc_ref.argtypes = [_SZ, _SZ, _VP, _SZ, _SZ, _SZ, _SZ, _SZ, _SZ, _VP,
                                                     _SZ, _SZ]
+        if hasattr(lib, "orc_ref_gemm_f16acc"):  # ref_shim.c: the fp16-accumulate reference with float scalars
+            lib.orc_ref_gemm_f16acc.argtypes = [_SZ] * 6 + [_F, _VP] + [_SZ] * 4 + [_VP] + [_SZ] * 4 + [_F, _VP] + \
+                [_SZ] * 4
         lib.skl_gemm_f32rc_f32rc_f32rc_ref.argtypes = [_SZ, _SZ, _SZ, _F, _VP, _SZ, _SZ, _VP, _SZ, _SZ, _F, _VP, _SZ,
                                                        _SZ]
         lib.skl_gemm_f64rc_f64rc_f64rc_ref.argtypes = [_SZ, _SZ, _SZ, C.c_double, _VP, _SZ, _SZ, _VP, _SZ, _SZ,

@@ -360,6 +360,41 @@ void orc_gemm_f64(size_t m0, size_t n0, size_t k0, size_t m1, size_t n1, size_t 
   }
 }
 
+/* ref/gemm/gemm_f16rcprc_f16rcprc_f16rcprc.c (and, with one block per dimension, gemm_f16rc_f16rc_f16rc.c:9-22):
+ * fp16 operands, accumulator, scalars and C.  Each statement of the reference -- `acc += a*b`,
+ * `c = beta*c + alpha*acc` -- is evaluated in fp32 and rounded to fp16 once, which is what a compiler without native
+ * half-precision arithmetic makes of the `_Float16` source (the product of two fp16 values is exact in fp32).
+ * fp16 values travel as bit patterns; alpha and beta are floats holding fp16-representable values. */
+void orc_gemm_f16acc(size_t m0, size_t n0, size_t k0, size_t m1, size_t n1, size_t k1, float alpha,
+                     const uint16_t *a, size_t rsa0, size_t csa0, size_t rsa1, size_t csa1, const uint16_t *b,
+                     size_t rsb0, size_t csb0, size_t rsb1, size_t csb1, float beta, uint16_t *c, size_t rsc0,
+                     size_t csc0, size_t rsc1, size_t csc1) {
+  const float alpha_h = orc_f16_to_f32(orc_f32_to_f16(alpha)), beta_h = orc_f16_to_f32(orc_f32_to_f16(beta));
+  for (size_t bi = 0; bi < m1; ++bi) {
+    for (size_t bj = 0; bj < n1; ++bj) {
+      for (size_t i = 0; i < m0; ++i) {
+        for (size_t j = 0; j < n0; ++j) {
+          float acc = 0.0f; /* always an fp16-representable value */
+          for (size_t bp = 0; bp < k1; ++bp) {
+            size_t abase = bi * rsa1 + bp * csa1 + i * rsa0;
+            size_t bbase = bp * rsb1 + bj * csb1 + j * csb0;
+            for (size_t p = 0; p < k0; ++p) {
+              float prod = orc_f16_to_f32(a[abase + p * csa0]) * orc_f16_to_f32(b[bbase + p * rsb0]);
+              float sum = acc + prod;
+              acc = orc_f16_to_f32(orc_f32_to_f16(sum));
+            }
+          }
+          uint16_t *cp = c + bi * rsc1 + bj * csc1 + i * rsc0 + j * csc0;
+          float left = beta_h * orc_f16_to_f32(*cp);
+          float right = alpha_h * acc;
+          float sum = left + right;
+          *cp = orc_f32_to_f16(sum);
+        }
+      }
+    }
+  }
+}
+
 /* ------------------------------------------------------------------ extended epilogue */
 static inline float load_c(int tc, const void *c, size_t idx) {
   if (tc == ORC_I8) {

@@ -77,6 +77,13 @@ void orc_gemm_f64(size_t m0, size_t n0, size_t k0, size_t m1, size_t n1, size_t 
                   size_t rsb1, size_t csb1, double beta, double *c, size_t rsc0, size_t csc0, size_t rsc1,
                   size_t csc1);
 
+/* fp16 accumulator: ref/gemm/gemm_f16rc_f16rc_f16rc.c:9-22 and gemm_f16rcprc_f16rcprc_f16rcprc.c, every statement
+ * evaluated in fp32 and rounded to fp16 once (see the definition). */
+void orc_gemm_f16acc(size_t m0, size_t n0, size_t k0, size_t m1, size_t n1, size_t k1, float alpha,
+                     const uint16_t *a, size_t rsa0, size_t csa0, size_t rsa1, size_t csa1, const uint16_t *b,
+                     size_t rsb0, size_t csb0, size_t rsb1, size_t csb1, float beta, uint16_t *c, size_t rsc0,
+                     size_t csc0, size_t rsc1, size_t csc1);
+
 /* ---- GEMM, packed (blocked 4-D) operands ----
  * int8: ref/gemm/gemm_i8rcprc_i8rcprc_i32rcprc.c:10-37;
  * float: gemm_bf16rcprc_bf16rcprc_f32rcprc.c:9-36 and its f16 / f8 siblings. */

@@ -31,6 +31,9 @@ _GEMM_R_F = [_SZ, _SZ, _SZ, _F, _VP, _SZ, _VP, _SZ, _F, _VP, _SZ]
 _GEMM_P_I = [_SZ] * 6 + [_I32, _VP] + [_SZ] * 4 + [_VP] + [_SZ] * 4 + [_I32, _VP] + [_SZ] * 4
 _GEMM_P_F = [_SZ] * 6 + [_F, _VP] + [_SZ] * 4 + [_VP] + [_SZ] * 4 + [_F, _VP] + [_SZ] * 4
 
+_GEMM_TE_I = [_SZ, _SZ, _SZ, _I32, _VP, _SZ, _SZ, _VP, _SZ, _SZ, _I32, _VP, _SZ, _SZ, _SZ, _SZ]
+_GEMM_TE_F = [_SZ, _SZ, _SZ, _F, _VP, _SZ, _SZ, _VP, _SZ, _SZ, _F, _VP, _SZ, _SZ, _SZ, _SZ]
+
 # every symbol include/skl-b200.h declares -> ctypes argument list (restype None unless noted)
 SIGNATURES = {
     "skl_b200_last_status": ([], _I),
@@ -45,9 +48,12 @@ SIGNATURES = {
     "skl_b200_last_path": ([], _I),
     "skl_b200_last_launch_count": ([], _I),
     "skl_b200_force_path": ([_I], None),
+    "skl_b200_set_wait_limit": ([C.c_uint], None),
+    "skl_b200_debug_skip_loads": ([_I], None),
     "skl_b200_profile_begin": ([_I], None),
     "skl_b200_profile_end": ([C.POINTER(C.c_double)], _I),
     "skl_b200_shard_columns": ([_SZ, _SZ, _SZ, _SZ, C.POINTER(_SZ), C.POINTER(_SZ)], None),
+    "skl_b200_unshard_columns_sm100a": ([_SZ, _SZ, _SZ, _SZ, _SZ, _VP, _SZ, _VP, _SZ], None),
     "skl_gemm_i8rc_i8rc_i32rc_sm100a": (_GEMM_RC_I, None),
     "skl_gemm_bf16rc_bf16rc_f32rc_sm100a": (_GEMM_RC_F, None),
     "skl_gemm_f16rc_f16rc_f32rc_sm100a": (_GEMM_RC_F, None),
@@ -61,7 +67,22 @@ SIGNATURES = {
     "skl_gemm_f16c_f16_f32_sm100a": (_GEMM_R_F, None),
     "skl_gemm_f8e4m3c_f8e4m3_f32_sm100a": (_GEMM_R_F, None),
     "skl_gemm_f8e5m2c_f8e5m2_f32_sm100a": (_GEMM_R_F, None),
+    "skl_b200_te": ([], _SZ),
+    "skl_gemm_i8rcptex1c_i8rcp1xte_i32rcptexterc_sm100a": (_GEMM_TE_I, None),
+    "skl_gemm_bf16rcptex1c_bf16rcp1xte_f32rcptexterc_sm100a": (_GEMM_TE_F, None),
+    "skl_gemm_f16rcptex1c_f16rcp1xte_f32rcptexterc_sm100a": (_GEMM_TE_F, None),
+    "skl_gemm_f8e4m3rcptex1c_f8e4m3rcp1xte_f32rcptexterc_sm100a": (_GEMM_TE_F, None),
+    "skl_gemm_f8e5m2rcptex1c_f8e5m2rcp1xte_f32rcptexterc_sm100a": (_GEMM_TE_F, None),
+    "skl_gemm_f32rcptex1c_f32rcp1xte_f32rcptexterc_sm100a": (_GEMM_TE_F, None),
+    "skl_pack_e8_e8rcptex1c_sm100a": ([_SZ, _SZ, _VP, _SZ, _VP, _SZ, _SZ, C.c_uint8], None),
+    "skl_pack_e16_e16rcptex1c_sm100a": ([_SZ, _SZ, _VP, _SZ, _VP, _SZ, _SZ, C.c_uint16], None),
+    "skl_pack_e32_e32rcptex1c_sm100a": ([_SZ, _SZ, _VP, _SZ, _VP, _SZ, _SZ, C.c_uint32], None),
     "skl_gemm_i8rcp1x4_i8p4x1c_i32_sm100a": ([_SZ, _SZ, _SZ, _I32, _VP, _SZ, _SZ, _VP, _SZ, _I32, _VP, _SZ], None),
+    # fp16 scalars by value cannot be passed through ctypes: declared and exported, called through the *_f32scalars forms
+    "skl_gemm_f16rc_f16rc_f16rc_sm100a": None,
+    "skl_gemm_f16rcprc_f16rcprc_f16rcprc_sm100a": None,
+    "skl_gemm_f16rc_f16rc_f16rc_f32scalars_sm100a": (_GEMM_RC_F, None),
+    "skl_gemm_f16rcprc_f16rcprc_f16rcprc_f32scalars_sm100a": (_GEMM_P_F, None),
     "skl_gemm_f32rc_f32rc_f32rc_sm100a": (_GEMM_RC_F, None),
     "skl_gemm_f64rc_f64rc_f64rc_sm100a": ([_SZ, _SZ, _SZ, C.c_double, _VP, _SZ, _SZ, _VP, _SZ, _SZ, C.c_double, _VP,
                                            _SZ, _SZ], None),
@@ -119,10 +140,11 @@ def lib() -> C.CDLL:
                 "(there is no fallback implementation)")
         handle = C.CDLL(LIB_PATH)
         for table in (SIGNATURES, _ABI_SIGNATURES):
-            for name, (args, res) in table.items():
+            for name, sig in table.items():
                 fn = getattr(handle, name)
-                fn.argtypes = args
-                fn.restype = res
+                if sig is None:  # exported, but its by-value arguments have no ctypes form
+                    continue
+                fn.argtypes, fn.restype = sig
         _lib = handle
     return _lib
 

@@ -35,7 +35,11 @@ enum {
   /* v = alpha*(float)acc; *row_scale[i]; *col_scale[j]; (+ beta*C when beta != 0); narrow to tc */
   SKL_EPI_FLOAT = 1,
   /* C = beta*C + alpha*acc in double, one rounding per operation (ref/gemm/gemm_f64rc_f64rc_f64rc.c:9-22) */
-  SKL_EPI_F64 = 2
+  SKL_EPI_F64 = 2,
+  /* fp16 operands, fp16 accumulator and fp16 C (ref/gemm/gemm_f16rc_f16rc_f16rc.c:9-22): each statement of the
+   * reference evaluated in fp32 and rounded to fp16 once -- acc = h(acc + a*b) per k (the product of two fp16
+   * values is exact in fp32), C = h(beta*C + alpha*acc); alpha_f / beta_f hold the fp16 scalars' values */
+  SKL_EPI_F16ACC = 3
 };
 
 /* Activation applied to the float epilogue's value v (same numbering as skl_b200_activation_t); the
@@ -75,6 +79,9 @@ typedef struct skl_b200_gemm_args {
   float act_param;         /* logistic / swish: beta; swiglu: delta */
   int32_t b_static;        /* the caller declared B (the weights) not written by earlier work on the stream: the
                               skinny kernel may then start streaming B before the preceding kernel has finished */
+  uint32_t wait_limit_ms;  /* bound of every device-side wait of this launch; 0 = the default (2000 ms) */
+  int32_t debug_skip_loads; /* testing aid: the kernel's producer announces its loads but does not issue them, so the
+                               consumers' bounded waits must run out (exercises the give-up path without any fault) */
 } skl_b200_gemm_args;
 
 /* Device status word written by kernels whose bounded waits expire: 0 = ok, else a stage code. */

@@ -160,8 +160,12 @@ __global__ void __launch_bounds__(CVT_THREADS)
     cvt_f8_to_bf16_2d_kernel(uint16_t *__restrict__ dst, size_t ld_dst, const uint8_t *__restrict__ src,
                              size_t ld_src, size_t rows, size_t cols, bool vec_ok) {
   constexpr int U = 8;
+  // Launched as a programmatic dependent of the kernel before it on the stream (its CTAs are resident and past their
+  // index set-up when that kernel ends) and itself lets the GEMM that follows start its own set-up early.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const size_t stride = (size_t)gridDim.x * blockDim.x;
   const size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  asm volatile("griddepcontrol.wait;" ::: "memory");  // nothing is read before the preceding kernel has finished
   if (vec_ok) {
     const size_t cvec = cols / 8;
     const size_t total = rows * cvec;
@@ -214,8 +218,10 @@ __global__ void __launch_bounds__(256)
     cvt_f8_to_bf16_transpose_kernel(uint16_t *__restrict__ dst, size_t ld_dst, const uint8_t *__restrict__ src,
                                     size_t ld_src, uint32_t rows, uint32_t cols, uint32_t tiles_r, uint32_t tiles_c) {
   __shared__ __align__(16) uint8_t tile[WT_C * WT_PITCH];
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // see cvt_f8_to_bf16_2d_kernel
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const uint32_t num_tiles = tiles_r * tiles_c;
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   for (uint32_t t = blockIdx.x; t < num_tiles; t += gridDim.x) {
     const uint32_t r0 = (t / tiles_c) * WT_R, c0 = (t % tiles_c) * WT_C;
     const bool full = r0 + WT_R <= rows && c0 + WT_C <= cols;
@@ -337,6 +343,21 @@ extern "C" int skl_b200_launch_cvt_f8_to_bf16(void *dst, const void *src, int sr
   return (int)cudaGetLastError();
 }
 
+// Launch configuration of a kernel that may start as a programmatic dependent of its predecessor on the stream
+// (the widening kernels of the bf16 x fp8 GEMM: they sit between two GEMM launches of a decode or training loop).
+static cudaLaunchConfig_t dependent_launch(int grid, int threads, cudaStream_t s, cudaLaunchAttribute *attr) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)grid);
+  cfg.blockDim = dim3((unsigned)threads);
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = s;
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cfg;
+}
+
 extern "C" int skl_b200_launch_cvt_f8_to_bf16_2d(void *dst, size_t ld_dst, const void *src,
                                                  size_t ld_src, int src_fmt, size_t rows,
                                                  size_t cols, void *stream) {
@@ -344,13 +365,17 @@ extern "C" int skl_b200_launch_cvt_f8_to_bf16_2d(void *dst, size_t ld_dst, const
   cudaStream_t s = (cudaStream_t)stream;
   const bool vec = aligned16(dst) && aligned16(src) && (cols % 8 == 0) && (ld_src % 8 == 0) && (ld_dst % 8 == 0);
   const int grid = cvt_grid(rows * cols, 8 * 8);
+  cudaLaunchAttribute attr[1];
+  const cudaLaunchConfig_t cfg = dependent_launch(grid, CVT_THREADS, s, attr);
+  cudaError_t e;
   if (src_fmt == SKL_DT_F8E4M3)
-    cvt_f8_to_bf16_2d_kernel<SKL_DT_F8E4M3><<<grid, CVT_THREADS, 0, s>>>(
-        (uint16_t *)dst, ld_dst, (const uint8_t *)src, ld_src, rows, cols, vec);
+    e = cudaLaunchKernelEx(&cfg, cvt_f8_to_bf16_2d_kernel<SKL_DT_F8E4M3>, (uint16_t *)dst, ld_dst, (const uint8_t *)src,
+                           ld_src, rows, cols, vec);
   else
-    cvt_f8_to_bf16_2d_kernel<SKL_DT_F8E5M2><<<grid, CVT_THREADS, 0, s>>>(
-        (uint16_t *)dst, ld_dst, (const uint8_t *)src, ld_src, rows, cols, vec);
+    e = cudaLaunchKernelEx(&cfg, cvt_f8_to_bf16_2d_kernel<SKL_DT_F8E5M2>, (uint16_t *)dst, ld_dst, (const uint8_t *)src,
+                           ld_src, rows, cols, vec);
   SKLB_COUNT_LAUNCH();
+  if (e != cudaSuccess) return (int)e;
   return (int)cudaGetLastError();
 }
 
@@ -367,13 +392,17 @@ extern "C" int skl_b200_launch_cvt_f8_to_bf16_2d_transposed(void *dst, size_t ld
   const uint64_t cap = (uint64_t)cvt_grid(~(size_t)0 >> 8, 1);  // 8 CTAs per SM
   const int grid = (int)(tiles < cap ? tiles : cap);
   cudaStream_t s = (cudaStream_t)stream;
+  cudaLaunchAttribute attr[1];
+  const cudaLaunchConfig_t cfg = dependent_launch(grid, 256, s, attr);
+  cudaError_t e;
   if (src_fmt == SKL_DT_F8E4M3)
-    cvt_f8_to_bf16_transpose_kernel<SKL_DT_F8E4M3><<<grid, 256, 0, s>>>((uint16_t *)dst, ld_dst, (const uint8_t *)src,
-                                                                         ld_src, (uint32_t)rows, (uint32_t)cols, tr, tc);
+    e = cudaLaunchKernelEx(&cfg, cvt_f8_to_bf16_transpose_kernel<SKL_DT_F8E4M3>, (uint16_t *)dst, ld_dst,
+                           (const uint8_t *)src, ld_src, (uint32_t)rows, (uint32_t)cols, tr, tc);
   else
-    cvt_f8_to_bf16_transpose_kernel<SKL_DT_F8E5M2><<<grid, 256, 0, s>>>((uint16_t *)dst, ld_dst, (const uint8_t *)src,
-                                                                         ld_src, (uint32_t)rows, (uint32_t)cols, tr, tc);
+    e = cudaLaunchKernelEx(&cfg, cvt_f8_to_bf16_transpose_kernel<SKL_DT_F8E5M2>, (uint16_t *)dst, ld_dst,
+                           (const uint8_t *)src, ld_src, (uint32_t)rows, (uint32_t)cols, tr, tc);
   SKLB_COUNT_LAUNCH();
+  if (e != cudaSuccess) return (int)e;
   return (int)cudaGetLastError();
 }
 

@@ -35,11 +35,15 @@ __device__ __forceinline__ int64_t offs(int64_t r, int64_t c, int64_t r0, int64_
   return (r / r0) * rs1 + (r % r0) * rs0 + (c / c0) * cs1 + (c % c0) * cs0;
 }
 
-// ACC: 0 = int32 (int8 operands), 1 = fp32 (bf16 / f16 / fp8 / f32 operands), 2 = fp64 (f64 operands)
+// fp32 value rounded to fp16 and back: the rounding the fp16-accumulate GEMM applies after every statement.
+__device__ __forceinline__ float round_to_f16(float x) { return dec_f16(enc_f16(x)); }
+
+// ACC: 0 = int32 (int8 operands), 1 = fp32 (bf16 / f16 / fp8 / f32 operands), 2 = fp64 (f64 operands),
+//      3 = fp16 accumulator held as an fp32 value (fp16 operands, SKL_EPI_F16ACC)
 template <int ACC, bool BLOCKED>
 __global__ void __launch_bounds__(256) gemm_generic_kernel(const GenericParams p) {
   constexpr bool IS_INT = ACC == 0;
-  using acc_t = typename std::conditional<ACC == 0, int32_t, typename std::conditional<ACC == 1, float, double>::type>::type;
+  using acc_t = typename std::conditional<ACC == 0, int32_t, typename std::conditional<ACC == 2, double, float>::type>::type;
   __shared__ acc_t As[TK][TM + 1];
   __shared__ acc_t Bs[TK][TN + 1];
 
@@ -124,6 +128,8 @@ __global__ void __launch_bounds__(256) gemm_generic_kernel(const GenericParams p
             acc[r][c] = (acc_t)((uint32_t)acc[r][c] + (uint32_t)((int32_t)av[r] * (int32_t)bv[c]));
           else if (ACC == 2)
             acc[r][c] = (acc_t)__dadd_rn((double)acc[r][c], __dmul_rn((double)av[r], (double)bv[c]));
+          else if (ACC == 3)
+            acc[r][c] = (acc_t)round_to_f16(__fadd_rn((float)acc[r][c], __fmul_rn((float)av[r], (float)bv[c])));
           else
             acc[r][c] = (acc_t)__fadd_rn((float)acc[r][c], __fmul_rn((float)av[r], (float)bv[c]));
         }
@@ -146,6 +152,11 @@ __global__ void __launch_bounds__(256) gemm_generic_kernel(const GenericParams p
         uint32_t prod = (uint32_t)g.alpha_i * (uint32_t)(int32_t)acc[r][c];
         uint32_t old = (g.beta_i != 0) ? (uint32_t)g.beta_i * (uint32_t)*cp : 0u;
         *cp = (int32_t)(old + prod);
+      } else if (g.epilogue == SKL_EPI_F16ACC) {
+        uint16_t *cp = (uint16_t *)g.c + o;
+        const float prod = __fmul_rn(g.alpha_f, (float)acc[r][c]);  // exact: two fp16 values
+        const float v = (g.beta_f != 0.0f) ? __fadd_rn(__fmul_rn(g.beta_f, dec_f16(*cp)), prod) : prod;
+        *cp = (uint16_t)enc_f16(v);
       } else if (g.epilogue == SKL_EPI_F64) {
         double *cp = (double *)g.c + o;
         const double prod = __dmul_rn(g.alpha_d, (double)acc[r][c]);
@@ -189,6 +200,7 @@ extern "C" int skl_b200_launch_gemm_generic(const skl_b200_gemm_args *args, void
   const bool blocked = !(args->m1 == 1 && args->n1 == 1 && args->k1 == 1);
   const bool is_int = (args->ta == SKL_DT_I8);
   const bool is_f64 = (args->ta == SKL_DT_F64);
+  const bool is_f16acc = (args->epilogue == SKL_EPI_F16ACC);
   dim3 grid((unsigned)((p.N + TN - 1) / TN), (unsigned)((p.M + TM - 1) / TM));
   if (grid.y > 65535u) return (int)cudaErrorInvalidConfiguration;
   cudaStream_t s = (cudaStream_t)stream;
@@ -202,6 +214,11 @@ extern "C" int skl_b200_launch_gemm_generic(const skl_b200_gemm_args *args, void
       gemm_generic_kernel<2, true><<<grid, 256, 0, s>>>(p);
     else
       gemm_generic_kernel<2, false><<<grid, 256, 0, s>>>(p);
+  } else if (is_f16acc) {
+    if (blocked)
+      gemm_generic_kernel<3, true><<<grid, 256, 0, s>>>(p);
+    else
+      gemm_generic_kernel<3, false><<<grid, 256, 0, s>>>(p);
   } else {
     if (blocked)
       gemm_generic_kernel<1, true><<<grid, 256, 0, s>>>(p);

@@ -14,7 +14,9 @@
 //
 // Rules for users, all consequences of the single shared array:
 //   * The first call on each device looks up the array's device address (cudaGetSymbolAddress) and
-//     caches it; make that first call outside any stream capture.
+//     caches it; that first call should come before any stream capture begins.  Every call, the first
+//     included, waits for its own work on the stream it was given before it returns, so that stream
+//     must not be in capture mode during a call.
 //   * The array keeps whatever the previous call left in it.  Nothing in it has to start at zero --
 //     each call rewrites every element it later reads -- but the four status words next to it do, and
 //     the entry point clears them itself at the start of every call.
@@ -66,13 +68,15 @@ int fail(const Message &msg, int code, const char *text) {
   return code;
 }
 
-bool is_device_pointer(const void *p) {
+// Device (or managed) memory of the current device `dev`?
+bool is_device_pointer(const void *p, int dev) {
   cudaPointerAttributes at;
   if (cudaPointerGetAttributes(&at, p) != cudaSuccess) {
     (void)cudaGetLastError();
     return false;
   }
-  return at.type == cudaMemoryTypeDevice || at.type == cudaMemoryTypeManaged;
+  if (at.type == cudaMemoryTypeManaged) return true;
+  return at.type == cudaMemoryTypeDevice && at.device == dev;
 }
 
 // Once per device, with that device current: resolve the device addresses of the two arrays.
@@ -104,8 +108,11 @@ int resolve_slots(DeviceSlots **out, const Message &msg) {
 }  // namespace
 
 // C[m x n] (bf16) = narrow( (alpha * sum_k A[i,k]*widen(B[k,j])) * col_scale[j] ), A bf16, B fp8 E4M3.
-// Same arithmetic, kernels and results as skl_gemm_ex_sm100a(BF16, F8E4M3 -> BF16, beta = 0); the only
-// difference is where the widened B is kept.  Returns 0, or a skl_b200_status_t value:
+// Same arithmetic, kernels and results as skl_gemm_ex_sm100a(BF16, F8E4M3 -> BF16, beta = 0) whenever that
+// call takes the tensor-core kernel (it sends problems under 32768 multiply-adds, and layouts the tensor-core
+// kernel declines, to the any-stride kernel; this entry point always uses the tensor-core kernel and refuses
+// those layouts with code 5); the only other difference is where the widened B is kept.
+// Returns 0, or a skl_b200_status_t value:
 //   1 bad argument (null or host pointer, B with no unit stride, widened B larger than the fixed array),
 //   2 CUDA error, 4 a bounded wait inside the kernel expired, 5 layout the tensor-core kernel declines.
 // On a non-zero return a sentence saying why is written to error_text (error_text_len bytes, may be
@@ -122,9 +129,17 @@ extern "C" int skl_gemm_bf16_f8e4m3_bf16_noalloc_sm100a(size_t m, size_t n, size
   if (k == 0)
     return fail(msg, 1, "k == 0 is not served by this entry point (nothing to widen); use skl_gemm_ex_sm100a");
   if (!a || !b || !c) return fail(msg, 1, "null matrix pointer");
-  if (!is_device_pointer(a) || !is_device_pointer(b) || !is_device_pointer(c) ||
-      (col_scale && !is_device_pointer(col_scale)))
-    return fail(msg, 1, "all pointers must be device memory: staging host memory would need an allocation");
+  if (m >= (size_t(1) << 31) || n >= (size_t(1) << 31) || k >= (size_t(1) << 31))
+    return fail(msg, 1, "m, n and k must each be below 2^31");
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return fail(msg, 2, "no current CUDA device");
+  }
+  if (!is_device_pointer(a, dev) || !is_device_pointer(b, dev) || !is_device_pointer(c, dev) ||
+      (col_scale && !is_device_pointer(col_scale, dev)))
+    return fail(msg, 1, "all pointers must be device memory of the current device: staging host memory would need "
+                        "an allocation");
 
   // Orientation of B decides the shape of its widened copy: rows x cols with cols contiguous.
   size_t rows, cols, ld_src;
@@ -136,13 +151,18 @@ extern "C" int skl_gemm_bf16_f8e4m3_bf16_noalloc_sm100a(size_t m, size_t n, size
   } else {
     return fail(msg, 1, "B needs a unit stride along k or along n");
   }
-  const size_t ld_dst = (cols + 7) & ~size_t(7);  // 16-byte aligned rows for TMA
-  if (rows * ld_dst > kScratchElems) {
+  // Like the regular entry point, an n-contiguous B of a problem with at least 512 rows is written into the
+  // array k-contiguous (the tensor-core kernel is faster on that orientation; the results are the same bits).
+  const bool transpose = !k_major && m >= 512 && (reinterpret_cast<uintptr_t>(b) & 3u) == 0 && ld_src % 4 == 0;
+  const size_t out_rows = transpose ? cols : rows, out_cols = transpose ? rows : cols;
+  const size_t ld_dst = (out_cols + 7) & ~size_t(7);  // 16-byte aligned rows for TMA
+  if (out_rows > kScratchElems / ld_dst) {  // dimensions are below 2^31: no product here can wrap
     msg.set("widened B needs %zu bytes, the fixed scratch array holds %u: split the problem along n or use "
             "skl_gemm_ex_sm100a",
-            rows * ld_dst * sizeof(uint16_t), (unsigned)SKL_B200_NOALLOC_SCRATCH_BYTES);
+            out_rows * ld_dst * sizeof(uint16_t), (unsigned)SKL_B200_NOALLOC_SCRATCH_BYTES);
     return 1;
   }
+  if (transpose) k_major = true;  // rows of the copy are B's columns
 
   DeviceSlots *slots = nullptr;
   if (int rc = resolve_slots(&slots, msg)) return rc;
@@ -165,11 +185,16 @@ extern "C" int skl_gemm_bf16_f8e4m3_bf16_noalloc_sm100a(size_t m, size_t n, size
 
   cudaError_t e = cudaMemsetAsync(slots->status, 0, SKL_B200_DEVSTATUS_WORDS * sizeof(uint32_t), stream);
   if (e == cudaSuccess)
-    e = (cudaError_t)skl_b200_launch_cvt_f8_to_bf16_2d(slots->scratch, ld_dst, b, ld_src, SKL_DT_F8E4M3, rows, cols, stream);
+    e = (cudaError_t)(transpose ? skl_b200_launch_cvt_f8_to_bf16_2d_transposed(slots->scratch, ld_dst, b, ld_src,
+                                                                               SKL_DT_F8E4M3, rows, cols, stream)
+                                : skl_b200_launch_cvt_f8_to_bf16_2d(slots->scratch, ld_dst, b, ld_src, SKL_DT_F8E4M3,
+                                                                    rows, cols, stream));
   if (e == cudaSuccess) e = (cudaError_t)skl_b200_launch_gemm_tc(&g, slots->status, stream);
-  if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
+  // The status word comes back on the caller's stream too, so the only wait is for that stream (a copy on the
+  // default stream would wait for every other stream of the process).
   uint32_t word = 0;
-  if (e == cudaSuccess) e = cudaMemcpy(&word, slots->status, sizeof word, cudaMemcpyDeviceToHost);
+  if (e == cudaSuccess) e = cudaMemcpyAsync(&word, slots->status, sizeof word, cudaMemcpyDeviceToHost, stream);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
   if (e != cudaSuccess) {
     (void)cudaGetLastError();
     msg.set("%s: %s", cudaGetErrorName(e), cudaGetErrorString(e));

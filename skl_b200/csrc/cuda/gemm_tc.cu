@@ -24,7 +24,7 @@
 // shared-memory matrix descriptors and the instruction descriptor carry the difference, no
 // transposing pre-pass is needed.  Edges in M, N and K rely on TMA zero fill.
 //
-// Every mbarrier wait is bounded (about two seconds of wall time); on expiry the thread records a
+// Every mbarrier wait is bounded (two seconds of wall time unless the caller set another limit); on expiry the thread records a
 // code in the status words, raises a CTA-wide abort flag and all roles fall through to the common
 // exit, which frees TMEM.  The kernel never spins unboundedly.
 //
@@ -45,6 +45,7 @@ constexpr int BM = 128;
 constexpr int SLAB_BYTES = 128;  // bytes of K per stage row = one swizzle atom
 constexpr int NUM_THREADS = 192;
 constexpr int KIND_F16 = 0, KIND_F8 = 1, KIND_I8 = 2;
+constexpr int PLAIN_PANEL = 0x7fffffff;  // TcParams::a_panel / b_panel of a plain (unpanelled) MN-major matrix
 
 constexpr uint32_t ERR_WAIT_EMPTY = 0x101, ERR_WAIT_FULL = 0x102, ERR_WAIT_TMEM_EMPTY = 0x103,
                    ERR_WAIT_TMEM_FULL = 0x104;
@@ -56,13 +57,26 @@ struct TcParams {
   // Tail splitting (one-CTA kernel): the tiles left over after the last full round of the grid are cut
   // into `tail_split` column strips each, one strip per CTA, so the last round is short instead of idle.
   int main_tiles, tail_round, tail_units, tail_split;
-  uint32_t idesc_tail;  // instruction descriptor with N = BN / tail_split
+  // Width of a full tile: the kernel's BN, or less (a multiple of 32 columns) when narrower tiles fill the rounds
+  // of the grid better; the shared-memory stage and the accumulator keep BN columns of room either way.
+  int bn_main;
+  int main_b_atoms;        // MN-major B: boxes a full tile loads per k-slab
+  uint32_t main_b_bytes;   // bytes of B a full tile loads per k-slab
+  uint32_t idesc_tail;  // instruction descriptor with N = bn_main / tail_split
   int tail_b_atoms;     // MN-major B: boxes one strip loads per k-slab
   uint32_t tail_b_bytes;  // bytes of B one strip loads per k-slab
   int a_mn, b_mn;  // 1: operand is MN-major in global/shared memory
+  // MN-major operands are described to TMA as panels: `panel` consecutive m (n) elements, then k, then the panel
+  // index.  A plain column-major A / row-major B is a single panel as wide as the matrix; SKL's matrix-engine
+  // packed operands (TE x 1 blocks of A, 1 x TE blocks of B) are panels of TE.
+  int a_panel, b_panel;
   uint32_t idesc;
   void *c;
   int64_t rsc, csc;
+  // Blocked C (SKL's packed C): blocks of c_block_m x c_block_n elements, rsc / csc inside a block, rsc1 / csc1
+  // between blocks.  c_block_m == 0: a plain matrix.
+  int c_block_m, c_block_n;
+  int64_t rsc1, csc1;
   int tc, epilogue;
   int c_vec_ok;  // csc == 1 and rows 16-byte aligned
   int c_tma;     // C has a tensor map: results leave through shared memory and TMA stores
@@ -76,6 +90,8 @@ struct TcParams {
   int activation;
   float act_param;
   uint32_t *status;
+  uint64_t wait_ns;  // bound of every mbarrier wait
+  int skip_loads;    // testing aid: the producer announces its loads but never issues them
 };
 
 // ------------------------------------------------------------------ PTX wrappers
@@ -110,7 +126,7 @@ __device__ __forceinline__ uint64_t globaltimer_ns() {
 
 // Bounded wait.  Returns false when the wait expired or another thread of the CTA already gave up.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t *abort_flag,
-                                          uint32_t *status, uint32_t code) {
+                                          uint32_t *status, uint32_t code, uint64_t limit_ns) {
   if (mbar_try(bar, parity)) return true;
   uint64_t t0 = 0;
   for (uint32_t spins = 1;; ++spins) {
@@ -119,7 +135,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
       if (*abort_flag) return false;
       uint64_t now = globaltimer_ns();
       if (t0 == 0) t0 = now;
-      if (now - t0 > 2000000000ull) {
+      if (now - t0 > limit_ns) {
         *abort_flag = 1u;
         atomicCAS(status, 0u, code);
         return false;
@@ -133,6 +149,41 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *tm,
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
       ::"r"(dst), "l"(tm), "r"(bar), "r"(x), "r"(y)
       : "memory");
+}
+
+// MN-major operands: x = element inside the panel, y = k, z = panel.
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *tm, uint32_t bar, int x, int y, int z) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(dst), "l"(tm), "r"(bar), "r"(x), "r"(y), "r"(z)
+      : "memory");
+}
+// Box coordinates of the MN-major boxes of one tile, worked out once per tile (the division stays out of the k loop):
+// box i starts at element mn0 + i*step of the operand, i.e. at (x[i], z[i]) = (element in panel, panel).
+template <int NB>
+struct MnBoxes {
+  int x[NB], z[NB];
+  __device__ __forceinline__ void set(int mn0, int step, int panel) {
+    int zz = mn0 / panel, xx = mn0 - zz * panel;
+#pragma unroll
+    for (int i = 0; i < NB; ++i) {
+      x[i] = xx;
+      z[i] = zz;
+      xx += step;
+      if (xx >= panel) {  // panels are whole numbers of boxes; a plain matrix (one unbounded panel) never wraps
+        xx -= panel;
+        ++zz;
+      }
+    }
+  }
+};
+
+// Offset of element (row, col) of C: plain strides, or SKL's blocked description.
+__device__ __forceinline__ int64_t c_offset(const TcParams &p, int row, int col) {
+  if (p.c_block_m == 0) return (int64_t)row * p.rsc + (int64_t)col * p.csc;
+  const int bi = row / p.c_block_m, bj = col / p.c_block_n;
+  return (int64_t)bi * p.rsc1 + (int64_t)bj * p.csc1 + (int64_t)(row - bi * p.c_block_m) * p.rsc +
+         (int64_t)(col - bj * p.c_block_n) * p.csc;
 }
 
 template <int KIND>
@@ -233,17 +284,17 @@ __device__ __forceinline__ bool get_unit(const TcParams &p, int it, TileUnit &u)
   if (t < p.main_tiles) {
     tile_coords(t, p.tiles_m, p.tiles_n, p.raster_gm, mi, ni);
     u.m0 = mi * BM;
-    u.n0 = ni * BN;
-    u.ncols = BN;
+    u.n0 = ni * p.bn_main;
+    u.ncols = p.bn_main;
     u.idesc = p.idesc;
     return true;
   }
   if (it == p.tail_round && (int)blockIdx.x < p.tail_units) {
     const int tt = p.main_tiles + (int)blockIdx.x / p.tail_split, sub = (int)blockIdx.x % p.tail_split;
     tile_coords(tt, p.tiles_m, p.tiles_n, p.raster_gm, mi, ni);
-    u.ncols = BN / p.tail_split;
+    u.ncols = p.bn_main / p.tail_split;
     u.m0 = mi * BM;
-    u.n0 = ni * BN + sub * u.ncols;
+    u.n0 = ni * p.bn_main + sub * u.ncols;
     u.idesc = p.idesc_tail;
     return true;
   }
@@ -275,6 +326,13 @@ __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap
   asm volatile(
       "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
       ::"r"(dst), "l"(tm), "r"(cluster_bar), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const CUtensorMap *tm, uint32_t cluster_bar, int x, int y,
+                                                 int z) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(dst), "l"(tm), "r"(cluster_bar), "r"(x), "r"(y), "r"(z)
       : "memory");
 }
 template <int KIND>
@@ -421,7 +479,8 @@ __device__ __forceinline__ float epilogue_chunk(const TcParams &p, const uint32_
                                                 int col0, const float *cs, const float *bs, float rs,
                                                 float row_bias, EpiStage &st, int lane) {
   const int ncols = (p.N - col0) < 32 ? (p.N - col0) : 32;
-  const int64_t base = (int64_t)row * p.rsc + (int64_t)col0 * p.csc;
+  // a 32-column chunk never crosses a block of a blocked C (block widths are multiples of 32)
+  const int64_t base = c_offset(p, row, col0);
   if (p.epilogue == SKL_EPI_INT) {
     uint32_t o[32];
     if (p.beta_i != 0 && row_ok) {
@@ -672,31 +731,48 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
       for (int it = 0; ok && get_unit<BN>(p, it, u); ++it) {
         const int m0 = u.m0, n0 = u.n0;
         // a tail strip loads only its own columns of B: a narrower box (k-major, through tmBs) or fewer boxes
-        const bool strip = u.ncols != BN;
-        const uint32_t stage_tx = Cfg::A_BYTES + (strip ? p.tail_b_bytes : (uint32_t)Cfg::B_BYTES);
-        const int b_boxes = strip ? p.tail_b_atoms : B_ATOMS;
+        const bool strip = u.ncols != p.bn_main;
+        const uint32_t stage_tx = Cfg::A_BYTES + (strip ? p.tail_b_bytes : p.main_b_bytes);
+        const int b_boxes = strip ? p.tail_b_atoms : p.main_b_atoms;
+        MnBoxes<A_ATOMS> abox;
+        MnBoxes<B_ATOMS> bbox;
+        if (p.a_mn && p.a_panel != PLAIN_PANEL) abox.set(m0, MN_PER_ATOM, p.a_panel);
+        if (p.b_mn && p.b_panel != PLAIN_PANEL) bbox.set(n0, MN_PER_ATOM, p.b_panel);
         for (int kb = 0; kb < p.num_kb; ++kb) {
-          if (!mbar_wait(empty_bar + 8 * stage, phase ^ 1u, abort_flag, p.status, ERR_WAIT_EMPTY)) {
+          if (!mbar_wait(empty_bar + 8 * stage, phase ^ 1u, abort_flag, p.status, ERR_WAIT_EMPTY, p.wait_ns)) {
             ok = false;
             break;
           }
           const uint32_t fb = full_bar + 8 * stage;
           const uint32_t sa = tiles + stage * Cfg::STAGE_BYTES, sb = sa + Cfg::A_BYTES;
           mbar_expect_tx(fb, stage_tx);
+          if (p.skip_loads) {  // testing aid: the bytes never arrive, the waits on this stage run out
+            ok = false;
+            break;
+          }
           const int k0 = kb * BKE;
           if (!p.a_mn) {
             tma_load_2d(sa, &tmA, fb, k0, m0);
           } else {
 #pragma unroll
-            for (int i = 0; i < A_ATOMS; ++i)
-              tma_load_2d(sa + i * ATOM_BYTES, &tmA, fb, m0 + i * MN_PER_ATOM, k0);
+            for (int i = 0; i < A_ATOMS; ++i) {
+              if (p.a_panel == PLAIN_PANEL)
+                tma_load_2d(sa + i * ATOM_BYTES, &tmA, fb, m0 + i * MN_PER_ATOM, k0);
+              else
+                tma_load_3d(sa + i * ATOM_BYTES, &tmA, fb, abox.x[i], k0, abox.z[i]);
+            }
           }
           if (!p.b_mn) {
             tma_load_2d(sb, strip ? &tmBs : &tmB, fb, k0, n0);
           } else {
 #pragma unroll
             for (int i = 0; i < B_ATOMS; ++i)
-              if (i < b_boxes) tma_load_2d(sb + i * ATOM_BYTES, &tmB, fb, n0 + i * MN_PER_ATOM, k0);
+              if (i < b_boxes) {
+                if (p.b_panel == PLAIN_PANEL)
+                  tma_load_2d(sb + i * ATOM_BYTES, &tmB, fb, n0 + i * MN_PER_ATOM, k0);
+                else
+                  tma_load_3d(sb + i * ATOM_BYTES, &tmB, fb, bbox.x[i], k0, bbox.z[i]);
+              }
           }
           if (++stage == Cfg::STAGES) {
             stage = 0;
@@ -717,12 +793,12 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
       const uint32_t b_adv = p.b_mn ? (UMMA_KE * SLAB_BYTES) >> 4 : 32 >> 4;
       TileUnit u;
       for (int it = 0; ok && get_unit<BN>(p, it, u); ++it) {
-        if (!mbar_wait(tempty_bar + 8 * acc, acc_phase ^ 1u, abort_flag, p.status, ERR_WAIT_TMEM_EMPTY))
+        if (!mbar_wait(tempty_bar + 8 * acc, acc_phase ^ 1u, abort_flag, p.status, ERR_WAIT_TMEM_EMPTY, p.wait_ns))
           break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
         for (int kb = 0; kb < p.num_kb; ++kb) {
-          if (!mbar_wait(full_bar + 8 * stage, phase, abort_flag, p.status, ERR_WAIT_FULL)) {
+          if (!mbar_wait(full_bar + 8 * stage, phase, abort_flag, p.status, ERR_WAIT_FULL, p.wait_ns)) {
             ok = false;
             break;
           }
@@ -760,7 +836,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
       EpiVectors<BN>::fill(p, cs, bs, n0, u.ncols, lane);
       const float rs = (p.row_scale && row < p.M) ? __ldg(p.row_scale + row) : 1.0f;
       const float row_bias = (p.bias && p.bias_per_row && row < p.M) ? __ldg(p.bias + row) : 0.0f;
-      if (!mbar_wait(tfull_bar + 8 * acc, acc_phase, abort_flag, p.status, ERR_WAIT_TMEM_FULL)) break;
+      if (!mbar_wait(tfull_bar + 8 * acc, acc_phase, abort_flag, p.status, ERR_WAIT_TMEM_FULL, p.wait_ns)) break;
       tc_fence_after();
       const uint32_t taddr = tmem_base + acc * BN + ((uint32_t)(quad * 32) << 16);
 #pragma unroll 1
@@ -894,28 +970,44 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         int mi, ni;
         tile_coords(t, p.tiles_m, p.tiles_n, p.raster_gm, mi, ni);
         const int m0 = mi * (2 * BM) + (int)rank * BM, n0 = ni * BN + (int)rank * BH;
+        MnBoxes<A_ATOMS> abox;
+        MnBoxes<B_ATOMS> bbox;
+        if (p.a_mn && p.a_panel != PLAIN_PANEL) abox.set(m0, MN_PER_ATOM, p.a_panel);
+        if (p.b_mn && p.b_panel != PLAIN_PANEL) bbox.set(n0, MN_PER_ATOM, p.b_panel);
         for (int kb = 0; kb < p.num_kb; ++kb) {
-          if (!mbar_wait(empty_bar + 8 * stage, phase ^ 1u, abort_flag, p.status, ERR_WAIT_EMPTY)) {
+          if (!mbar_wait(empty_bar + 8 * stage, phase ^ 1u, abort_flag, p.status, ERR_WAIT_EMPTY, p.wait_ns)) {
             ok = false;
             break;
           }
           const uint32_t fb = leader_full + 8 * stage;
           const uint32_t sa = tiles + stage * Cfg::STAGE_BYTES, sb = sa + Cfg::A_BYTES;
           if (rank == 0) mbar_expect_tx(full_bar + 8 * stage, 2 * Cfg::STAGE_BYTES);
+          if (p.skip_loads) {  // testing aid, as in gemm_tc_kernel
+            ok = false;
+            break;
+          }
           const int k0 = kb * BKE;
           if (!p.a_mn) {
             tma_load_2d_pair(sa, &tmA, fb, k0, m0);
           } else {
 #pragma unroll
-            for (int i = 0; i < A_ATOMS; ++i)
-              tma_load_2d_pair(sa + i * ATOM_BYTES, &tmA, fb, m0 + i * MN_PER_ATOM, k0);
+            for (int i = 0; i < A_ATOMS; ++i) {
+              if (p.a_panel == PLAIN_PANEL)
+                tma_load_2d_pair(sa + i * ATOM_BYTES, &tmA, fb, m0 + i * MN_PER_ATOM, k0);
+              else
+                tma_load_3d_pair(sa + i * ATOM_BYTES, &tmA, fb, abox.x[i], k0, abox.z[i]);
+            }
           }
           if (!p.b_mn) {
             tma_load_2d_pair(sb, &tmB, fb, k0, n0);
           } else {
 #pragma unroll
-            for (int i = 0; i < B_ATOMS; ++i)
-              tma_load_2d_pair(sb + i * ATOM_BYTES, &tmB, fb, n0 + i * MN_PER_ATOM, k0);
+            for (int i = 0; i < B_ATOMS; ++i) {
+              if (p.b_panel == PLAIN_PANEL)
+                tma_load_2d_pair(sb + i * ATOM_BYTES, &tmB, fb, n0 + i * MN_PER_ATOM, k0);
+              else
+                tma_load_3d_pair(sb + i * ATOM_BYTES, &tmB, fb, bbox.x[i], k0, bbox.z[i]);
+            }
           }
           if (++stage == Cfg::STAGES) {
             stage = 0;
@@ -934,12 +1026,12 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
       const uint32_t a_adv = p.a_mn ? (UMMA_KE * SLAB_BYTES) >> 4 : 32 >> 4;
       const uint32_t b_adv = p.b_mn ? (UMMA_KE * SLAB_BYTES) >> 4 : 32 >> 4;
       for (int t = pair; ok && t < num_tiles; t += num_pairs) {
-        if (!mbar_wait(tempty_bar + 8 * acc, acc_phase ^ 1u, abort_flag, p.status, ERR_WAIT_TMEM_EMPTY))
+        if (!mbar_wait(tempty_bar + 8 * acc, acc_phase ^ 1u, abort_flag, p.status, ERR_WAIT_TMEM_EMPTY, p.wait_ns))
           break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
         for (int kb = 0; kb < p.num_kb; ++kb) {
-          if (!mbar_wait(full_bar + 8 * stage, phase, abort_flag, p.status, ERR_WAIT_FULL)) {
+          if (!mbar_wait(full_bar + 8 * stage, phase, abort_flag, p.status, ERR_WAIT_FULL, p.wait_ns)) {
             ok = false;
             break;
           }
@@ -979,7 +1071,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
       EpiVectors<BN>::fill(p, cs, bs, n0, BN, lane);
       const float rs = (p.row_scale && row < p.M) ? __ldg(p.row_scale + row) : 1.0f;
       const float row_bias = (p.bias && p.bias_per_row && row < p.M) ? __ldg(p.bias + row) : 0.0f;
-      if (!mbar_wait(tfull_bar + 8 * acc, acc_phase, abort_flag, p.status, ERR_WAIT_TMEM_FULL)) break;
+      if (!mbar_wait(tfull_bar + 8 * acc, acc_phase, abort_flag, p.status, ERR_WAIT_TMEM_FULL, p.wait_ns)) break;
       tc_fence_after();
       const uint32_t taddr = tmem_base + acc * BN + ((uint32_t)(quad * 32) << 16);
 #pragma unroll 1
@@ -1036,13 +1128,15 @@ EncodeTiledFn encode_fn() {
 
 struct OperandView {
   int mn_major;     // 1: unit stride runs along m (A) / n (B)
-  int64_t ld;       // leading stride in elements
+  int64_t ld;       // leading stride in elements (MN-major: the stride between consecutive k)
   bool ok;
+  // MN-major only: the operand as `panels` panels of `panel` consecutive m (n) elements, `panel_ld` elements apart
+  int64_t panel, panels, panel_ld;
 };
 
 // extent_mn x K operand with strides (s_mn, s_k) in elements.
 OperandView classify(const void *base, int64_t extent_mn, int64_t K, int64_t s_mn, int64_t s_k, int es) {
-  OperandView v{0, 0, false};
+  OperandView v{0, 0, false, extent_mn, 1, 0};
   if ((reinterpret_cast<uintptr_t>(base) & 15u) != 0) return v;
   auto ld_ok = [&](int64_t ld, int64_t inner, int64_t outer) {
     if (outer <= 1) return true;
@@ -1058,6 +1152,36 @@ OperandView classify(const void *base, int64_t extent_mn, int64_t K, int64_t s_m
     v.ok = true;
   }
   return v;
+}
+
+// SKL's matrix-engine packed operand (src/gemm/gemm_i8c_i8_i32_xsfmm32a8i.h:86-100): blocks of `panel` x 1 (A) or
+// 1 x `panel` (B) elements with unit stride inside a block, `k_stride` between consecutive k and `panel_stride`
+// between block rows (A) / block columns (B).  TMA reads it as an MN-major operand when a panel is a whole number
+// of 128-byte rows.
+OperandView classify_panels(const void *base, int64_t panel, int64_t panels, int64_t K, int64_t k_stride,
+                            int64_t panel_stride, int es) {
+  OperandView v{1, k_stride, false, panel, panels, panel_stride};
+  if ((reinterpret_cast<uintptr_t>(base) & 15u) != 0) return v;
+  if (panel <= 0 || (panel * es) % SLAB_BYTES != 0) return v;
+  if (K > 1 && (k_stride < panel || ((k_stride * es) & 15) != 0)) return v;
+  if (panels > 1 && (panel_stride < panel || ((panel_stride * es) & 15) != 0)) return v;
+  v.ok = true;
+  return v;
+}
+
+// The two operand views of a problem: plain matrices (one block per dimension) or the panel form above
+// (k0 == 1: every k is its own block row / column).
+bool operand_views(const skl_b200_gemm_args *g, int es, OperandView &va, OperandView &vb) {
+  const int64_t K = (int64_t)(g->k0 * g->k1);
+  if (g->m1 == 1 && g->n1 == 1 && g->k1 == 1) {
+    va = classify(g->a, (int64_t)g->m0, K, g->rsa0, g->csa0, es);
+    vb = classify(g->b, (int64_t)g->n0, K, g->csb0, g->rsb0, es);
+    return va.ok && vb.ok;
+  }
+  if (g->k0 != 1 || g->rsa0 != 1 || g->csb0 != 1) return false;
+  va = classify_panels(g->a, (int64_t)g->m0, (int64_t)g->m1, K, g->csa1, g->rsa1, es);
+  vb = classify_panels(g->b, (int64_t)g->n0, (int64_t)g->n1, K, g->rsb1, g->csb1, es);
+  return va.ok && vb.ok;
 }
 
 int kind_of(int ta, int tb) {
@@ -1076,24 +1200,42 @@ bool make_map(CUtensorMap *tm, int kind, int dt, const void *base, const Operand
   CUtensorMapDataType cdt = kind == KIND_F16 ? (dt == SKL_DT_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
                                                                   : CU_TENSOR_MAP_DATA_TYPE_FLOAT16)
                                              : CU_TENSOR_MAP_DATA_TYPE_UINT8;
-  cuuint64_t dims[2], strides[1];
-  cuuint32_t box[2], estr[2] = {1, 1};
+  cuuint64_t dims[3], strides[2];
+  cuuint32_t box[3], estr[3] = {1, 1, 1};
   const int per_row = SLAB_BYTES / es;  // elements across 128 bytes
+  cuuint32_t rank = 2;
   if (!v.mn_major) {
     dims[0] = (cuuint64_t)K;
     dims[1] = (cuuint64_t)extent_mn;
     box[0] = (cuuint32_t)per_row;
     box[1] = (cuuint32_t)box_mn;
-  } else {
+    int64_t ld = v.ld;
+    if (dims[1] <= 1) ld = (int64_t)((dims[0] * es + 15) / 16 * 16) / es;  // stride unused; keep it legal
+    strides[0] = (cuuint64_t)ld * es;
+  } else if (v.panels <= 1) {
     dims[0] = (cuuint64_t)extent_mn;
     dims[1] = (cuuint64_t)K;
     box[0] = (cuuint32_t)per_row;
     box[1] = (cuuint32_t)per_row;  // BKE rows
+    int64_t ld = v.ld;
+    if (dims[1] <= 1) ld = (int64_t)((dims[0] * es + 15) / 16 * 16) / es;  // stride unused; keep it legal
+    strides[0] = (cuuint64_t)ld * es;
+  } else {
+    // (element in panel, k, panel)
+    rank = 3;
+    dims[0] = (cuuint64_t)v.panel;
+    dims[1] = (cuuint64_t)K;
+    dims[2] = (cuuint64_t)v.panels;
+    box[0] = (cuuint32_t)per_row;
+    box[1] = (cuuint32_t)per_row;  // BKE rows
+    box[2] = 1;
+    int64_t ld = v.ld;
+    if (dims[1] <= 1) ld = (int64_t)((dims[0] * es + 15) / 16 * 16) / es;  // stride unused; keep it legal
+    strides[0] = (cuuint64_t)ld * es;
+    int64_t pld = v.panels > 1 ? v.panel_ld : ld;  // unused for a single panel; keep it legal
+    strides[1] = (cuuint64_t)pld * es;
   }
-  int64_t ld = v.ld;
-  if (dims[1] <= 1) ld = (int64_t)((dims[0] * es + 15) / 16 * 16) / es;  // stride unused; keep it legal
-  strides[0] = (cuuint64_t)ld * es;
-  CUresult r = enc(tm, cdt, 2, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+  CUresult r = enc(tm, cdt, rank, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS;
@@ -1304,16 +1446,23 @@ bool use_pair_kernel(int kind, int64_t M, int64_t N, const OperandView &vb) {
 using namespace sklb;
 
 extern "C" int skl_b200_gemm_tc_supported(const skl_b200_gemm_args *g) {
-  if (g->m1 != 1 || g->n1 != 1 || g->k1 != 1) return 0;
   const int kind = kind_of(g->ta, g->tb);
   if (kind < 0) return 0;
-  const int64_t M = (int64_t)g->m0, N = (int64_t)g->n0, K = (int64_t)g->k0;
+  if (g->epilogue != SKL_EPI_INT && g->epilogue != SKL_EPI_FLOAT) return 0;  // fp16 / fp64 accumulators: CUDA cores
+  if (g->m0 >= (1ull << 31) || g->m1 >= (1ull << 31) || g->n0 >= (1ull << 31) || g->n1 >= (1ull << 31) ||
+      g->k0 >= (1ull << 31) || g->k1 >= (1ull << 31))
+    return 0;
+  const int64_t M = (int64_t)(g->m0 * g->m1), N = (int64_t)(g->n0 * g->n1), K = (int64_t)(g->k0 * g->k1);
   if (M < 1 || N < 1 || K < 1) return 0;
   if (M >= (1ll << 31) - 256 || N >= (1ll << 31) - 256 || K >= (1ll << 31) - 256) return 0;
   if (kind == KIND_I8 && K > 65536) return 0;  // keeps |acc| < 2^31 so no wrap-around question arises
   const int es = kind == KIND_F16 ? 2 : 1;
-  if (!classify(g->a, M, K, g->rsa0, g->csa0, es).ok) return 0;
-  if (!classify(g->b, N, K, g->csb0, g->rsb0, es).ok) return 0;
+  OperandView va, vb;
+  if (!operand_views(g, es, va, vb)) return 0;
+  if (g->m1 != 1 || g->n1 != 1) {
+    // blocked C: a 32-column chunk of the epilogue must stay inside one block
+    if (g->n0 % 32 != 0) return 0;
+  }
   if (g->epilogue == SKL_EPI_INT) {
     if (kind != KIND_I8 || g->tc != SKL_DT_I32) return 0;
   } else {
@@ -1327,32 +1476,75 @@ extern "C" int skl_b200_gemm_tc_supported(const skl_b200_gemm_args *g) {
 
 extern "C" int skl_b200_launch_gemm_tc(const skl_b200_gemm_args *g, uint32_t *dev_status, void *stream) {
   const int kind = kind_of(g->ta, g->tb);
-  const int64_t M = (int64_t)g->m0, N = (int64_t)g->n0, K = (int64_t)g->k0;
+  const int64_t M = (int64_t)(g->m0 * g->m1), N = (int64_t)(g->n0 * g->n1), K = (int64_t)(g->k0 * g->k1);
   const int es = kind == KIND_F16 ? 2 : 1;
-  const OperandView va = classify(g->a, M, K, g->rsa0, g->csa0, es);
-  const OperandView vb = classify(g->b, N, K, g->csb0, g->rsb0, es);
-  if (kind < 0 || !va.ok || !vb.ok) return (int)cudaErrorInvalidValue;
+  OperandView va, vb;
+  if (kind < 0 || !operand_views(g, es, va, vb)) return (int)cudaErrorInvalidValue;
+  const bool blocked_c = g->m1 != 1 || g->n1 != 1;
   const bool pair = use_pair_kernel(kind, M, N, vb);
   const int bn = pair ? 256 : pick_bn(M, N, kind, vb.mn_major != 0);
   const int tile_rows = pair ? 2 * BM : BM;
 
+  // Full tiles may be narrower than the kernel's 256 columns when that fills the rounds of the grid better
+  // (one-CTA kernel only).  Candidates keep whole 32-column epilogue chunks and, for an MN-major B, whole boxes.
+  int bn_main = bn;
+  if (!pair && bn == 256) {
+    const int step = vb.mn_major ? SLAB_BYTES / es : 32;
+    const int64_t tm = (M + BM - 1) / BM;
+    const int sms = sm_count();
+    static const int forced = [] {
+      const char *e = getenv("SKL_B200_TC_BN");  // tuning override
+      return e ? atoi(e) : 0;
+    }();
+    double best = 1e300;
+    for (int w = 256; w >= 160; w -= 32) {
+      if (w % step != 0) continue;
+      const int64_t T = tm * ((N + w - 1) / w);
+      const int64_t full = T / sms, rem = T % sms;
+      // cost of one tile ~ its width plus a fixed part (pipeline fill, epilogue tail, narrower MMAs being a little
+      // less efficient); a short last round is cut into strips (see below), so it costs about a strip
+      double cost = (double)full * (w + 28.0);
+      if (rem > 0) {
+        int split = 1;
+        if (T > sms && rem * 2 <= sms && (w / 2) % 32 == 0 && (w / 2) % step == 0) split = 2;
+        if (T > sms && rem * 4 <= sms && (w / 4) % 32 == 0 && (w / 4) % step == 0) split = 4;
+        cost += (double)w / split + 28.0;
+      }
+      if (forced ? w == forced : cost < best) {
+        best = cost;
+        bn_main = w;
+        if (forced) break;
+      }
+    }
+  }
+
   CUtensorMap tmA, tmB;
   if (!make_map(&tmA, kind, g->ta, g->a, va, M, K, BM)) return (int)cudaErrorInvalidValue;
-  if (!make_map(&tmB, kind, g->tb, g->b, vb, N, K, pair ? bn / 2 : bn)) return (int)cudaErrorInvalidValue;
+  if (!make_map(&tmB, kind, g->tb, g->b, vb, N, K, pair ? bn / 2 : bn_main)) return (int)cudaErrorInvalidValue;
 
   TcParams p;
   p.M = (int)M;
   p.N = (int)N;
   p.K = (int)K;
   p.tiles_m = (int)((M + tile_rows - 1) / tile_rows);
-  p.tiles_n = (int)((N + bn - 1) / bn);
+  p.tiles_n = (int)((N + bn_main - 1) / bn_main);
+  p.bn_main = bn_main;
   const int bke = SLAB_BYTES / es;
   p.num_kb = (int)((K + bke - 1) / bke);
   p.a_mn = va.mn_major;
   p.b_mn = vb.mn_major;
+  // A plain MN-major matrix keeps its 2-D tensor map and box-aligned x (TMA needs x * element size to be a multiple
+  // of 16 bytes; a tile that reaches past the last row / column reads the zero fill).  Panelled operands get a 3-D
+  // map; panels are whole numbers of boxes (classify_panels), so x stays aligned there too.
+  p.a_panel = va.panels > 1 ? (int)va.panel : PLAIN_PANEL;
+  p.b_panel = vb.panels > 1 ? (int)vb.panel : PLAIN_PANEL;
+  p.c_block_m = blocked_c ? (int)g->m0 : 0;
+  p.c_block_n = blocked_c ? (int)g->n0 : 0;
+  p.rsc1 = g->rsc1;
+  p.csc1 = g->csc1;
   const uint32_t cfmt = kind == KIND_I8 ? 2u : 1u;  // S32 : F32 accumulator
   p.idesc = (cfmt << 4) | (fmt_code(kind, g->ta) << 7) | (fmt_code(kind, g->tb) << 10) |
-            ((uint32_t)va.mn_major << 15) | ((uint32_t)vb.mn_major << 16) | ((uint32_t)(bn >> 3) << 17) |
+            ((uint32_t)va.mn_major << 15) | ((uint32_t)vb.mn_major << 16) | ((uint32_t)(bn_main >> 3) << 17) |
             ((uint32_t)(tile_rows >> 4) << 24);
   {
     // rasterisation group: keep the A rows of one group near 32 MiB (a quarter of the L2)
@@ -1374,23 +1566,27 @@ extern "C" int skl_b200_launch_gemm_tc(const skl_b200_gemm_args *g, uint32_t *de
     const bool enabled = !(e && atoi(e) == 0);
     if (enabled && !pair && bn == 256 && T > G && rem > 0 && rem * 2 <= G) {
       const int atom_cols = vb.mn_major ? SLAB_BYTES / es : 32;  // columns per MN-major box; else the epilogue chunk
-      int split = 2;
-      if (rem * 4 <= G && bn / 4 >= atom_cols && bn / 4 >= 32) split = 4;
-      if (bn / split >= atom_cols) {
+      int split = 1;
+      if ((bn_main / 2) % 32 == 0 && (bn_main / 2) % atom_cols == 0) split = 2;
+      if (rem * 4 <= G && (bn_main / 4) % 32 == 0 && (bn_main / 4) % atom_cols == 0) split = 4;
+      if (split > 1) {
         p.main_tiles = T - rem;
         p.tail_round = p.main_tiles / G;
         p.tail_split = split;
         p.tail_units = rem * split;
       }
     }
-    p.idesc_tail = (p.idesc & ~(0x3Fu << 17)) | ((uint32_t)((bn / p.tail_split) >> 3) << 17);
-    const int strip_cols = bn / p.tail_split, per_atom = SLAB_BYTES / es;
+    p.idesc_tail = (p.idesc & ~(0x3Fu << 17)) | ((uint32_t)((bn_main / p.tail_split) >> 3) << 17);
+    const int strip_cols = bn_main / p.tail_split, per_atom = SLAB_BYTES / es;
     p.tail_b_atoms = (strip_cols + per_atom - 1) / per_atom;
     p.tail_b_bytes = vb.mn_major ? (uint32_t)p.tail_b_atoms * (uint32_t)(per_atom * SLAB_BYTES)
                                  : (uint32_t)strip_cols * SLAB_BYTES;
+    p.main_b_atoms = (bn_main + per_atom - 1) / per_atom;
+    p.main_b_bytes = vb.mn_major ? (uint32_t)p.main_b_atoms * (uint32_t)(per_atom * SLAB_BYTES)
+                                 : (uint32_t)bn_main * SLAB_BYTES;
   }
   CUtensorMap tmBs = tmB;  // the strips' own box of B (k-major B only; MN-major strips load fewer boxes of tmB)
-  if (p.tail_split > 1 && !vb.mn_major && !make_map(&tmBs, kind, g->tb, g->b, vb, N, K, bn / p.tail_split))
+  if (p.tail_split > 1 && !vb.mn_major && !make_map(&tmBs, kind, g->tb, g->b, vb, N, K, bn_main / p.tail_split))
     return (int)cudaErrorInvalidValue;
   p.c = g->c;
   p.rsc = g->rsc0;
@@ -1399,7 +1595,8 @@ extern "C" int skl_b200_launch_gemm_tc(const skl_b200_gemm_args *g, uint32_t *de
   p.epilogue = g->epilogue;
   const int cs = dtype_size(g->tc);
   p.c_vec_ok = (g->csc0 == 1 && (reinterpret_cast<uintptr_t>(g->c) & 15u) == 0 &&
-                (M <= 1 || ((g->rsc0 * cs) & 15) == 0))
+                (M <= 1 || ((g->rsc0 * cs) & 15) == 0) &&
+                (!blocked_c || (((g->rsc1 * cs) & 15) == 0 && ((g->csc1 * cs) & 15) == 0)))
                    ? 1
                    : 0;
   // Results leave through TMA stores when C is a plain row-major matrix with 16-byte-aligned rows; any other C
@@ -1410,7 +1607,8 @@ extern "C" int skl_b200_launch_gemm_tc(const skl_b200_gemm_args *g, uint32_t *de
     const char *e = getenv("SKL_B200_TC_TMA_STORE");
     // The row length must be a whole number of 16-byte units: a store box that crosses the matrix edge inside
     // such a unit was observed to write the unit's remaining bytes.
-    if (p.c_vec_ok && (N * cs) % 16 == 0 && !(e && atoi(e) == 0) && make_c_map(&tmC, g->c, M, N, g->rsc0, cs))
+    if (!blocked_c && p.c_vec_ok && (N * cs) % 16 == 0 && !(e && atoi(e) == 0) &&
+        make_c_map(&tmC, g->c, M, N, g->rsc0, cs))
       p.c_tma = 1;
   }
   p.alpha_i = g->alpha_i;
@@ -1426,6 +1624,8 @@ extern "C" int skl_b200_launch_gemm_tc(const skl_b200_gemm_args *g, uint32_t *de
   p.activation = g->activation;
   p.act_param = g->act_param;
   p.status = dev_status;
+  p.wait_ns = (uint64_t)(g->wait_limit_ms ? g->wait_limit_ms : 2000u) * 1000000ull;
+  p.skip_loads = g->debug_skip_loads;
   cudaStream_t s = (cudaStream_t)stream;
 
   if (pair) {

@@ -296,9 +296,12 @@ __device__ __forceinline__ float activation_value(int act, float p, float v, flo
 
 // *addr = max(*addr, v) for floats (NaN never wins): the IEEE ordering of non-negative floats equals the
 // ordering of their bit patterns as signed integers, that of negative floats the reverse as unsigned.
+// The branch is on the sign bit, not on v >= 0: -0.0 belongs with the negative patterns (it is the largest of
+// them), so a maximum over values that are all <= -0.0 ends at -0.0 and +0.0 still wins over -0.0, which is
+// the bit pattern a sequential `if (v > max) max = v` over the same values can end with.
 __device__ __forceinline__ void atomic_max_f32(float *addr, float v) {
   if (!(v == v)) return;
-  if (v >= 0.0f)
+  if ((__float_as_uint(v) >> 31) == 0u)
     atomicMax(reinterpret_cast<int *>(addr), __float_as_int(v));
   else
     atomicMin(reinterpret_cast<unsigned int *>(addr), __float_as_uint(v));

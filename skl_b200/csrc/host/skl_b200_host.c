@@ -13,6 +13,7 @@
 #include "../abi.h"
 
 #include <cuda_runtime_api.h>
+#include <pthread.h>
 #include <stdio.h>
 #include <stdlib.h>
 #include <string.h>
@@ -54,6 +55,9 @@ typedef struct {
   cudaEvent_t *prof_ev;
   int prof_cap, prof_used;
   /* row-chunk pipeline for host operands */
+  int exit_registered; /* this thread's exit hook (thread_exit_release) is in place */
+  unsigned wait_limit_ms; /* skl_b200_set_wait_limit: bound of the kernels' device-side waits, 0 = default */
+  int debug_skip_loads;   /* skl_b200_debug_skip_loads */
   int pipe_ready;
   cudaStream_t s_in, s_out;
   cudaEvent_t ev_in[PIPE_MAX_CHUNKS], ev_done[PIPE_MAX_CHUNKS], ev_ready;
@@ -97,12 +101,52 @@ static void release_resources(void) {
   g_ctx.device = -1;
 }
 
+/* A thread that used the library owns device workspaces, pinned status words, streams and events.  They are
+ * released when the thread ends: a pthread key whose destructor runs at thread exit (registered by the
+ * thread's first call) makes the owning device current and frees them.  The main thread's resources go with
+ * the process.  skl_b200_release_workspace() does the same on request. */
+static pthread_key_t g_exit_key;
+static pthread_once_t g_exit_once = PTHREAD_ONCE_INIT;
+
+static void thread_exit_release(void *arg) {
+  (void)arg;
+  if (g_ctx.device < 0) return;
+  int cur = -1;
+  if (cudaGetDevice(&cur) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return; /* the runtime is already gone (process teardown): nothing left to free */
+  }
+  if (cur != g_ctx.device && cudaSetDevice(g_ctx.device) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return;
+  }
+  (void)cudaStreamSynchronize((cudaStream_t)g_ctx.stream);
+  release_resources();
+  if (g_ctx.prof_ev) {
+    for (int i = 0; i < 2 * g_ctx.prof_cap; ++i) (void)cudaEventDestroy(g_ctx.prof_ev[i]);
+    free(g_ctx.prof_ev);
+    g_ctx.prof_ev = 0;
+  }
+  (void)cudaGetLastError();
+}
+
+static void make_exit_key(void) { (void)pthread_key_create(&g_exit_key, thread_exit_release); }
+
+static void register_thread_exit(void) {
+  (void)pthread_once(&g_exit_once, make_exit_key);
+  if (!g_ctx.exit_registered) {
+    /* any non-null value makes the destructor run for this thread */
+    if (pthread_setspecific(g_exit_key, &g_ctx) == 0) g_ctx.exit_registered = 1;
+  }
+}
+
 /* Start of every public call: clears the status, binds the cached resources to the current device. */
 static int begin_call(void) {
   g_ctx.status = SKL_B200_OK;
   g_ctx.cuda_err[0] = 0;
   g_ctx.last_launches = 0;
   (void)skl_b200_launch_counter(1);
+  register_thread_exit();
   int dev = -1;
   if (!cuda_ok(cudaGetDevice(&dev))) return 0;
   if (dev != g_ctx.device) {
@@ -125,6 +169,21 @@ static int begin_call(void) {
 }
 
 static void end_call(void) { g_ctx.last_launches = skl_b200_launch_counter(0); }
+
+/* End of every public call that got past begin_call().  A call that failed half way may have queued copies to or
+ * from the caller's host buffers (staging, the row-chunk pipeline): they are waited for before the call returns,
+ * so that the caller, who sees the error status, may free or reuse those buffers at once. */
+static void leave_call(void) {
+  if (g_ctx.status != SKL_B200_OK) {
+    (void)cudaStreamSynchronize((cudaStream_t)g_ctx.stream);
+    if (g_ctx.pipe_ready) {
+      (void)cudaStreamSynchronize(g_ctx.s_in);
+      (void)cudaStreamSynchronize(g_ctx.s_out);
+    }
+    (void)cudaGetLastError();
+  }
+  end_call();
+}
 
 static uint32_t *device_status_words(void) {
   if (!g_ctx.dev_status) {
@@ -215,6 +274,8 @@ void skl_b200_set_static_weights(int enabled) { g_ctx.static_weights = enabled !
 skl_b200_path_t skl_b200_last_path(void) { return g_ctx.last_path; }
 int skl_b200_last_launch_count(void) { return g_ctx.last_launches; }
 void skl_b200_force_path(int path) { g_ctx.force_path = path; }
+void skl_b200_set_wait_limit(unsigned milliseconds) { g_ctx.wait_limit_ms = milliseconds; }
+void skl_b200_debug_skip_loads(int enabled) { g_ctx.debug_skip_loads = enabled != 0; }
 
 void skl_b200_profile_begin(int max_calls) {
   if (g_ctx.prof_ev) {
@@ -409,11 +470,14 @@ static int widen_fp8_operand(skl_b200_gemm_args *g) {
 static int reads_old_c(const skl_b200_gemm_args *g) {
   if (g->epilogue == SKL_EPI_INT) return g->beta_i != 0;
   if (g->epilogue == SKL_EPI_F64) return g->beta_d != 0.0;
+  if (g->epilogue == SKL_EPI_F16ACC) return g->beta_f != 0.0f;
   return g->beta_f != 0.0f || g->activation == SKL_ACT_SWIGLU;
 }
 
 static int dispatch_launch(const skl_b200_gemm_args *gin) {
   skl_b200_gemm_args local = *gin, *g = &local;
+  local.wait_limit_ms = g_ctx.wait_limit_ms;
+  local.debug_skip_loads = g_ctx.debug_skip_loads;
   const uint64_t M = g->m0 * g->m1, N = g->n0 * g->n1, K = g->k0 * g->k1;
   int path = SKL_B200_PATH_GENERIC;
   const int gemv_ok = K != 0 && skl_b200_gemv_i8_supported(g);
@@ -603,6 +667,8 @@ typedef struct {
 static int unblock_operands(skl_b200_gemm_args *g, unblock_t *u) {
   memset(u, 0, sizeof *u);
   if (g->m1 == 1 && g->n1 == 1 && g->k1 == 1) return 1;
+  /* panels the tensor-core kernel reads in place (the matrix-engine packed layout with 128-byte rows) */
+  if (g_ctx.force_path != SKL_B200_PATH_GENERIC && g->k0 * g->k1 != 0 && skl_b200_gemm_tc_supported(g)) return 1;
   const uint64_t M = g->m0 * g->m1, N = g->n0 * g->n1, K = g->k0 * g->k1;
   double threshold = 16777216.0; /* 2^24 multiply-adds */
   {
@@ -613,6 +679,7 @@ static int unblock_operands(skl_b200_gemm_args *g, unblock_t *u) {
   if (g_ctx.force_path == SKL_B200_PATH_GENERIC) return 1;
   if (K > 65536 && g->ta == SKL_DT_I8) return 1; /* the tensor path's int8 limit */
   if (g->ta == SKL_DT_F32 || g->ta == SKL_DT_F64) return 1; /* no tensor-core kernel for these */
+  if (g->epilogue == SKL_EPI_F16ACC) return 1;               /* nor for an fp16 accumulator */
   const size_t ea = dt_size(g->ta), eb = dt_size(g->tb), ec = dt_size(g->tc);
   const size_t ldk_a = (size_t)((K * ea + 15) / 16 * 16) / ea, ldk_b = (size_t)((K * eb + 15) / 16 * 16) / eb;
   const size_t ldc = (size_t)((N * ec + 15) / 16 * 16) / ec;
@@ -651,12 +718,10 @@ static int reblock_result(const skl_b200_gemm_args *plain, const unblock_t *u) {
                                                    (size_t)q->rsc1, (size_t)q->csc1, 0, g_ctx.stream));
 }
 
-static void run_gemm(skl_b200_gemm_args *g) {
-  if (!begin_call()) return;
+static void run_gemm_body(skl_b200_gemm_args *g) {
   g_ctx.last_path = SKL_B200_PATH_NONE;
   const uint64_t M = g->m0 * g->m1, N = g->n0 * g->n1, K = g->k0 * g->k1;
   if (M == 0 || N == 0) {
-    end_call();
     return;
   }
   if (!g->c || (K != 0 && (!g->a || !g->b))) {
@@ -706,7 +771,6 @@ static void run_gemm(skl_b200_gemm_args *g) {
     if (host_gmax && g_ctx.status == SKL_B200_OK)
       cuda_ok(cudaMemcpyAsync(host_gmax, g->global_max, sizeof(float), cudaMemcpyDeviceToHost, (cudaStream_t)g_ctx.stream));
     finish(host_any);
-    end_call();
     return;
   }
 
@@ -751,7 +815,12 @@ static void run_gemm(skl_b200_gemm_args *g) {
       !cuda_ok(cudaMemcpyAsync(host_gmax, g->global_max, sizeof(float), cudaMemcpyDeviceToHost, (cudaStream_t)g_ctx.stream)))
     return;
   finish(host_any);
-  end_call();
+}
+
+static void run_gemm(skl_b200_gemm_args *g) {
+  if (!begin_call()) return;
+  run_gemm_body(g);
+  leave_call();
 }
 
 static void gemm_plain(int ta, int tb, int tc, int epi, size_t m, size_t n, size_t k, const void *a,
@@ -872,6 +941,30 @@ SKL_B200_DEF_GEMM_PACKED_F32(skl_gemm_f16rcprc_f16rcprc_f32rcprc_sm100a, skl_f16
 SKL_B200_DEF_GEMM_PACKED_F32(skl_gemm_f8e4m3rcprc_f8e4m3rcprc_f32rcprc_sm100a, uint8_t, SKL_DT_F8E4M3)
 SKL_B200_DEF_GEMM_PACKED_F32(skl_gemm_f8e5m2rcprc_f8e5m2rcprc_f32rcprc_sm100a, uint8_t, SKL_DT_F8E5M2)
 
+/* Operands packed for the matrix engine (src/gemm/gemm_i8c_i8_i32_xsfmm32a8i.h:62-100 and siblings): the general
+ * packed GEMM with m0 = n0 = TE, k0 = 1, (rsa0, csa0) = (1, 0), (rsb0, csb0) = (0, 1).  With TE = 128 the tensor-core
+ * kernel reads these panels directly (see skl_b200_gemm_tc_supported): no unblocking pass. */
+size_t skl_b200_te(void) { return SKL_B200_TE; }
+
+void skl_gemm_i8rcptex1c_i8rcp1xte_i32rcptexterc_sm100a(size_t m1, size_t n1, size_t k, int32_t alpha, const int8_t *a,
+                                                        size_t rsa1, size_t csa1, const int8_t *b, size_t rsb1,
+                                                        size_t csb1, int32_t beta, int32_t *c, size_t rsc0, size_t csc0,
+                                                        size_t rsc1, size_t csc1) {
+  gemm_packed(SKL_DT_I8, SKL_DT_I32, SKL_EPI_INT, SKL_B200_TE, SKL_B200_TE, 1, m1, n1, k, a, 1, 0, rsa1, csa1, b, 0, 1,
+              rsb1, csb1, c, rsc0, csc0, rsc1, csc1, alpha, beta, 0.0f, 0.0f);
+}
+#define SKL_B200_DEF_GEMM_TE_F32(NAME, TYPE, DT)                                                                  \
+  void NAME(size_t m1, size_t n1, size_t k, float alpha, const TYPE *a, size_t rsa1, size_t csa1, const TYPE *b,   \
+            size_t rsb1, size_t csb1, float beta, float *c, size_t rsc0, size_t csc0, size_t rsc1, size_t csc1) {  \
+    gemm_packed(DT, SKL_DT_F32, SKL_EPI_FLOAT, SKL_B200_TE, SKL_B200_TE, 1, m1, n1, k, a, 1, 0, rsa1, csa1, b, 0, 1, \
+                rsb1, csb1, c, rsc0, csc0, rsc1, csc1, 0, 0, alpha, beta);                                         \
+  }
+SKL_B200_DEF_GEMM_TE_F32(skl_gemm_bf16rcptex1c_bf16rcp1xte_f32rcptexterc_sm100a, skl_bf16_t, SKL_DT_BF16)
+SKL_B200_DEF_GEMM_TE_F32(skl_gemm_f16rcptex1c_f16rcp1xte_f32rcptexterc_sm100a, skl_f16_t, SKL_DT_F16)
+SKL_B200_DEF_GEMM_TE_F32(skl_gemm_f8e4m3rcptex1c_f8e4m3rcp1xte_f32rcptexterc_sm100a, uint8_t, SKL_DT_F8E4M3)
+SKL_B200_DEF_GEMM_TE_F32(skl_gemm_f8e5m2rcptex1c_f8e5m2rcp1xte_f32rcptexterc_sm100a, uint8_t, SKL_DT_F8E5M2)
+SKL_B200_DEF_GEMM_TE_F32(skl_gemm_f32rcptex1c_f32rcp1xte_f32rcptexterc_sm100a, float, SKL_DT_F32)
+
 /* src/gemm/gemm_i8rcp1x4_i8p4x1c_i32_xsfvqdotq.h:43-52: the general packed GEMM with m0 = n0 = 1, k0 = 4 */
 void skl_gemm_i8rcp1x4_i8p4x1c_i32_sm100a(size_t m, size_t n, size_t k1, int32_t alpha, const int8_t *a, size_t rsa1,
                                           size_t csa1, const int8_t *b, size_t rsb1, int32_t beta, int32_t *c,
@@ -919,6 +1012,43 @@ void skl_gemm_f64rc_f64rc_f64rc_sm100a(size_t m, size_t n, size_t k, double alph
                                        size_t rsc, size_t csc) {
   skl_gemm_f64rcprc_f64rcprc_f64rcprc_sm100a(m, n, k, 1, 1, 1, alpha, a, rsa, csa, 0, 0, b, rsb, csb, 0, 0, beta, c, rsc,
                                              csc, 0, 0);
+}
+
+/* fp16 operands with an fp16 accumulator and fp16 C (ref/gemm/gemm_f16rc_f16rc_f16rc.c:9-22 and
+ * gemm_f16rcprc_f16rcprc_f16rcprc.c): on the any-stride kernel, every statement of the reference evaluated in fp32
+ * and rounded to fp16 once.  The *_f32scalars forms take alpha and beta as floats (rounded to fp16 first) for
+ * callers whose language binding cannot pass a 16-bit float by value. */
+static float as_f16_value(float x) { return (float)(skl_f16_t)x; }
+
+void skl_gemm_f16rcprc_f16rcprc_f16rcprc_f32scalars_sm100a(size_t m0, size_t n0, size_t k0, size_t m1, size_t n1,
+                                                           size_t k1, float alpha, const skl_f16_t *a, size_t rsa0,
+                                                           size_t csa0, size_t rsa1, size_t csa1, const skl_f16_t *b,
+                                                           size_t rsb0, size_t csb0, size_t rsb1, size_t csb1,
+                                                           float beta, skl_f16_t *c, size_t rsc0, size_t csc0,
+                                                           size_t rsc1, size_t csc1) {
+  gemm_packed(SKL_DT_F16, SKL_DT_F16, SKL_EPI_F16ACC, m0, n0, k0, m1, n1, k1, a, rsa0, csa0, rsa1, csa1, b, rsb0, csb0,
+              rsb1, csb1, c, rsc0, csc0, rsc1, csc1, 0, 0, as_f16_value(alpha), as_f16_value(beta));
+}
+void skl_gemm_f16rcprc_f16rcprc_f16rcprc_sm100a(size_t m0, size_t n0, size_t k0, size_t m1, size_t n1, size_t k1,
+                                                skl_f16_t alpha, const skl_f16_t *a, size_t rsa0, size_t csa0,
+                                                size_t rsa1, size_t csa1, const skl_f16_t *b, size_t rsb0, size_t csb0,
+                                                size_t rsb1, size_t csb1, skl_f16_t beta, skl_f16_t *c, size_t rsc0,
+                                                size_t csc0, size_t rsc1, size_t csc1) {
+  skl_gemm_f16rcprc_f16rcprc_f16rcprc_f32scalars_sm100a(m0, n0, k0, m1, n1, k1, (float)alpha, a, rsa0, csa0, rsa1, csa1,
+                                                        b, rsb0, csb0, rsb1, csb1, (float)beta, c, rsc0, csc0, rsc1,
+                                                        csc1);
+}
+void skl_gemm_f16rc_f16rc_f16rc_f32scalars_sm100a(size_t m, size_t n, size_t k, float alpha, const skl_f16_t *a,
+                                                  size_t rsa, size_t csa, const skl_f16_t *b, size_t rsb, size_t csb,
+                                                  float beta, skl_f16_t *c, size_t rsc, size_t csc) {
+  skl_gemm_f16rcprc_f16rcprc_f16rcprc_f32scalars_sm100a(m, n, k, 1, 1, 1, alpha, a, rsa, csa, 0, 0, b, rsb, csb, 0, 0,
+                                                        beta, c, rsc, csc, 0, 0);
+}
+void skl_gemm_f16rc_f16rc_f16rc_sm100a(size_t m, size_t n, size_t k, skl_f16_t alpha, const skl_f16_t *a, size_t rsa,
+                                       size_t csa, const skl_f16_t *b, size_t rsb, size_t csb, skl_f16_t beta,
+                                       skl_f16_t *c, size_t rsc, size_t csc) {
+  skl_gemm_f16rc_f16rc_f16rc_f32scalars_sm100a(m, n, k, (float)alpha, a, rsa, csa, b, rsb, csb, (float)beta, c, rsc,
+                                               csc);
 }
 
 /* extended epilogue */
@@ -970,9 +1100,8 @@ void skl_gemm_ex_sm100a(size_t m, size_t n, size_t k, skl_b200_dtype_t ta, const
 
 /* ------------------------------------------------------------------ cvt */
 
-static void run_cvt_to_f8(void *dst, const void *src, int src_type, int fmt, int sat, float scale, size_t n) {
-  if (!begin_call()) return;
-  if (n == 0) { end_call(); return; }
+static void run_cvt_to_f8_body(void *dst, const void *src, int src_type, int fmt, int sat, float scale, size_t n) {
+  if (n == 0) return;
   if (!dst || !src) { set_err(SKL_B200_ERR_INVALID_ARGUMENT); return; }
   int host_any = 0;
   const void *dsrc = src;
@@ -994,7 +1123,12 @@ static void run_cvt_to_f8(void *dst, const void *src, int src_type, int fmt, int
       !cuda_ok(cudaMemcpyAsync(dst, ddst, n, cudaMemcpyDeviceToHost, (cudaStream_t)g_ctx.stream)))
     return;
   finish(host_any);
-  end_call();
+}
+
+static void run_cvt_to_f8(void *dst, const void *src, int src_type, int fmt, int sat, float scale, size_t n) {
+  if (!begin_call()) return;
+  run_cvt_to_f8_body(dst, src, src_type, fmt, sat, scale, n);
+  leave_call();
 }
 
 #define SKL_B200_DEF_CVT_TO_F8(NAME, SRC_T, SRC_DT, FMT, SAT)                           \
@@ -1011,9 +1145,8 @@ SKL_B200_DEF_CVT_TO_F8(skl_cvt_bf16_f8e5m2_sm100a, skl_bf16_t, SKL_DT_BF16, SKL_
 SKL_B200_DEF_CVT_TO_F8(skl_cvt_sat_bf16_f8e5m2_sm100a, skl_bf16_t, SKL_DT_BF16, SKL_DT_F8E5M2, 1)
 
 /* widening directions: mode 0 = fp8 -> bf16 (out 2 bytes/elt, in 1), mode 1 = fp4 -> fp8 (out 1, in 1/2) */
-static void run_cvt_widen(void *dst, const void *src, int mode, int fmt, size_t n) {
-  if (!begin_call()) return;
-  if (n == 0) { end_call(); return; }
+static void run_cvt_widen_body(void *dst, const void *src, int mode, int fmt, size_t n) {
+  if (n == 0) return;
   if (!dst || !src) { set_err(SKL_B200_ERR_INVALID_ARGUMENT); return; }
   const size_t in_bytes = mode == 0 ? n : (n + 1) / 2, out_bytes = mode == 0 ? 2 * n : n;
   int host_any = 0;
@@ -1037,7 +1170,12 @@ static void run_cvt_widen(void *dst, const void *src, int mode, int fmt, size_t 
       !cuda_ok(cudaMemcpyAsync(dst, ddst, out_bytes, cudaMemcpyDeviceToHost, (cudaStream_t)g_ctx.stream)))
     return;
   finish(host_any);
-  end_call();
+}
+
+static void run_cvt_widen(void *dst, const void *src, int mode, int fmt, size_t n) {
+  if (!begin_call()) return;
+  run_cvt_widen_body(dst, src, mode, fmt, n);
+  leave_call();
 }
 
 void skl_cvt_f8e4m3_bf16_sm100a(skl_bf16_t *pDst, const uint8_t *pSrc, size_t n) {
@@ -1053,12 +1191,11 @@ void skl_cvt_f4e2m1_f8e4m3_sm100a(uint8_t *pDst, const uint8_t *pSrc, size_t n) 
 /* ------------------------------------------------------------------ pack / unpack / transpose */
 
 /* op: 0 pack, 1 unpack, 2 transpose.  `plain` is the 2-D side, `blk` the blocked side. */
-static void run_relayout(int op, size_t esize, size_t m, size_t n, const void *src, void *dst, size_t rs,
+static void run_relayout_body(int op, size_t esize, size_t m, size_t n, const void *src, void *dst, size_t rs,
                          size_t cs, size_t m0, size_t n0, size_t rs0, size_t cs0, size_t rs1, size_t cs1,
                          uint32_t pad) {
-  if (!begin_call()) return;
-  if (op != 2 && (m0 == 0 || n0 == 0)) { end_call(); return; } /* ref/pack/unpack_e8rcprc_e8rc.c:16-18 */
-  if (m == 0 || n == 0) { end_call(); return; }
+  if (op != 2 && (m0 == 0 || n0 == 0)) return; /* ref/pack/unpack_e8rcprc_e8rc.c:16-18 */
+  if (m == 0 || n == 0) return;
   if (!src || !dst) { set_err(SKL_B200_ERR_INVALID_ARGUMENT); return; }
   size_t src_span, dst_span;
   if (op == 0) {
@@ -1099,7 +1236,14 @@ static void run_relayout(int op, size_t esize, size_t m, size_t n, const void *s
   if (!cuda_ok((cudaError_t)rc)) return;
   if (dst_host && !stage_out_end(&out)) return;
   finish(host_any);
-  end_call();
+}
+
+static void run_relayout(int op, size_t esize, size_t m, size_t n, const void *src, void *dst, size_t rs,
+                         size_t cs, size_t m0, size_t n0, size_t rs0, size_t cs0, size_t rs1, size_t cs1,
+                         uint32_t pad) {
+  if (!begin_call()) return;
+  run_relayout_body(op, esize, m, n, src, dst, rs, cs, m0, n0, rs0, cs0, rs1, cs1, pad);
+  leave_call();
 }
 
 #define SKL_B200_DEF_PACK(BITS, TYPE)                                                                  \
@@ -1116,6 +1260,47 @@ static void run_relayout(int op, size_t esize, size_t m, size_t n, const void *s
 SKL_B200_DEF_PACK(8, uint8_t)
 SKL_B200_DEF_PACK(16, uint16_t)
 SKL_B200_DEF_PACK(32, uint32_t)
+
+/* Gathered column shards -> row-major matrix (see the header).  Equal shards: the buffer is a packed matrix of
+ * 1 x parts blocks of m x n/parts, unpacked in one launch; otherwise each shard is a 1 x 1 "packed" matrix. */
+void skl_b200_unshard_columns_sm100a(size_t esize, size_t m, size_t n, size_t parts, size_t align,
+                                     const void *gathered, size_t part_stride, void *dst, size_t rsd) {
+  if ((esize != 1 && esize != 2 && esize != 4) || parts == 0 || rsd < n) {
+    g_ctx.status = SKL_B200_ERR_INVALID_ARGUMENT;
+    g_ctx.cuda_err[0] = 0;
+    return;
+  }
+  size_t start0 = 0, count0 = 0;
+  int equal = 1;
+  skl_b200_shard_columns(n, parts, 0, align, &start0, &count0);
+  for (size_t g = 1; g < parts && equal; ++g) {
+    size_t s_g = 0, c_g = 0;
+    skl_b200_shard_columns(n, parts, g, align, &s_g, &c_g);
+    if (c_g != count0 || s_g != g * count0) equal = 0;
+  }
+  if (equal) {
+    run_relayout(1, esize, m, n, gathered, dst, rsd, 1, m, count0, count0, 1, 0, part_stride, 0);
+    return;
+  }
+  for (size_t g = 0; g < parts; ++g) {
+    size_t s_g = 0, c_g = 0;
+    skl_b200_shard_columns(n, parts, g, align, &s_g, &c_g);
+    if (c_g == 0) continue;
+    run_relayout(1, esize, m, c_g, (const uint8_t *)gathered + g * part_stride * esize, (uint8_t *)dst + s_g * esize, rsd,
+                 1, m, c_g, c_g, 1, 0, 0, 0);
+    if (g_ctx.status != SKL_B200_OK) return;
+  }
+}
+
+/* src/pack/pack_e16_xsfmmbase.h:20-51: the general pack with (m0, n0) = (TE, 1), (rs0, cs0) = (1, 0), row-major src */
+#define SKL_B200_DEF_PACK_TE(BITS, TYPE)                                                                       \
+  void skl_pack_e##BITS##_e##BITS##rcptex1c_sm100a(size_t m, size_t n, const TYPE *src, size_t rs, TYPE *dst,  \
+                                                   size_t rs1, size_t cs1, TYPE pad) {                         \
+    run_relayout(0, sizeof(TYPE), m, n, src, dst, rs, 1, SKL_B200_TE, 1, 1, 0, rs1, cs1, (uint32_t)pad);       \
+  }
+SKL_B200_DEF_PACK_TE(8, uint8_t)
+SKL_B200_DEF_PACK_TE(16, uint16_t)
+SKL_B200_DEF_PACK_TE(32, uint32_t)
 
 void skl_unpack_e8rcprc_e8rc_sm100a(size_t m0, size_t n0, const uint8_t *SKL_RESTRICT src, size_t rs0,
                                     size_t cs0, size_t rs1, size_t cs1, size_t m, size_t n,

@@ -74,6 +74,33 @@ def test_int8_bias_and_global_max_are_exact(skl, m, n, k, expect, beta, where):
     assert np.array_equal(got.view(np.uint32), want.view(np.uint32)) and gg == gw
 
 
+@pytest.mark.parametrize("m,n,k,expect", [(1, 600, 512, S.PATH_GEMV), (200, 300, 256, S.PATH_TCGEN05),
+                                          (33, 17, 48, S.PATH_GENERIC)])
+def test_global_max_of_results_that_are_all_zero_or_negative(skl, m, n, k, expect):
+    """Non-negative operands and a negative alpha: every result is negative or -0.0 (rows of A that are all zero).
+    The maximum must come out as a zero, as the sequential definition gives -- a float atomic maximum that files
+    -0.0 with the non-negative bit patterns would leave the initial -inf in place."""
+    import torch
+
+    g = H.rng(m + n)
+    a = g.integers(0, 100, size=(m, k), dtype=np.int8)
+    a[0, :] = 0  # a whole row of exact zeros -> -0.0 after the negative alpha
+    b = g.integers(1, 100, size=(n, k), dtype=np.int8)  # [N][K]
+    da, db = torch.from_numpy(a).cuda(), torch.from_numpy(b).cuda()
+    dc = torch.zeros((m, n), dtype=torch.float32, device="cuda")
+    dg = torch.full((1,), -np.inf, dtype=torch.float32, device="cuda")
+    f = S.Fused(-0.5, 0.0, None, None, None, dg.data_ptr(), 0, 0.0)
+    skl.skl_gemm_fused_sm100a(m, n, k, S.I8, da.data_ptr(), k, 1, S.I8, db.data_ptr(), 1, k, C.byref(f), S.F32,
+                              dc.data_ptr(), n, 1)
+    S.check()
+    assert skl.skl_b200_last_path() == expect
+    out = dc.cpu().numpy()
+    assert np.all(out <= 0.0) and np.all(out[0] == 0.0) and np.all(np.signbit(out[0]))
+    assert float(dg.cpu()[0]) == 0.0
+    if m > 1:
+        assert np.all(out[1:] < 0.0)
+
+
 @pytest.mark.parametrize("pair", [(H.BF16, H.BF16), (H.F8E4M3, H.F8E5M2), (H.BF16, H.F8E4M3)])
 @pytest.mark.parametrize("tc", [H.F32, H.BF16])
 def test_float_pairs_with_bias_and_global_max(skl, pair, tc):

@@ -82,6 +82,43 @@ def test_host_threads_have_their_own_context(skl):
     assert not errors, errors
 
 
+def test_thread_exit_releases_the_threads_workspaces(skl):
+    """A thread that used the library with host operands owns device workspaces; when it ends without calling
+    skl_b200_release_workspace() the library's thread-exit hook frees them: free device memory after the threads have
+    gone is back where it was (short-lived worker threads must not leak device memory)."""
+    import torch
+
+    torch.cuda.synchronize()
+    m, n, k = 2048, 2048, 2048  # 4 MiB A + 4 MiB B + 16 MiB C staged per thread
+    a = np.ones((m, k), np.int8)
+    b = np.ones((k, n), np.int8)
+    errors = []
+
+    def work():
+        c = np.zeros((m, n), np.int32)
+        skl.skl_gemm_i8_i8_i32_sm100a(m, n, k, 1, S.ptr(a), k, S.ptr(b), n, 0, S.ptr(c), n)
+        if skl.skl_b200_last_status() != 0 or c[5, 7] != k:
+            errors.append("bad result")
+
+    # one throw-away thread first so that one-time costs (module load, streams) are not counted
+    t = threading.Thread(target=work)
+    t.start()
+    t.join()
+    torch.cuda.synchronize()
+    free0, _ = torch.cuda.mem_get_info()
+    for _ in range(3):
+        ts = [threading.Thread(target=work) for _ in range(4)]
+        for t in ts:
+            t.start()
+        for t in ts:
+            t.join()
+    torch.cuda.synchronize()
+    free1, _ = torch.cuda.mem_get_info()
+    assert not errors, errors
+    # 12 threads x 24 MiB would be 288 MiB if nothing were released
+    assert free0 - free1 < (32 << 20), f"device memory not returned: {(free0 - free1) >> 20} MiB still held"
+
+
 def test_async_mode_on_a_caller_stream(skl):
     """With device operands, async mode and a caller's stream, the call only enqueues: work the caller puts
     on the same stream before and after it is ordered with the library's kernels."""

@@ -187,3 +187,50 @@ def test_int8_wrap_around_equals_reference():
     ref.skl_gemm_i8rc_i8rc_i32rc_ref(m, n, k, alpha, P(a), k, 1, P(b), n, 1, beta, P(c0), n, 1)
     port.orc_gemm_i8_i32(m, n, k, alpha, P(a), k, 1, P(b), n, 1, beta, P(c1), n, 1)
     assert np.array_equal(c0, c1)
+
+
+@pytest.mark.parametrize("shape", [(1, 1, 1), (7, 9, 33), (17, 5, 300), (4, 5, 0), (33, 20, 64)])
+def test_f16_accumulate_gemm_port_equals_compiled_reference(shape):
+    """ref/gemm/gemm_f16rc_f16rc_f16rc.c / gemm_f16rcprc_f16rcprc_f16rcprc.c: the port states each `_Float16` statement
+    as one fp32 evaluation rounded to fp16; the reference compiled by this toolchain must agree bit for bit (plain
+    and blocked operands)."""
+    ref, port = orc.ref(), orc.port()
+    if not hasattr(ref, "orc_ref_gemm_f16acc"):
+        pytest.skip("reference library built without the fp16-scalar shim")
+    m, n, k = shape
+    g = H.rng(m * 100 + n * 10 + k)
+    for blocked in (False, True):
+        if blocked:
+            m0, n0, k0, m1, n1, k1 = 2, 3, 2, m, n, (k + 1) // 2
+            sa = (k0, 1, max(k1, 1) * m0 * k0, m0 * k0)
+            sb = (1, k0, n1 * k0 * n0, k0 * n0)
+            sc = (1, m0, m0 * n0, m1 * m0 * n0)
+            na, nb, ncc = m1 * max(k1, 1) * m0 * k0, max(k1, 1) * n1 * k0 * n0, m1 * n1 * m0 * n0
+        else:
+            m0, n0, k0, m1, n1, k1 = m, n, k, 1, 1, 1
+            sa, sb, sc = (max(k, 1), 1, 0, 0), (n, 1, 0, 0), (n, 1, 0, 0)
+            na, nb, ncc = m * max(k, 1), max(k, 1) * n, m * n
+        a = H.f32_to_f16_bits(g.uniform(-2, 2, na).astype(np.float32))
+        b = H.f32_to_f16_bits(g.uniform(-2, 2, nb).astype(np.float32))
+        c0 = H.f32_to_f16_bits(g.uniform(-8, 8, ncc).astype(np.float32))
+        for alpha, beta in ((1.0, 0.0), (1.25, -0.75)):
+            want, got = c0.copy(), c0.copy()
+            ref.orc_ref_gemm_f16acc(m0, n0, k0, m1, n1, k1, alpha, P(a), *sa, P(b), *sb, beta, P(want), *sc)
+            port.orc_gemm_f16acc(m0, n0, k0, m1, n1, k1, alpha, P(a), *sa, P(b), *sb, beta, P(got), *sc)
+            assert np.array_equal(want, got)
+
+
+def test_fp8_encoders_against_the_reference_on_a_sample_of_all_inputs():
+    """`make -C oracle check-cvt CVT_STRIDE=n`: the port's encoders and decoders against the compiled reference on every
+    n-th fp32 bit pattern (offsets rotating through all residues), both formats, both overflow flavours.  The full
+    sweep (CVT_STRIDE=1, all 2^32 patterns, about half a minute) runs when SKL_B200_FULL_CVT_CHECK=1."""
+    import os
+    import subprocess
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    stride = "1" if os.environ.get("SKL_B200_FULL_CVT_CHECK") == "1" else "257"
+    out = subprocess.run(["make", "-C", os.path.join(root, "oracle"), "check-cvt", f"CVT_STRIDE={stride}"],
+                         capture_output=True, text=True)
+    assert out.returncode == 0, out.stdout + out.stderr
+    assert "decode mismatches: 0" in out.stdout
+    assert "flavours: 0" in out.stdout
