@@ -4,7 +4,8 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--no-also]
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
 
-Headline workload ("c5", BASELINE configs[4]): the LLM MLP projection
+Headline workload ("c5", the largest configured single-GPU workload and the one defined at 1/2/4/8 GPUs): the
+LLM MLP projection
     C[16384, 14336] (bf16) = X[16384, 4096] (bf16) . W[4096, 14336] (fp8 E4M3, per-column fp32 scale)
 with W and C partitioned by columns over the N ranks (X replicated, no data-path collective, outputs
 left sharded).  One step = one call of skl_gemm_ex_sm100a per rank: the exact fp8->bf16 widening of the
@@ -15,7 +16,7 @@ copies of X, W, scales and the device->host copy of C are inside the timed regio
 fixed as N grows ("strong" scaling).  Inputs are seeded synthetic tensors of the configured
 shapes and distributions; every operand set is larger than the 126 MB L2.
 
-At N = 1 the line also carries, under "also", short measurements of the other BASELINE configs
+At N = 1 the line also carries, under "also", short measurements of the other configured workloads
 (int8 8192^3, bf16/fp16 4096^3, fp8 8192^3, the decode GEMV at M = 1/4/16) and a `cpu_baseline`:
 the reference's scalar routines (oracle/_ref when built, else the oracle port) timed on the host cores
 on a bounded row sample of the same workload.
@@ -508,7 +509,7 @@ def run_workload(torch, S, lib, peaks, build, warmup=3, reps=None):
 
 
 def also_configs(torch, S, lib, peaks):
-    """Short device-resident measurements of the other BASELINE configs and companions (1 GPU)."""
+    """Short device-resident measurements of the other configured workloads and companions (1 GPU)."""
     out = {}
     for name, build in make_workloads(torch, S, lib).items():
         if "_n" in name.rsplit("_m", 1)[-1]:
@@ -749,8 +750,8 @@ def main() -> None:
     roofline = {"bound": "tensor", "kernel": "gemm_tc_kernel<256, f16> (bf16 x bf16 -> fp32 in TMEM -> bf16)",
                 "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": (achieved / peak if achieved else None),
                 "peak_kind": f"{peak_kind}, of {peaks['source']}", "kernel_ms": kern_ms,
-                # dram__bytes_read + dram__bytes_write of one launch at the 1-GPU shape, from the ncu capture
-                # summarised in profiles/gemm_tc_kernel_bf16_c5.md (algorithmic: 0.70e9); not captured per shard
+                # dram__bytes_read + dram__bytes_write of one launch at the 1-GPU shape, from a profiler capture of
+                # this kernel on this workload (algorithmic: 0.70e9); not captured per shard
                 "traffic": (C5_DRAM_BYTES_PER_LAUNCH_1GPU if world == 1 else None)}
 
     line = {

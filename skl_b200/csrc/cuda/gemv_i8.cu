@@ -6,28 +6,30 @@
 // the kernel is a weight-streaming kernel bounded by HBM bandwidth.  SKL's counterpart is the m == 1
 // branch of its int8 kernel (src/gemm/gemm_i8rcp1x4_i8p4x1c_i32_xsfvqdotq.c:543-632, dispatch :645-658).
 //
-// Design.  A plain 16-byte-per-thread read of the weight matrix with 128 KiB of loads in flight per SM runs
-// at 0.96 of the device's copy bandwidth at this size; staging the rows through shared memory with bulk
-// copies measured 20-50 % slower.  So the kernel IS that read, with the arithmetic hung on it:
-//   * One CTA of 16 warps per SM; every thread keeps 16 independent 16-byte loads (ld.global.nc, no L1
-//     allocation) in flight in registers.
-//   * The weight rows are dealt to the CTAs in layers: layer l is a run of consecutive rows cut into one
-//     piece per CTA, so at any moment all CTAs read neighbouring rows and every CTA gets the same number
-//     of bytes to within one row.  A piece is up to 8 rows (more when k is short).
-//   * Inside a CTA the k range is split over the warps in 128-byte blocks, so the warps are balanced
-//     whatever the row count.  One warp-wide load fetches 64 bytes of each of 8 rows: lane (g, t) holds
-//     bytes [16t, 16t+16) of row g -- the operand layout of mma.m16n8k32 with the 8 weight rows as its
-//     8-column operand (the k order inside a fragment is a fixed permutation applied to both operands).
-//       m <= 2   dp4a on that chunk against the same chunk of the activations, two shuffles fold the
-//                four lanes of a row.  No tensor cores.
-//       m >= 3   mma.sync.m16n8k32.s8 with the activations as the 16-row operand: dp4a cannot keep up
-//                with HBM here (4*m dp4a per 16 weight bytes on a two-per-clock pipe).
-//     The activations sit in shared memory, rows 64 bytes off the 128-byte grid so that the fragment loads
-//     of neighbouring rows hit different banks.
-//   * A warp's partial sums go to its own slice of shared memory without any synchronisation; after the
-//     CTA's last piece (or every `round` pieces when there are many) one barrier, then one thread per
-//     output adds the partial sums and runs the fused alpha/beta or dequantising epilogue.  int32 sums wrap
-//     around like the reference's, in any order, so the result is exact.
+// Design.  A plain 16-byte-per-thread read of the weight matrix, 1024 threads per SM with 8 loads each in flight
+// (128 KiB per SM), runs at 0.96 of the device's copy bandwidth at this size; staging the rows through shared memory
+// with bulk copies measured 20-50 % slower, and so did fewer threads with more loads each or warp-wide loads that
+// gather 64-byte pieces of 8 rows.  So the kernel IS that read, with the arithmetic hung on it:
+//   * One CTA of 32 warps per SM.  A warp owns 512 bytes of k (KS = k / 512 warps share a group of 8 rows; the other
+//     warps of the CTA take further groups), and one warp-wide load is 512 contiguous bytes of one row: a step of the
+//     CTA reads up to 32 consecutive rows of 4 KiB, every thread holding 8 independent 16-byte loads
+//     (ld.global.nc, no L1 allocation).
+//   * The weight rows are dealt to the CTAs in layers: layer l is a run of consecutive rows cut into one piece per
+//     CTA, so at any moment all CTAs read neighbouring rows and every CTA gets the same number of bytes to within
+//     one row.  (Measured against per-CTA contiguous ranges and a grid-stride over 8-row units: 9.9 vs 10.6 / 10.3 us.)
+//       m <= 2   dp4a straight from the load registers against the same chunk of the activations, a butterfly
+//                warp-shuffle fold of the 8 rows' partial sums.  No tensor cores.
+//       m >= 3   mma.sync.m16n8k32.s8: dp4a cannot keep up with HBM here (4*m dp4a per 16 weight bytes on a
+//                two-per-clock pipe).  The warp parks its 8 x 512 bytes in a private shared-memory tile (rows 64
+//                bytes off the 128-byte grid, so fragment loads of neighbouring rows hit different banks) and reads
+//                them back in the operand layout of the instruction, the 8 weight rows as its 8-column operand, the
+//                activations (16 rows, zero padded) as the other; the k order inside a fragment is a fixed permutation
+//                applied to both operands.
+//     The activations sit in shared memory, rows 64 bytes off the 128-byte grid for the same reason.
+//   * The KS partial sums of an output meet in shared memory through integer atomic adds (int32 sums wrap around
+//     like the reference's, in any order, so the result is exact); after the CTA's last piece (or every `round`
+//     pieces when there are many) one barrier, then one thread per output runs the fused alpha/beta or dequantising
+//     epilogue.
 // The kernel has no waits on barriers that another agent completes, hence nothing that could time out.
 //
 // Launch overlap.  The kernel lets its successor on the stream start early (griddepcontrol) and is itself
@@ -41,12 +43,12 @@
 namespace sklb {
 namespace {
 
-constexpr int GV_WARPS = 16;
+constexpr int GV_WARPS = 32;
 constexpr int GV_THREADS = GV_WARPS * 32;
-constexpr int GV_G = 8;            // weight rows per warp-wide load (the 8-column operand of one mma)
-constexpr int GV_INFLIGHT = 16;    // 16-byte loads a thread keeps in flight
-constexpr int GV_OUT_PER_THREAD = 4;  // outputs one thread finishes per round, at most
-constexpr int GV_MATH_DP4A = 0, GV_MATH_MMA = 1;
+constexpr int GV_G = 8;               // weight rows per warp and step (the 8-column operand of one mma)
+constexpr int GV_KW = 512;            // bytes of k per warp
+constexpr int GV_KSEG = 8 * GV_KW;    // most bytes of k per step
+constexpr int GV_TILE_PITCH = GV_KW + 64;  // warp-private tile of the mma variant: 8 rows of 512 bytes, 64 mod 128 apart
 
 struct GemvParams {
   const int8_t *x;  // activations, row i at x + i*ldx
@@ -54,7 +56,8 @@ struct GemvParams {
   void *c;
   int64_t ldx, ldw, rsc, csc;
   int m, n, k;
-  int ksplit_log2;    // warps sharing one group of 8 rows: KS = 1 << ksplit_log2 (they split k in 128-byte blocks)
+  int ksplit_log2;    // warps sharing one group of 8 rows: KS = 1 << ksplit_log2, each takes 512 bytes of a k segment
+  int nseg;           // k segments of KS * 512 bytes
   int piece_rows;     // rows of one piece = 8 * (GV_WARPS / KS)
   int xpitch;         // bytes between activation rows in shared memory (64 mod 128)
   int layers;         // pieces per CTA
@@ -74,17 +77,13 @@ struct GemvParams {
 
 __device__ __forceinline__ uint32_t gv_smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
-__device__ __forceinline__ uint4 gv_ldg(const void *p) {
-  uint4 v;
-  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
-               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-               : "l"(p));
-  return v;
-}
 __device__ __forceinline__ uint4 gv_lds128(uint32_t addr) {
   uint4 v;
   asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
   return v;
+}
+__device__ __forceinline__ void gv_sts128(uint32_t addr, const uint4 &v) {
+  asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
 }
 // D (16 x 8, int32) += A (16 x 32, int8, row) * B (32 x 8, int8, col); sums wrap around.
 __device__ __forceinline__ void gv_mma(int32_t (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
@@ -93,6 +92,33 @@ __device__ __forceinline__ void gv_mma(int32_t (&d)[4], uint32_t a0, uint32_t a1
       "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
       : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// Folds V partial sums held by every lane across the warp.  Each halving step exchanges half of the
+// values a lane still holds, so the total is V-1+... shuffles instead of 5*V.  On return v[0..W)
+// (W = max(V/32, 1)) are complete sums; lane L holds value indices (L >> s) * W + w where
+// s = max(0, 5 - log2 V).
+template <int V>
+__device__ __forceinline__ void warp_fold(int32_t (&v)[V], int lane) {
+  int cur = V;
+#pragma unroll
+  for (int off = 16; off >= 1; off >>= 1) {
+    if (cur > 1) {
+      const int half = cur / 2;
+      const bool upper = (lane & off) != 0;
+#pragma unroll
+      for (int i = 0; i < (V > 1 ? V / 2 : 1); ++i) {
+        if (i < half) {
+          int32_t send = upper ? v[i] : v[i + half];
+          int32_t keep = upper ? v[i + half] : v[i];
+          v[i] = keep + __shfl_xor_sync(0xFFFFFFFFu, send, off);
+        }
+      }
+      cur = half;
+    } else {
+      v[0] += __shfl_xor_sync(0xFFFFFFFFu, v[0], off);
+    }
+  }
 }
 
 // rs / cs: the row and column scale of this element, fetched ahead of time (1.0f when absent; the
@@ -127,172 +153,283 @@ __device__ __forceinline__ void gv_piece(const GemvParams &p, int l, int b, int 
   nr = pq + (b < pr ? 1 : 0);
 }
 
-// MATH: GV_MATH_DP4A with MP in {1, 2} (activation rows, padded), or GV_MATH_MMA with MP in {8, 16}.
-// NBW: 128-byte k blocks per warp and group (1, 2, 4 or 8: k up to 2048 * NBW bytes at a 16-way split).
-template <int MATH, int MP, int NBW>
-__global__ void __launch_bounds__(GV_THREADS, 1) gemv_i8_kernel(const GemvParams p) {
-  constexpr int L = 2 * NBW;           // 16-byte loads per lane and piece: two 64-byte halves of every block
-  constexpr int U = GV_INFLIGHT / L;   // pieces in flight
-  constexpr int NOUT = GV_G * MP;      // outputs per group of 8 rows
+// 16-byte global load that bypasses L1 allocation.
+__device__ __forceinline__ uint4 gv_ldg(const void *p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+
+// Shared-memory carve-up common to both kernels: activations (mma kernel only) | sums | column scale and bias | tiles.
+struct GvSmem {
+  int32_t *red;    // sums [round * piece_rows][MP]
+  float2 *scl;     // (column scale, bias) of every row slot of the round
+  float *rowsc;    // 16 row scales (1.0 when absent), after scl
+  int red_ints;
+};
+
+// Start of a round: clears the sums and brings the round's column scales and biases into shared memory, so that their
+// latency hides behind the stream.  Row slot = piece of the round, then row of the piece.
+__device__ __forceinline__ void gv_round_begin(const GemvParams &p, const GvSmem &sm, int base, int count, int b, int tid) {
+  for (int e = tid; e < sm.red_ints; e += GV_THREADS) sm.red[e] = 0;
+  if (tid < 16) sm.rowsc[tid] = (p.row_scale && tid < p.m) ? __ldg(p.row_scale + tid) : 1.0f;
+  if (p.col_scale || p.bias) {
+    const int slots = count * p.piece_rows;
+    for (int slot = tid; slot < slots; slot += GV_THREADS) {
+      const int pc = slot / p.piece_rows, row = slot - pc * p.piece_rows;
+      int r0, nr;
+      gv_piece(p, base + pc, b, r0, nr);
+      float2 v = make_float2(1.0f, 0.0f);
+      if (row < nr) {
+        if (p.col_scale) v.x = __ldg(p.col_scale + r0 + row);
+        if (p.bias) v.y = __ldg(p.bias + r0 + row);
+      }
+      sm.scl[slot] = v;
+    }
+  }
+}
+
+// End of a round (after a barrier): one thread per output runs the epilogue.  Returns the largest value stored.
+template <int MP>
+__device__ __forceinline__ float gv_round_end(const GemvParams &p, const GvSmem &sm, int base, int count, int b, int tid) {
+  float mx = -INFINITY;
+  const int total = count * p.piece_rows * MP;
+  for (int o = tid; o < total; o += GV_THREADS) {
+    const int slot = o / MP, mi = o - slot * MP, pc = slot / p.piece_rows, row = slot - pc * p.piece_rows;
+    int r0, nr;
+    gv_piece(p, base + pc, b, r0, nr);
+    if (row < nr && mi < p.m) {
+      const float rsc = sm.rowsc[mi];
+      const float2 cb = (p.col_scale || p.bias) ? sm.scl[slot] : make_float2(1.0f, 0.0f);
+      mx = fmaxf(mx, gemv_store(p, mi, r0 + row, sm.red[o], rsc, cb.x, cb.y));
+    }
+  }
+  return mx;
+}
+
+// ---- m <= 2: dp4a straight from the load registers, the thread's chunk of the activations in registers as well.
+// The 8 loads of a step are two half batches of 4 rows that are consumed and re-requested separately, which keeps the
+// memory pipe fuller across step boundaries (measured: 10.25 vs 11.1 us with the arithmetic below on the configured size).
+template <int MP>
+__global__ void __launch_bounds__(GV_THREADS, 1) gemv_i8_dp4a_kernel(const GemvParams p) {
   extern __shared__ __align__(128) uint8_t gv_smem[];
-  // layout: activations [MP][xpitch] | partial sums [round][GV_WARPS][NOUT]
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int g = lane >> 2, t = lane & 3;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, b = (int)blockIdx.x;
   const int KS = 1 << p.ksplit_log2;
-  const int ks = warp & (KS - 1), rs = warp >> p.ksplit_log2;  // this warp's share of k and its group inside a piece
-  const uint32_t x_s = gv_smem_u32(gv_smem);
-  int32_t *red = reinterpret_cast<int32_t *>(gv_smem + (size_t)MP * p.xpitch);
-  const int b = (int)blockIdx.x;
+  const int ks = warp & (KS - 1), grp = warp >> p.ksplit_log2;  // this warp's share of k and its group inside a piece
+  GvSmem sm;
+  sm.red = reinterpret_cast<int32_t *>(gv_smem);
+  sm.red_ints = p.round * p.piece_rows * MP;
+  sm.scl = reinterpret_cast<float2 *>(sm.red + sm.red_ints);
+  sm.rowsc = reinterpret_cast<float *>(sm.scl + p.round * p.piece_rows);
+  const int kw0 = ks * GV_KW + lane * 16;  // this lane's byte of k inside a segment
+  const int seg_bytes = KS * GV_KW;
 
   // The next kernel on the stream may be scheduled from now on (it waits for this one where it must).
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-  if (!p.overlap) asm volatile("griddepcontrol.wait;" ::: "memory");
+  if (!p.overlap) {
+    // While the preceding kernel drains, ask the L2 for the lines of the first step: a prefetch changes no
+    // architectural state, so it is safe even if that kernel is still writing the weights (its writes go through
+    // the same L2), and the first loads after the wait then find their data on chip.
+    if (p.layers > 0 && (lane & 7) == 0 && kw0 < p.k) {
+      int r0, nr;
+      gv_piece(p, 0, b, r0, nr);
+      const int rows = nr - grp * GV_G;
+      const int8_t *src = p.w + (int64_t)(r0 + grp * GV_G) * p.ldw + kw0;
+      for (int u = 0; u < GV_G && u < rows; ++u) asm volatile("prefetch.global.L2 [%0];" ::"l"(src + (int64_t)u * p.ldw));
+    }
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+  }
 
-  uint4 wv[U][L];
-  // Requests the loads of piece `l` into one register set.  Lane (g, t) fetches, for every 128-byte block this warp
-  // owns, bytes [16t, 16t+16) of both 64-byte halves of row g of the warp's group; rows and k past the end read as 0.
-  auto issue = [&](uint4 (&dst)[L], int l) {
+  // Step = (piece l, k segment seg).  A half batch h (rows 4h .. 4h+3 of the warp's group) is requested for a step;
+  // rows past the end of the piece and k past the end of the row read as 0.
+  uint4 va[4], vb[4];
+  auto request = [&](uint4 (&dst)[4], int h, int l, int seg) {
     int r0, nr;
     gv_piece(p, l, b, r0, nr);
-    const int row = rs * GV_G + g;
-    const bool row_ok = row < nr;
-    const int8_t *src = p.w + (int64_t)(r0 + row) * p.ldw + t * 16;
+    const int koff = seg * seg_bytes + kw0;
+    const int first = grp * GV_G + 4 * h;
+    const int rows = koff < p.k ? nr - first : 0;
+    const int8_t *src = p.w + (int64_t)(r0 + first) * p.ldw + koff;
 #pragma unroll
-    for (int j = 0; j < NBW; ++j) {
-#pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        const int off = ((ks + (j << p.ksplit_log2)) << 7) + h * 64;
-        dst[2 * j + h] = (row_ok && off + t * 16 < p.k) ? gv_ldg(src + off) : make_uint4(0, 0, 0, 0);
-      }
-    }
+    for (int u = 0; u < 4; ++u) dst[u] = u < rows ? gv_ldg(src + (int64_t)u * p.ldw) : make_uint4(0, 0, 0, 0);
   };
-
-#pragma unroll
-  for (int u = 0; u < U; ++u)
-    if (u < p.layers) issue(wv[u], u);
+  const int steps = p.layers * p.nseg;
+  if (steps > 0) {
+    request(va, 0, 0, 0);
+    request(vb, 1, 0, 0);
+  }
   if (p.overlap) asm volatile("griddepcontrol.wait;" ::: "memory");
 
-  // Activations -> shared memory (rows past m are zero), while the first weights are on their way.
+  // this lane's 16 bytes of every activation row for the current k segment
+  uint4 xq[MP];
+  auto load_x = [&](int seg) {
+    const int koff = seg * seg_bytes + kw0;
+#pragma unroll
+    for (int mi = 0; mi < MP; ++mi)
+      xq[mi] = (mi < p.m && koff < p.k) ? *reinterpret_cast<const uint4 *>(p.x + (int64_t)mi * p.ldx + koff)
+                                        : make_uint4(0, 0, 0, 0);
+  };
+  load_x(0);
+
+  float my_max = -INFINITY;
+  int l_next = 0, seg_next = 0;  // the step after the one being consumed
+  auto advance = [&]() {
+    if (++seg_next == p.nseg) {
+      seg_next = 0;
+      ++l_next;
+    }
+  };
+  advance();
+  for (int base = 0; base < p.layers; base += p.round) {
+    const int count = (p.layers - base) < p.round ? (p.layers - base) : p.round;
+    gv_round_begin(p, sm, base, count, b, tid);
+    __syncthreads();
+    for (int l = 0; l < count; ++l) {
+      int32_t *sums = sm.red + (size_t)(l * p.piece_rows + grp * GV_G) * MP;  // this warp's 8 rows of the piece
+      for (int seg = 0; seg < p.nseg; ++seg) {
+        const bool more = l_next < p.layers;
+        int32_t acc[GV_G * MP];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+#pragma unroll
+          for (int mi = 0; mi < MP; ++mi) {
+            int32_t a = __dp4a((int)va[u].x, (int)xq[mi].x, 0);
+            a = __dp4a((int)va[u].y, (int)xq[mi].y, a);
+            a = __dp4a((int)va[u].z, (int)xq[mi].z, a);
+            acc[u * MP + mi] = __dp4a((int)va[u].w, (int)xq[mi].w, a);
+          }
+        }
+        if (more) request(va, 0, l_next, seg_next);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+#pragma unroll
+          for (int mi = 0; mi < MP; ++mi) {
+            int32_t a = __dp4a((int)vb[u].x, (int)xq[mi].x, 0);
+            a = __dp4a((int)vb[u].y, (int)xq[mi].y, a);
+            a = __dp4a((int)vb[u].z, (int)xq[mi].z, a);
+            acc[(4 + u) * MP + mi] = __dp4a((int)vb[u].w, (int)xq[mi].w, a);
+          }
+        }
+        if (more) request(vb, 1, l_next, seg_next);
+        if (p.nseg > 1 && more) load_x(seg_next);  // the activations of the next step's k segment
+        advance();
+        constexpr int V = GV_G * MP;
+        constexpr int share = V == 16 ? 1 : 2;  // 2^share lanes hold the same finished value
+        warp_fold<V>(acc, lane);
+        if ((lane & ((1 << share) - 1)) == 0) atomicAdd(sums + (lane >> share), acc[0]);  // index row*MP + mi
+      }
+    }
+    __syncthreads();
+    my_max = fmaxf(my_max, gv_round_end<MP>(p, sm, base, count, b, tid));
+    if (base + p.round < p.layers) __syncthreads();  // the sums are cleared for the next round
+  }
+  if (p.global_max) {
+    my_max = warp_max_f32(my_max);
+    if (lane == 0 && my_max != -INFINITY) atomic_max_f32(p.global_max, my_max);
+  }
+}
+
+// ---- m >= 3: mma.sync.m16n8k32.s8 on fragments read back from a warp-private shared-memory tile; MP = 8 or 16
+// activation rows (zero padded) in shared memory.
+template <int MP>
+__global__ void __launch_bounds__(GV_THREADS, 1) gemv_i8_mma_kernel(const GemvParams p) {
+  extern __shared__ __align__(128) uint8_t gv_smem[];
+  // layout: activations [MP][xpitch] | sums | column scale and bias | tiles [GV_WARPS][8][GV_TILE_PITCH]
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, b = (int)blockIdx.x;
+  const int KS = 1 << p.ksplit_log2;
+  const int ks = warp & (KS - 1), grp = warp >> p.ksplit_log2;
+  const uint32_t x_s = gv_smem_u32(gv_smem);
+  GvSmem sm;
+  sm.red = reinterpret_cast<int32_t *>(gv_smem + (size_t)MP * p.xpitch);
+  sm.red_ints = p.round * p.piece_rows * MP;
+  sm.scl = reinterpret_cast<float2 *>(sm.red + sm.red_ints);
+  sm.rowsc = reinterpret_cast<float *>(sm.scl + p.round * p.piece_rows);
+  const uint32_t tile_s = x_s + (uint32_t)MP * p.xpitch + (uint32_t)sm.red_ints * 4 +
+                          (uint32_t)(p.round * p.piece_rows) * 8 + 64 + (uint32_t)warp * (GV_G * GV_TILE_PITCH);
+  const int kw0 = ks * GV_KW + lane * 16;
+  const int seg_bytes = KS * GV_KW;
+
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  if (!p.overlap) asm volatile("griddepcontrol.wait;" ::: "memory");
+
+  uint4 wv[GV_G];
+  auto request = [&](int l, int seg) {
+    int r0, nr;
+    gv_piece(p, l, b, r0, nr);
+    const int koff = seg * seg_bytes + kw0;
+    const int first = grp * GV_G;
+    const int rows = koff < p.k ? nr - first : 0;
+    const int8_t *src = p.w + (int64_t)(r0 + first) * p.ldw + koff;
+#pragma unroll
+    for (int u = 0; u < GV_G; ++u) wv[u] = u < rows ? gv_ldg(src + (int64_t)u * p.ldw) : make_uint4(0, 0, 0, 0);
+  };
+  if (p.layers > 0) request(0, 0);
+  if (p.overlap) asm volatile("griddepcontrol.wait;" ::: "memory");
+
+  // Activations -> shared memory (rows past m and the pad past k are zero), while the first weights are on their way.
   {
-    const int chunks = p.k >> 4;
+    const int chunks = p.xpitch >> 4, kchunks = p.k >> 4;
     for (int e = tid; e < MP * chunks; e += GV_THREADS) {
       const int mi = e / chunks, ch = e - mi * chunks;
       uint4 v = make_uint4(0, 0, 0, 0);
-      if (mi < p.m) v = *reinterpret_cast<const uint4 *>(p.x + (int64_t)mi * p.ldx + (int64_t)ch * 16);
+      if (mi < p.m && ch < kchunks) v = *reinterpret_cast<const uint4 *>(p.x + (int64_t)mi * p.ldx + (int64_t)ch * 16);
       *reinterpret_cast<uint4 *>(gv_smem + (size_t)mi * p.xpitch + (size_t)ch * 16) = v;
     }
   }
-  __syncthreads();
 
   float my_max = -INFINITY;
-  const int groups_per_piece = GV_WARPS >> p.ksplit_log2;
+  const int g = lane >> 2, t = lane & 3;
   for (int base = 0; base < p.layers; base += p.round) {
     const int count = (p.layers - base) < p.round ? (p.layers - base) : p.round;
-    // Scales and bias of the outputs this thread will finish after this round, requested now so that their latency
-    // hides behind the stream.  Output o of the round: piece o / (groups * NOUT), then group, then mi*8 + row.
-    float cs_pre[GV_OUT_PER_THREAD], bias_pre[GV_OUT_PER_THREAD];
-    const int per_piece = groups_per_piece * NOUT, total = count * per_piece;
+    gv_round_begin(p, sm, base, count, b, tid);
+    __syncthreads();  // activations staged (first round), sums cleared
+    for (int l = 0; l < count; ++l) {
+      int32_t *sums = sm.red + (size_t)(l * p.piece_rows + grp * GV_G) * MP;
+      for (int seg = 0; seg < p.nseg; ++seg) {
+        const int kabs = seg * seg_bytes + ks * GV_KW;  // first byte of k this warp covers in this step
+        // park the 8 x 512 bytes in the warp's tile, then read them back as mma fragments
 #pragma unroll
-    for (int q = 0; q < GV_OUT_PER_THREAD; ++q) {
-      cs_pre[q] = 1.0f;
-      bias_pre[q] = 0.0f;
-      const int o = tid + q * GV_THREADS;
-      if (o < total && (p.col_scale || p.bias)) {
-        const int pc = o / per_piece, rem = o - pc * per_piece;
-        const int grp = rem / NOUT, wr = (rem - grp * NOUT) & 7;
-        int r0, nr;
-        gv_piece(p, base + pc, b, r0, nr);
-        const int row = grp * GV_G + wr;
-        if (row < nr) {
-          if (p.col_scale) cs_pre[q] = __ldg(p.col_scale + r0 + row);
-          if (p.bias) bias_pre[q] = __ldg(p.bias + r0 + row);
-        }
-      }
-    }
-
-    for (int l0 = 0; l0 < count; l0 += U) {
+        for (int u = 0; u < GV_G; ++u) gv_sts128(tile_s + u * GV_TILE_PITCH + lane * 16, wv[u]);
+        __syncwarp();
+        if (seg + 1 < p.nseg)
+          request(base + l, seg + 1);
+        else if (base + l + 1 < p.layers)
+          request(base + l + 1, 0);
+        int32_t acc[4] = {0, 0, 0, 0};
 #pragma unroll
-      for (int u = 0; u < U; ++u) {
-        const int l = l0 + u;  // piece inside the round; (base + l) % U == u because round is a multiple of U
-        if (l < count) {
-          int32_t acc[MATH == GV_MATH_MMA ? 4 : MP];
-#pragma unroll
-          for (int i = 0; i < (MATH == GV_MATH_MMA ? 4 : MP); ++i) acc[i] = 0;
-#pragma unroll
-          for (int j = 0; j < NBW; ++j) {
-#pragma unroll
-            for (int h = 0; h < 2; ++h) {
-              const int off = ((ks + (j << p.ksplit_log2)) << 7) + h * 64;
-              if (off < p.k) {  // uniform across the warp
-                const uint4 wq = wv[u][2 * j + h];
-                const uint32_t xa_addr = x_s + (uint32_t)off + (uint32_t)t * 16;
-                if constexpr (MATH == GV_MATH_DP4A) {
-#pragma unroll
-                  for (int mi = 0; mi < MP; ++mi) {
-                    const uint4 xq = gv_lds128(xa_addr + mi * p.xpitch);
-                    int32_t a = acc[mi];
-                    a = __dp4a((int)wq.x, (int)xq.x, a);
-                    a = __dp4a((int)wq.y, (int)xq.y, a);
-                    a = __dp4a((int)wq.z, (int)xq.z, a);
-                    a = __dp4a((int)wq.w, (int)xq.w, a);
-                    acc[mi] = a;
-                  }
-                } else {
-                  const uint4 xa = gv_lds128(xa_addr + g * p.xpitch);
-                  if constexpr (MP == 16) {
-                    const uint4 xb = gv_lds128(xa_addr + (g + 8) * p.xpitch);
-                    gv_mma(acc, xa.x, xb.x, xa.y, xb.y, wq.x, wq.y);
-                    gv_mma(acc, xa.z, xb.z, xa.w, xb.w, wq.z, wq.w);
-                  } else {
-                    gv_mma(acc, xa.x, 0u, xa.y, 0u, wq.x, wq.y);
-                    gv_mma(acc, xa.z, 0u, xa.w, 0u, wq.z, wq.w);
-                  }
-                }
-              }
+        for (int blk = 0; blk < GV_KW / 64; ++blk) {
+          const int koff = kabs + blk * 64;
+          if (koff < p.k) {  // uniform across the warp
+            const uint4 wq = gv_lds128(tile_s + g * GV_TILE_PITCH + blk * 64 + t * 16);
+            const uint32_t xa_addr = x_s + (uint32_t)(koff + t * 16);
+            const uint4 xa = gv_lds128(xa_addr + g * p.xpitch);
+            if constexpr (MP == 16) {
+              const uint4 xb = gv_lds128(xa_addr + (g + 8) * p.xpitch);
+              gv_mma(acc, xa.x, xb.x, xa.y, xb.y, wq.x, wq.y);
+              gv_mma(acc, xa.z, xb.z, xa.w, xb.w, wq.z, wq.w);
+            } else {
+              gv_mma(acc, xa.x, 0u, xa.y, 0u, wq.x, wq.y);
+              gv_mma(acc, xa.z, 0u, xa.w, 0u, wq.z, wq.w);
             }
           }
-          // the registers are free again: request the piece U further on (possibly of the next round)
-          if (base + l + U < p.layers) issue(wv[u], base + l + U);
-          // this warp's partial sums for its group of the piece, index mi*8 + row
-          int32_t *mine = red + ((size_t)l * GV_WARPS + warp) * NOUT;
-          if constexpr (MATH == GV_MATH_DP4A) {
-#pragma unroll
-            for (int mi = 0; mi < MP; ++mi) {
-              int32_t a = acc[mi];
-              a += __shfl_xor_sync(0xFFFFFFFFu, a, 1);
-              a += __shfl_xor_sync(0xFFFFFFFFu, a, 2);
-              if (t == 0) mine[mi * 8 + g] = a;
-            }
-          } else {
-            // lane (g, t) holds D[g][2t], D[g][2t+1], D[g+8][2t], D[g+8][2t+1]: activation row x weight row
-            *reinterpret_cast<int2 *>(mine + g * 8 + 2 * t) = make_int2(acc[0], acc[1]);
-            if constexpr (MP == 16) *reinterpret_cast<int2 *>(mine + (g + 8) * 8 + 2 * t) = make_int2(acc[2], acc[3]);
+        }
+        __syncwarp();  // every lane has read the tile before the next step overwrites it
+        if (kabs < p.k) {
+          // lane (g, t) holds D[g][2t], D[g][2t+1], D[g+8][2t], D[g+8][2t+1]: activation row x weight row
+          atomicAdd(sums + (2 * t) * MP + g, acc[0]);
+          atomicAdd(sums + (2 * t + 1) * MP + g, acc[1]);
+          if constexpr (MP == 16) {
+            atomicAdd(sums + (2 * t) * MP + g + 8, acc[2]);
+            atomicAdd(sums + (2 * t + 1) * MP + g + 8, acc[3]);
           }
         }
       }
     }
     __syncthreads();
-    // one thread per output: add the KS partial sums, run the epilogue
-#pragma unroll
-    for (int q = 0; q < GV_OUT_PER_THREAD; ++q) {
-      const int o = tid + q * GV_THREADS;
-      if (o < total) {
-        const int pc = o / per_piece, rem = o - pc * per_piece;
-        const int grp = rem / NOUT, idx = rem - grp * NOUT;
-        const int mi = idx >> 3, wr = idx & 7;
-        int r0, nr;
-        gv_piece(p, base + pc, b, r0, nr);
-        const int row = grp * GV_G + wr;
-        if (row < nr && mi < p.m) {
-          const int32_t *src = red + ((size_t)pc * GV_WARPS + (grp << p.ksplit_log2)) * NOUT + idx;
-          int32_t sum = 0;
-          for (int s = 0; s < KS; ++s) sum += src[s * NOUT];
-          const float rsc = p.row_scale ? __ldg(p.row_scale + mi) : 1.0f;
-          my_max = fmaxf(my_max, gemv_store(p, mi, r0 + row, sum, rsc, cs_pre[q], bias_pre[q]));
-        }
-      }
-    }
-    if (base + p.round < p.layers) __syncthreads();  // the partial sums are rewritten by the next round
+    my_max = fmaxf(my_max, gv_round_end<MP>(p, sm, base, count, b, tid));
+    if (base + p.round < p.layers) __syncthreads();
   }
   if (p.global_max) {
     my_max = warp_max_f32(my_max);
@@ -313,11 +450,13 @@ int num_sms() {
   return sms;
 }
 
-constexpr size_t GV_SMEM_MAX = 200 * 1024;
+constexpr size_t GV_SMEM_MAX = 227 * 1024;
+constexpr size_t GV_RED_MAX = 8 * 1024;  // shared memory for one round's sums; their rows' scale and bias take at most as much again
 
 // Activation rows the kernel variant for m carries (dp4a: m itself; mma: 8 or 16).
 inline int padded_m(int m) { return m <= 2 ? m : (m <= 8 ? 8 : 16); }
 inline int x_pitch(int k) { return ((k + 63) / 128) * 128 + 64; }
+inline size_t tile_bytes(int m) { return m <= 2 ? 0 : (size_t)GV_WARPS * GV_G * GV_TILE_PITCH; }
 
 }  // namespace
 }  // namespace sklb
@@ -329,12 +468,12 @@ extern "C" int skl_b200_gemv_i8_supported(const skl_b200_gemm_args *g) {
   if (g->m1 != 1 || g->n1 != 1 || g->k1 != 1) return 0;
   if (g->m0 == 0 || g->m0 > 16 || g->n0 == 0 || g->k0 == 0) return 0;
   if (g->csa0 != 1 || g->rsb0 != 1) return 0;
-  if ((g->k0 & 15) != 0 || g->k0 > 16384 || g->n0 > (1u << 30)) return 0;  // 8 blocks of 128 bytes per warp
+  if ((g->k0 & 15) != 0 || g->k0 > (1u << 20) || g->n0 > (1u << 30)) return 0;
   if (!al16(g->a) || !al16(g->b)) return 0;
   if ((g->m0 > 1 && (g->rsa0 & 15) != 0) || (g->n0 > 1 && (g->csb0 & 15) != 0)) return 0;
-  // the activations and the partial sums of eight pieces (as many as can be in flight) must fit in shared memory
+  // the activations, one round of sums and (mma variant) the warps' tiles must fit in shared memory
   const int mp = padded_m((int)g->m0);
-  if ((size_t)mp * x_pitch((int)g->k0) + 8 * (size_t)GV_WARPS * GV_G * mp * 4 > GV_SMEM_MAX) return 0;
+  if ((g->m0 <= 2 ? 0 : (size_t)mp * x_pitch((int)g->k0)) + 2 * GV_RED_MAX + 64 + tile_bytes((int)g->m0) > GV_SMEM_MAX) return 0;
   if (g->epilogue == SKL_EPI_INT && g->tc != SKL_DT_I32) return 0;
   if (g->epilogue == SKL_EPI_FLOAT && g->tc == SKL_DT_I32) return 0;
   return 1;
@@ -367,20 +506,17 @@ extern "C" int skl_b200_launch_gemv_i8(const skl_b200_gemm_args *g, uint32_t *de
   p.act_param = g->act_param;
   p.overlap = g->b_static ? 1 : 0;
 
-  // k split: the 128-byte blocks of a row go round the KS warps that share a group of 8 rows; KS is the largest
-  // power of two (at most 16) not above the block count, the other warps take further groups of the same piece.
-  const int blocks = (p.k + 127) / 128;
+  // k split: a warp takes 512 bytes of k; KS warps (a power of two, at most 8) share a group of 8 rows and cover a
+  // segment of KS * 512 bytes, longer k is walked segment by segment; the other warps take further groups of the piece.
+  const int kseg = p.k < GV_KSEG ? p.k : GV_KSEG;
   int ks_log2 = 0;
-  while (ks_log2 < 4 && (2 << ks_log2) <= blocks) ++ks_log2;
+  while ((GV_KW << ks_log2) < kseg) ++ks_log2;  // 0..3
   const int KS = 1 << ks_log2;
-  const int nbw_need = (blocks + KS - 1) / KS;  // 1..8 since k <= 16384
-  int nbw = 1;
-  while (nbw < nbw_need) nbw <<= 1;
   p.ksplit_log2 = ks_log2;
+  p.nseg = (p.k + KS * GV_KW - 1) / (KS * GV_KW);
   p.piece_rows = GV_G * (GV_WARPS / KS);
   p.xpitch = x_pitch(p.k);
   const int mp = padded_m(p.m);
-  const int nout = GV_G * mp;
 
   int grid = num_sms();
   {
@@ -395,66 +531,47 @@ extern "C" int skl_b200_launch_gemv_i8(const skl_b200_gemm_args *g, uint32_t *de
   p.pq1 = (p.lq + 1) / grid;
   p.pr1 = (p.lq + 1) % grid;
 
-  // pieces per round: bounded by the outputs a thread can finish (its scale registers) and by shared memory;
-  // a multiple of the pieces in flight so that a piece always lands in the same register set
-  const int u = GV_INFLIGHT / (2 * nbw);
-  const size_t x_bytes = (size_t)mp * p.xpitch;
-  const size_t piece_red = (size_t)GV_WARPS * nout * 4;
-  int round = (GV_OUT_PER_THREAD * GV_THREADS) / ((GV_WARPS / KS) * nout);
-  const int by_smem = (int)((GV_SMEM_MAX - x_bytes) / piece_red);
-  if (round > by_smem) round = by_smem;
-  round = round / u * u;
-  if (round < u) return (int)cudaErrorInvalidValue;
-  if (round > ((p.layers + u - 1) / u) * u) round = ((p.layers + u - 1) / u) * u;
+  // pieces per round: as many as one round's sums (and the threads' scale registers) allow
+  int round = (int)(GV_RED_MAX / 4) / (p.piece_rows * mp);
+  if (round < 1) round = 1;  // 256 rows x 16 activations: one piece fills 16 KiB
+  if (round > p.layers) round = p.layers;
   p.round = round;
-  const size_t smem = x_bytes + (size_t)round * piece_red;
+  const size_t smem = (p.m <= 2 ? 0 : (size_t)mp * p.xpitch) + (size_t)round * p.piece_rows * (mp * 4 + 8) + 64 + tile_bytes(p.m);
+  if (smem > GV_SMEM_MAX) return (int)cudaErrorInvalidValue;
 
   cudaStream_t s = (cudaStream_t)stream;
   cudaError_t e = cudaSuccess;
-#define GV_LAUNCH(MATHV, MPV, NBWV)                                                                          \
-  do {                                                                                                       \
-    static bool attr_set[64] = {}; /* per device */                                                          \
-    int dev = 0;                                                                                             \
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = 0;                                 \
-    if (!attr_set[dev]) {                                                                                    \
-      e = cudaFuncSetAttribute(gemv_i8_kernel<MATHV, MPV, NBWV>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
-                               (int)GV_SMEM_MAX);                                                            \
-      attr_set[dev] = (e == cudaSuccess);                                                                    \
-    }                                                                                                        \
-    if (e == cudaSuccess) {                                                                                  \
-      cudaLaunchConfig_t cfg = {};                                                                           \
-      cfg.gridDim = dim3((unsigned)grid);                                                                    \
-      cfg.blockDim = dim3(GV_THREADS);                                                                       \
-      cfg.dynamicSmemBytes = smem;                                                                           \
-      cfg.stream = s;                                                                                        \
-      cudaLaunchAttribute attr[1];                                                                           \
-      attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;                                       \
-      attr[0].val.programmaticStreamSerializationAllowed = 1;                                                \
-      cfg.attrs = attr;                                                                                      \
-      cfg.numAttrs = 1;                                                                                      \
-      e = cudaLaunchKernelEx(&cfg, gemv_i8_kernel<MATHV, MPV, NBWV>, p);                                     \
-    }                                                                                                        \
-  } while (0)
-#define GV_LAUNCH_NBW(MATHV, MPV)              \
-  do {                                         \
-    if (nbw == 1)                              \
-      GV_LAUNCH(MATHV, MPV, 1);                \
-    else if (nbw == 2)                         \
-      GV_LAUNCH(MATHV, MPV, 2);                \
-    else if (nbw == 4)                         \
-      GV_LAUNCH(MATHV, MPV, 4);                \
-    else                                       \
-      GV_LAUNCH(MATHV, MPV, 8);                \
+#define GV_LAUNCH(KERNEL)                                                                              \
+  do {                                                                                                 \
+    static bool attr_set[64] = {}; /* per device */                                                    \
+    int dev = 0;                                                                                       \
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = 0;                           \
+    if (!attr_set[dev]) {                                                                              \
+      e = cudaFuncSetAttribute(KERNEL, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GV_SMEM_MAX);  \
+      attr_set[dev] = (e == cudaSuccess);                                                              \
+    }                                                                                                  \
+    if (e == cudaSuccess) {                                                                            \
+      cudaLaunchConfig_t cfg = {};                                                                     \
+      cfg.gridDim = dim3((unsigned)grid);                                                              \
+      cfg.blockDim = dim3(GV_THREADS);                                                                 \
+      cfg.dynamicSmemBytes = smem;                                                                     \
+      cfg.stream = s;                                                                                  \
+      cudaLaunchAttribute attr[1];                                                                     \
+      attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;                                 \
+      attr[0].val.programmaticStreamSerializationAllowed = 1;                                          \
+      cfg.attrs = attr;                                                                                \
+      cfg.numAttrs = 1;                                                                                \
+      e = cudaLaunchKernelEx(&cfg, KERNEL, p);                                                         \
+    }                                                                                                  \
   } while (0)
   if (p.m == 1)
-    GV_LAUNCH_NBW(GV_MATH_DP4A, 1);
+    GV_LAUNCH(gemv_i8_dp4a_kernel<1>);
   else if (p.m == 2)
-    GV_LAUNCH_NBW(GV_MATH_DP4A, 2);
+    GV_LAUNCH(gemv_i8_dp4a_kernel<2>);
   else if (p.m <= 8)
-    GV_LAUNCH_NBW(GV_MATH_MMA, 8);
+    GV_LAUNCH(gemv_i8_mma_kernel<8>);
   else
-    GV_LAUNCH_NBW(GV_MATH_MMA, 16);
-#undef GV_LAUNCH_NBW
+    GV_LAUNCH(gemv_i8_mma_kernel<16>);
 #undef GV_LAUNCH
   if (e != cudaSuccess) return (int)e;
   SKLB_COUNT_LAUNCH();

@@ -1,4 +1,6 @@
-"""The five BASELINE configurations at their full sizes, through the C ABI with device-resident operands.
+"""The five configured workloads (int8 512 x 512 x 1024 and its 8192^3 companion, bf16 / fp16 4096^3, fp8 8192^3 from cvt,
+the decode-shape skinny int8 product, the bf16 x fp8 projection) at their full sizes, through the C ABI with
+device-resident operands.
 
 The scalar oracle cannot finish a full 4096^3 .. 16384 x 4096 x 14336 product in seconds, so each
 case is checked two ways: (1) exactly the reference's arithmetic on sampled rows of C -- every class of
@@ -146,7 +148,17 @@ def test_config3_fp8_8192_from_cvt(skl, ta):
     ref = H.bf16_bits_to_f32(want_rows).astype(np.float64)
     out = H.bf16_bits_to_f32(got).astype(np.float64)
     bound = H.skl_forward_bound(ta, a_rows, H.F8E4M3, b_host, alpha, 0.0, None, k)
-    assert np.all(np.abs(out - ref) <= H.bf16_ulp(ref) + bound)
+    ulp = H.bf16_ulp(ref)
+    err = np.abs(out - ref)
+    err_ulps = err / ulp
+    tight = bound < 0.5 * ulp  # where the accumulation-order slack cannot move the fp32 value across a rounding boundary
+    print(f"fp8 8192^3 ({'E4M3' if ta == H.F8E4M3 else 'E5M2'} x E4M3): worst error {err_ulps.max():.3f} bf16 ulp over "
+          f"{err.size} sampled outputs; {np.count_nonzero(err > 0)} differ from the oracle's rounding at all; "
+          f"{np.count_nonzero(tight)} have a forward bound under half an ulp")
+    # the stated rule, pure, wherever the summation-order slack is below half an ulp of the output type
+    assert np.all(err[tight] <= ulp[tight])
+    # elsewhere the fp32 value itself may differ by the reference suite's bound before it is rounded
+    assert np.all(err <= ulp + bound)
 
 
 @pytest.mark.parametrize("mm", [1, 4, 16])

@@ -58,7 +58,7 @@ def test_tensor_core_matches_generic_bits_for_int8_and_bound_for_float(skl, t):
 
 @pytest.mark.parametrize("pair", ["0", "2"])
 def test_config1_int8_512x512x1024_bit_exact(skl, pair, monkeypatch):
-    """BASELINE config 1: A row-major, B K x N row-major, int32 out, alpha 1, beta 0; both pointer domains."""
+    """The first configured workload (int8 512 x 512 x 1024): A row-major, B K x N row-major, int32 out, alpha 1, beta 0; both pointer domains."""
     monkeypatch.setenv("SKL_B200_TC_PAIR", pair)
     for where in ("device", "host"):
         check_gemm_rc(skl, H.I8, 512, 512, 1024, "rrr", 1, 0, where=where, seed=1, expect_path=S.PATH_TCGEN05)

@@ -66,7 +66,7 @@ def ex_case(skl, m, n, k, ta, tb, tc, layout, alpha, beta, use_rs, use_cs, where
 
 @pytest.mark.parametrize("m", [1, 4, 16])
 def test_config4_decode_gemv_dequantised(skl, m):
-    """BASELINE config 4 at full size: int8 weights 14336 x 4096 with per-row scales, int8 activations with
+    """The decode-shape workload at full size: int8 weights 14336 x 4096 with per-row scales, int8 activations with
     per-row scale, fp32 out = ((float)acc * s_x[i]) * s_w[j].  The accumulator is exact, so the result
     must equal the oracle's bit for bit."""
     for where in ("device", "host"):
