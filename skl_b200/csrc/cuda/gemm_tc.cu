@@ -727,6 +727,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
+      const bool panelled = p.a_panel != PLAIN_PANEL;  // the packed matrix-engine form: both operands in panels
       TileUnit u;
       for (int it = 0; ok && get_unit<BN>(p, it, u); ++it) {
         const int m0 = u.m0, n0 = u.n0;
@@ -734,49 +735,68 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         const bool strip = u.ncols != p.bn_main;
         const uint32_t stage_tx = Cfg::A_BYTES + (strip ? p.tail_b_bytes : p.main_b_bytes);
         const int b_boxes = strip ? p.tail_b_atoms : p.main_b_atoms;
-        MnBoxes<A_ATOMS> abox;
-        MnBoxes<B_ATOMS> bbox;
-        if (p.a_mn && p.a_panel != PLAIN_PANEL) abox.set(m0, MN_PER_ATOM, p.a_panel);
-        if (p.b_mn && p.b_panel != PLAIN_PANEL) bbox.set(n0, MN_PER_ATOM, p.b_panel);
-        for (int kb = 0; kb < p.num_kb; ++kb) {
-          if (!mbar_wait(empty_bar + 8 * stage, phase ^ 1u, abort_flag, p.status, ERR_WAIT_EMPTY, p.wait_ns)) {
-            ok = false;
-            break;
-          }
-          const uint32_t fb = full_bar + 8 * stage;
-          const uint32_t sa = tiles + stage * Cfg::STAGE_BYTES, sb = sa + Cfg::A_BYTES;
-          mbar_expect_tx(fb, stage_tx);
-          if (p.skip_loads) {  // testing aid: the bytes never arrive, the waits on this stage run out
-            ok = false;
-            break;
-          }
-          const int k0 = kb * BKE;
-          if (!p.a_mn) {
-            tma_load_2d(sa, &tmA, fb, k0, m0);
-          } else {
+        // The k loop exists twice: plain operands (2-D maps, box coordinates known without arithmetic) and panelled ones
+        // (3-D maps).  The producer thread issues up to five loads per stage and is close to being the bottleneck for
+        // an MN-major B, so the choice is made once per tile, not once per box.
+        if (!panelled) {
+          for (int kb = 0; kb < p.num_kb; ++kb) {
+            if (!mbar_wait(empty_bar + 8 * stage, phase ^ 1u, abort_flag, p.status, ERR_WAIT_EMPTY, p.wait_ns)) {
+              ok = false;
+              break;
+            }
+            const uint32_t fb = full_bar + 8 * stage;
+            const uint32_t sa = tiles + stage * Cfg::STAGE_BYTES, sb = sa + Cfg::A_BYTES;
+            mbar_expect_tx(fb, stage_tx);
+            if (p.skip_loads) {  // testing aid: the bytes never arrive, the waits on this stage run out
+              ok = false;
+              break;
+            }
+            const int k0 = kb * BKE;
+            if (!p.a_mn) {
+              tma_load_2d(sa, &tmA, fb, k0, m0);
+            } else {
 #pragma unroll
-            for (int i = 0; i < A_ATOMS; ++i) {
-              if (p.a_panel == PLAIN_PANEL)
-                tma_load_2d(sa + i * ATOM_BYTES, &tmA, fb, m0 + i * MN_PER_ATOM, k0);
-              else
-                tma_load_3d(sa + i * ATOM_BYTES, &tmA, fb, abox.x[i], k0, abox.z[i]);
+              for (int i = 0; i < A_ATOMS; ++i) tma_load_2d(sa + i * ATOM_BYTES, &tmA, fb, m0 + i * MN_PER_ATOM, k0);
+            }
+            if (!p.b_mn) {
+              tma_load_2d(sb, strip ? &tmBs : &tmB, fb, k0, n0);
+            } else {
+#pragma unroll
+              for (int i = 0; i < B_ATOMS; ++i)
+                if (i < b_boxes) tma_load_2d(sb + i * ATOM_BYTES, &tmB, fb, n0 + i * MN_PER_ATOM, k0);
+            }
+            if (++stage == Cfg::STAGES) {
+              stage = 0;
+              phase ^= 1u;
             }
           }
-          if (!p.b_mn) {
-            tma_load_2d(sb, strip ? &tmBs : &tmB, fb, k0, n0);
-          } else {
+        } else {
+          MnBoxes<A_ATOMS> abox;
+          MnBoxes<B_ATOMS> bbox;
+          abox.set(m0, MN_PER_ATOM, p.a_panel);
+          bbox.set(n0, MN_PER_ATOM, p.b_panel);
+          for (int kb = 0; kb < p.num_kb; ++kb) {
+            if (!mbar_wait(empty_bar + 8 * stage, phase ^ 1u, abort_flag, p.status, ERR_WAIT_EMPTY, p.wait_ns)) {
+              ok = false;
+              break;
+            }
+            const uint32_t fb = full_bar + 8 * stage;
+            const uint32_t sa = tiles + stage * Cfg::STAGE_BYTES, sb = sa + Cfg::A_BYTES;
+            mbar_expect_tx(fb, stage_tx);
+            if (p.skip_loads) {
+              ok = false;
+              break;
+            }
+            const int k0 = kb * BKE;
+#pragma unroll
+            for (int i = 0; i < A_ATOMS; ++i) tma_load_3d(sa + i * ATOM_BYTES, &tmA, fb, abox.x[i], k0, abox.z[i]);
 #pragma unroll
             for (int i = 0; i < B_ATOMS; ++i)
-              if (i < b_boxes) {
-                if (p.b_panel == PLAIN_PANEL)
-                  tma_load_2d(sb + i * ATOM_BYTES, &tmB, fb, n0 + i * MN_PER_ATOM, k0);
-                else
-                  tma_load_3d(sb + i * ATOM_BYTES, &tmB, fb, bbox.x[i], k0, bbox.z[i]);
-              }
-          }
-          if (++stage == Cfg::STAGES) {
-            stage = 0;
-            phase ^= 1u;
+              if (i < b_boxes) tma_load_3d(sb + i * ATOM_BYTES, &tmB, fb, bbox.x[i], k0, bbox.z[i]);
+            if (++stage == Cfg::STAGES) {
+              stage = 0;
+              phase ^= 1u;
+            }
           }
         }
       }
@@ -972,8 +992,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         const int m0 = mi * (2 * BM) + (int)rank * BM, n0 = ni * BN + (int)rank * BH;
         MnBoxes<A_ATOMS> abox;
         MnBoxes<B_ATOMS> bbox;
-        if (p.a_mn && p.a_panel != PLAIN_PANEL) abox.set(m0, MN_PER_ATOM, p.a_panel);
-        if (p.b_mn && p.b_panel != PLAIN_PANEL) bbox.set(n0, MN_PER_ATOM, p.b_panel);
+        if (p.a_panel != PLAIN_PANEL) abox.set(m0, MN_PER_ATOM, p.a_panel);
+        if (p.b_panel != PLAIN_PANEL) bbox.set(n0, MN_PER_ATOM, p.b_panel);
         for (int kb = 0; kb < p.num_kb; ++kb) {
           if (!mbar_wait(empty_bar + 8 * stage, phase ^ 1u, abort_flag, p.status, ERR_WAIT_EMPTY, p.wait_ns)) {
             ok = false;
@@ -1132,11 +1152,12 @@ struct OperandView {
   bool ok;
   // MN-major only: the operand as `panels` panels of `panel` consecutive m (n) elements, `panel_ld` elements apart
   int64_t panel, panels, panel_ld;
+  bool panel_form;  // SKL's packed matrix-engine operand (3-D tensor map) rather than a plain matrix
 };
 
 // extent_mn x K operand with strides (s_mn, s_k) in elements.
 OperandView classify(const void *base, int64_t extent_mn, int64_t K, int64_t s_mn, int64_t s_k, int es) {
-  OperandView v{0, 0, false, extent_mn, 1, 0};
+  OperandView v{0, 0, false, extent_mn, 1, 0, false};
   if ((reinterpret_cast<uintptr_t>(base) & 15u) != 0) return v;
   auto ld_ok = [&](int64_t ld, int64_t inner, int64_t outer) {
     if (outer <= 1) return true;
@@ -1160,7 +1181,7 @@ OperandView classify(const void *base, int64_t extent_mn, int64_t K, int64_t s_m
 // of 128-byte rows.
 OperandView classify_panels(const void *base, int64_t panel, int64_t panels, int64_t K, int64_t k_stride,
                             int64_t panel_stride, int es) {
-  OperandView v{1, k_stride, false, panel, panels, panel_stride};
+  OperandView v{1, k_stride, false, panel, panels, panel_stride, true};
   if ((reinterpret_cast<uintptr_t>(base) & 15u) != 0) return v;
   if (panel <= 0 || (panel * es) % SLAB_BYTES != 0) return v;
   if (K > 1 && (k_stride < panel || ((k_stride * es) & 15) != 0)) return v;
@@ -1212,7 +1233,7 @@ bool make_map(CUtensorMap *tm, int kind, int dt, const void *base, const Operand
     int64_t ld = v.ld;
     if (dims[1] <= 1) ld = (int64_t)((dims[0] * es + 15) / 16 * 16) / es;  // stride unused; keep it legal
     strides[0] = (cuuint64_t)ld * es;
-  } else if (v.panels <= 1) {
+  } else if (!v.panel_form) {
     dims[0] = (cuuint64_t)extent_mn;
     dims[1] = (cuuint64_t)K;
     box[0] = (cuuint32_t)per_row;
@@ -1536,8 +1557,8 @@ extern "C" int skl_b200_launch_gemm_tc(const skl_b200_gemm_args *g, uint32_t *de
   // A plain MN-major matrix keeps its 2-D tensor map and box-aligned x (TMA needs x * element size to be a multiple
   // of 16 bytes; a tile that reaches past the last row / column reads the zero fill).  Panelled operands get a 3-D
   // map; panels are whole numbers of boxes (classify_panels), so x stays aligned there too.
-  p.a_panel = va.panels > 1 ? (int)va.panel : PLAIN_PANEL;
-  p.b_panel = vb.panels > 1 ? (int)vb.panel : PLAIN_PANEL;
+  p.a_panel = va.panel_form ? (int)va.panel : PLAIN_PANEL;
+  p.b_panel = vb.panel_form ? (int)vb.panel : PLAIN_PANEL;
   p.c_block_m = blocked_c ? (int)g->m0 : 0;
   p.c_block_n = blocked_c ? (int)g->n0 : 0;
   p.rsc1 = g->rsc1;

@@ -9,32 +9,31 @@
 // Design.  A plain 16-byte-per-thread read of the weight matrix, 1024 threads per SM with 8 loads each in flight
 // (128 KiB per SM), runs at 0.96 of the device's copy bandwidth at this size; staging the rows through shared memory
 // with bulk copies measured 20-50 % slower, and so did fewer threads with more loads each or warp-wide loads that
-// gather 64-byte pieces of 8 rows.  So the kernel IS that read, with the arithmetic hung on it:
-//   * One CTA of 32 warps per SM.  A warp owns 512 bytes of k (KS = k / 512 warps share a group of 8 rows; the other
-//     warps of the CTA take further groups), and one warp-wide load is 512 contiguous bytes of one row: a step of the
-//     CTA reads up to 32 consecutive rows of 4 KiB, every thread holding 8 independent 16-byte loads
-//     (ld.global.nc, no L1 allocation).
-//   * The weight rows are dealt to the CTAs in layers: layer l is a run of consecutive rows cut into one piece per
-//     CTA, so at any moment all CTAs read neighbouring rows and every CTA gets the same number of bytes to within
-//     one row.  (Measured against per-CTA contiguous ranges and a grid-stride over 8-row units: 9.9 vs 10.6 / 10.3 us.)
-//       m <= 2   dp4a straight from the load registers against the same chunk of the activations, a butterfly
-//                warp-shuffle fold of the 8 rows' partial sums.  No tensor cores.
-//       m >= 3   mma.sync.m16n8k32.s8: dp4a cannot keep up with HBM here (4*m dp4a per 16 weight bytes on a
-//                two-per-clock pipe).  The warp parks its 8 x 512 bytes in a private shared-memory tile (rows 64
-//                bytes off the 128-byte grid, so fragment loads of neighbouring rows hit different banks) and reads
-//                them back in the operand layout of the instruction, the 8 weight rows as its 8-column operand, the
-//                activations (16 rows, zero padded) as the other; the k order inside a fragment is a fixed permutation
-//                applied to both operands.
-//     The activations sit in shared memory, rows 64 bytes off the 128-byte grid for the same reason.
-//   * The KS partial sums of an output meet in shared memory through integer atomic adds (int32 sums wrap around
-//     like the reference's, in any order, so the result is exact); after the CTA's last piece (or every `round`
-//     pieces when there are many) one barrier, then one thread per output runs the fused alpha/beta or dequantising
-//     epilogue.
-// The kernel has no waits on barriers that another agent completes, hence nothing that could time out.
+// gather 64-byte pieces of 8 rows.  So one warp-wide access is always 512 contiguous bytes of one weight row, and:
+//   * One CTA of 32 warps per SM.  The weight rows are dealt to the CTAs in layers: layer l is a run of consecutive
+//     rows cut into one piece per CTA, so at any moment all CTAs read neighbouring rows and every CTA gets the same
+//     number of bytes to within one row.  (Measured against per-CTA contiguous ranges and a grid-stride over 8-row
+//     units: 9.9 vs 10.6 / 10.3 us.)
+//   * m <= 2: the kernel IS that read, with the arithmetic hung on it.  A warp owns 512 bytes of k (KS = k / 512
+//     warps share a group of 8 rows; the other warps of the CTA take further groups), a step of the CTA reads up to 32
+//     consecutive rows of 4 KiB, every thread holding 8 independent 16-byte loads (ld.global.nc, no L1 allocation);
+//     dp4a straight from the load registers against the same chunk of the activations, a butterfly warp-shuffle fold
+//     of the 8 rows' partial sums.  The KS partial sums of an output meet in shared memory through integer atomic adds
+//     (int32 sums wrap around like the reference's, in any order, so the result is exact); after the CTA's last piece
+//     (or every `round` pieces when there are many) one barrier, then one thread per output runs the fused alpha/beta
+//     or dequantising epilogue.  No tensor cores, no waits on barriers that another agent completes.
+//   * 3 <= m <= 16: dp4a cannot keep up with HBM (4*m dp4a per 16 weight bytes on a two-per-clock pipe), so the sums
+//     are formed by mma.sync.m16n8k32.s8 straight from the same load registers after a transposition across the warp
+//     (see the kernel's comment).  The library's dispatcher prefers the tcgen05 GEMM kernel with swapped operands for
+//     these m (15.3 us against 17.4 us on 14336 x 4096 at m = 4); this variant serves callers that force the skinny
+//     path.  Other designs measured on that size and dropped: tcgen05.mma on 128-row tiles filled by plain loads and
+//     st.shared (20-25 us), the same filled by cp.async in three 72 KiB stages (16.7 us: the tensor core's reads of a
+//     tile and the fills of the next did not overlap), fragments re-read from a warp-private shared-memory tile (22-30 us).
 //
-// Launch overlap.  The kernel lets its successor on the stream start early (griddepcontrol) and is itself
-// launched as such a dependent; it waits for its predecessor before its first global read.  When the caller
-// declared the weights static the first loads of the weight stream are issued before that wait.
+// Launch overlap.  The kernels let their successor on the stream start early (griddepcontrol) and are themselves
+// launched as such dependents; they wait for their predecessor before their first global read, having asked the L2
+// for the first lines.  When the caller declared the weights static the first reads of the weight stream are issued
+// before that wait.
 // Algorithmic bytes per launch: N*K (weights) + m*K (activations) + output and scale vectors.
 #include <cstdlib>
 
@@ -45,10 +44,9 @@ namespace {
 
 constexpr int GV_WARPS = 32;
 constexpr int GV_THREADS = GV_WARPS * 32;
-constexpr int GV_G = 8;               // weight rows per warp and step (the 8-column operand of one mma)
+constexpr int GV_G = 8;               // weight rows per warp and step
 constexpr int GV_KW = 512;            // bytes of k per warp
 constexpr int GV_KSEG = 8 * GV_KW;    // most bytes of k per step
-constexpr int GV_TILE_PITCH = GV_KW + 64;  // warp-private tile of the mma variant: 8 rows of 512 bytes, 64 mod 128 apart
 
 struct GemvParams {
   const int8_t *x;  // activations, row i at x + i*ldx
@@ -59,7 +57,6 @@ struct GemvParams {
   int ksplit_log2;    // warps sharing one group of 8 rows: KS = 1 << ksplit_log2, each takes 512 bytes of a k segment
   int nseg;           // k segments of KS * 512 bytes
   int piece_rows;     // rows of one piece = 8 * (GV_WARPS / KS)
-  int xpitch;         // bytes between activation rows in shared memory (64 mod 128)
   int layers;         // pieces per CTA
   int round;          // pieces between two reductions
   // layer l covers rows [l*lq + min(l, lr), +lq + (l < lr)); a layer of length len is cut into gridDim.x pieces,
@@ -82,8 +79,10 @@ __device__ __forceinline__ uint4 gv_lds128(uint32_t addr) {
   asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
   return v;
 }
-__device__ __forceinline__ void gv_sts128(uint32_t addr, const uint4 &v) {
-  asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+__device__ __forceinline__ uint2 gv_lds64(uint32_t addr) {
+  uint2 v;
+  asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
+  return v;
 }
 // D (16 x 8, int32) += A (16 x 32, int8, row) * B (32 x 8, int8, col); sums wrap around.
 __device__ __forceinline__ void gv_mma(int32_t (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
@@ -162,7 +161,7 @@ __device__ __forceinline__ uint4 gv_ldg(const void *p) {
   return v;
 }
 
-// Shared-memory carve-up common to both kernels: activations (mma kernel only) | sums | column scale and bias | tiles.
+// Shared-memory carve-up of the dp4a kernel: sums | column scale and bias | row scales.
 struct GvSmem {
   int32_t *red;    // sums [round * piece_rows][MP]
   float2 *scl;     // (column scale, bias) of every row slot of the round
@@ -331,99 +330,150 @@ __global__ void __launch_bounds__(GV_THREADS, 1) gemv_i8_dp4a_kernel(const GemvP
   }
 }
 
-// ---- m >= 3: mma.sync.m16n8k32.s8 on fragments read back from a warp-private shared-memory tile; MP = 8 or 16
-// activation rows (zero padded) in shared memory.
+// ---- 3 <= m <= 16: mma.sync.m16n8k32.s8 straight from the load registers, after a transposition across the warp.
+// The loads leave lane L with chunk L (16 bytes) of each of the 8 rows; the instruction wants lane (g, t) = (L / 4,
+// L % 4) to supply bytes of row g.  Three rounds of exchanges (lanes 4, 8, 16 apart swap half of their registers) turn
+// "register u = row u, lane = chunk" into "register j = chunk 4 j + t of row g": 48 shuffles for 4 KiB.  The order of k
+// inside a fragment is then a fixed permutation, which the activations' fragments -- built once per CTA in shared
+// memory, one 16-byte (MP = 16) or 8-byte (MP = 8) entry per lane and instruction, so that a warp reads 512 or 256
+// contiguous bytes -- follow.  The activations are the 16-row operand (rows past m are zero), the 8 weight rows the
+// 8-column one.  Everything else is the dp4a kernel: same loads, pieces, sums in shared memory, epilogue.
 template <int MP>
 __global__ void __launch_bounds__(GV_THREADS, 1) gemv_i8_mma_kernel(const GemvParams p) {
   extern __shared__ __align__(128) uint8_t gv_smem[];
-  // layout: activations [MP][xpitch] | sums | column scale and bias | tiles [GV_WARPS][8][GV_TILE_PITCH]
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, b = (int)blockIdx.x;
   const int KS = 1 << p.ksplit_log2;
   const int ks = warp & (KS - 1), grp = warp >> p.ksplit_log2;
-  const uint32_t x_s = gv_smem_u32(gv_smem);
+  const int g = lane >> 2, t = lane & 3;
+  // layout: activation fragments [windows of 512 bytes][16 instructions][32 lanes] | sums | column scale and bias | row scales
+  constexpr int ENTRY = MP == 16 ? 16 : 8;
+  const int windows = p.nseg * KS;
   GvSmem sm;
-  sm.red = reinterpret_cast<int32_t *>(gv_smem + (size_t)MP * p.xpitch);
+  sm.red = reinterpret_cast<int32_t *>(gv_smem + (size_t)windows * 512 * ENTRY);
   sm.red_ints = p.round * p.piece_rows * MP;
   sm.scl = reinterpret_cast<float2 *>(sm.red + sm.red_ints);
   sm.rowsc = reinterpret_cast<float *>(sm.scl + p.round * p.piece_rows);
-  const uint32_t tile_s = x_s + (uint32_t)MP * p.xpitch + (uint32_t)sm.red_ints * 4 +
-                          (uint32_t)(p.round * p.piece_rows) * 8 + 64 + (uint32_t)warp * (GV_G * GV_TILE_PITCH);
+  const uint32_t xfrag = gv_smem_u32(gv_smem);
   const int kw0 = ks * GV_KW + lane * 16;
   const int seg_bytes = KS * GV_KW;
 
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-  if (!p.overlap) asm volatile("griddepcontrol.wait;" ::: "memory");
+  if (!p.overlap) {
+    if (p.layers > 0 && (lane & 7) == 0 && kw0 < p.k) {
+      int r0, nr;
+      gv_piece(p, 0, b, r0, nr);
+      const int rows = nr - grp * GV_G;
+      const int8_t *src = p.w + (int64_t)(r0 + grp * GV_G) * p.ldw + kw0;
+      for (int u = 0; u < GV_G && u < rows; ++u) asm volatile("prefetch.global.L2 [%0];" ::"l"(src + (int64_t)u * p.ldw));
+    }
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+  }
 
-  uint4 wv[GV_G];
-  auto request = [&](int l, int seg) {
+  uint4 va[4], vb[4];
+  auto request = [&](uint4 (&dst)[4], int h, int l, int seg) {
     int r0, nr;
     gv_piece(p, l, b, r0, nr);
     const int koff = seg * seg_bytes + kw0;
-    const int first = grp * GV_G;
+    const int first = grp * GV_G + 4 * h;
     const int rows = koff < p.k ? nr - first : 0;
     const int8_t *src = p.w + (int64_t)(r0 + first) * p.ldw + koff;
 #pragma unroll
-    for (int u = 0; u < GV_G; ++u) wv[u] = u < rows ? gv_ldg(src + (int64_t)u * p.ldw) : make_uint4(0, 0, 0, 0);
+    for (int u = 0; u < 4; ++u) dst[u] = u < rows ? gv_ldg(src + (int64_t)u * p.ldw) : make_uint4(0, 0, 0, 0);
   };
-  if (p.layers > 0) request(0, 0);
+  const int steps = p.layers * p.nseg;
+  if (steps > 0) {
+    request(va, 0, 0, 0);
+    request(vb, 1, 0, 0);
+  }
   if (p.overlap) asm volatile("griddepcontrol.wait;" ::: "memory");
 
-  // Activations -> shared memory (rows past m and the pad past k are zero), while the first weights are on their way.
+  // Activation fragments.  A thread takes one 16-byte chunk of one row (lanes: 8 rows x 4 chunks, 64 contiguous bytes
+  // per row) and scatters its 4 words: word w of chunk 4 j + t of row i belongs to instruction 2 j + w / 2 of the
+  // window, lane (i % 8, t), operand register (w % 2) * 2 + i / 8.
   {
-    const int chunks = p.xpitch >> 4, kchunks = p.k >> 4;
-    for (int e = tid; e < MP * chunks; e += GV_THREADS) {
-      const int mi = e / chunks, ch = e - mi * chunks;
+    const int items = windows * 8 * (MP / 8) * 32;  // (window, j, upper half of the rows) x lane
+    for (int e = tid; e < items; e += GV_THREADS) {
+      const int ln = e & 31, rest = e >> 5;
+      const int hi = MP == 16 ? (rest & 1) : 0, r2 = MP == 16 ? (rest >> 1) : rest;
+      const int j = r2 & 7, win = r2 >> 3;
+      const int row = (ln >> 2) + 8 * hi, tt = ln & 3;
+      const int koff = win * GV_KW + 16 * (4 * j + tt);
       uint4 v = make_uint4(0, 0, 0, 0);
-      if (mi < p.m && ch < kchunks) v = *reinterpret_cast<const uint4 *>(p.x + (int64_t)mi * p.ldx + (int64_t)ch * 16);
-      *reinterpret_cast<uint4 *>(gv_smem + (size_t)mi * p.xpitch + (size_t)ch * 16) = v;
+      if (row < p.m && koff < p.k) v = *reinterpret_cast<const uint4 *>(p.x + (int64_t)row * p.ldx + koff);
+      const uint32_t e0 = xfrag + (uint32_t)(((win * 16 + 2 * j) * 32 + ln) * ENTRY) + (uint32_t)(hi * 4);
+      const uint32_t step2 = MP == 16 ? 8u : 4u;  // distance between the operand registers of the two halves of k
+      asm volatile("st.shared.u32 [%0], %1;" ::"r"(e0), "r"(v.x) : "memory");
+      asm volatile("st.shared.u32 [%0], %1;" ::"r"(e0 + step2), "r"(v.y) : "memory");
+      asm volatile("st.shared.u32 [%0], %1;" ::"r"(e0 + 32u * ENTRY), "r"(v.z) : "memory");
+      asm volatile("st.shared.u32 [%0], %1;" ::"r"(e0 + 32u * ENTRY + step2), "r"(v.w) : "memory");
     }
   }
 
   float my_max = -INFINITY;
-  const int g = lane >> 2, t = lane & 3;
+  int l_next = 0, seg_next = 0;
+  auto advance = [&]() {
+    if (++seg_next == p.nseg) {
+      seg_next = 0;
+      ++l_next;
+    }
+  };
+  advance();
+  // one exchange: lanes `dist` apart swap, the lower one giving `hi` for the partner's `lo`
+  auto swap_words = [&](uint4 &lo, uint4 &hi, bool upper, int dist) {
+    uint32_t s, r;
+    s = upper ? lo.x : hi.x; r = __shfl_xor_sync(0xFFFFFFFFu, s, dist); if (upper) lo.x = r; else hi.x = r;
+    s = upper ? lo.y : hi.y; r = __shfl_xor_sync(0xFFFFFFFFu, s, dist); if (upper) lo.y = r; else hi.y = r;
+    s = upper ? lo.z : hi.z; r = __shfl_xor_sync(0xFFFFFFFFu, s, dist); if (upper) lo.z = r; else hi.z = r;
+    s = upper ? lo.w : hi.w; r = __shfl_xor_sync(0xFFFFFFFFu, s, dist); if (upper) lo.w = r; else hi.w = r;
+  };
+  const bool up4 = (lane & 4) != 0, up8 = (lane & 8) != 0, up16 = (lane & 16) != 0;
   for (int base = 0; base < p.layers; base += p.round) {
     const int count = (p.layers - base) < p.round ? (p.layers - base) : p.round;
     gv_round_begin(p, sm, base, count, b, tid);
-    __syncthreads();  // activations staged (first round), sums cleared
+    __syncthreads();  // also: the activation fragments are complete
     for (int l = 0; l < count; ++l) {
       int32_t *sums = sm.red + (size_t)(l * p.piece_rows + grp * GV_G) * MP;
       for (int seg = 0; seg < p.nseg; ++seg) {
-        const int kabs = seg * seg_bytes + ks * GV_KW;  // first byte of k this warp covers in this step
-        // park the 8 x 512 bytes in the warp's tile, then read them back as mma fragments
+        const bool more = l_next < p.layers;
+        const uint32_t xw = xfrag + (uint32_t)(((seg * KS + ks) * 16 * 32 + lane) * ENTRY);
+        // rows <-> chunks: register j ends up holding chunk 4 j + t of row g
+        swap_words(va[0], va[1], up4, 4);
+        swap_words(va[2], va[3], up4, 4);
+        swap_words(va[0], va[2], up8, 8);
+        swap_words(va[1], va[3], up8, 8);
+        swap_words(vb[0], vb[1], up4, 4);
+        swap_words(vb[2], vb[3], up4, 4);
+        swap_words(vb[0], vb[2], up8, 8);
+        swap_words(vb[1], vb[3], up8, 8);
 #pragma unroll
-        for (int u = 0; u < GV_G; ++u) gv_sts128(tile_s + u * GV_TILE_PITCH + lane * 16, wv[u]);
-        __syncwarp();
-        if (seg + 1 < p.nseg)
-          request(base + l, seg + 1);
-        else if (base + l + 1 < p.layers)
-          request(base + l + 1, 0);
-        int32_t acc[4] = {0, 0, 0, 0};
-#pragma unroll
-        for (int blk = 0; blk < GV_KW / 64; ++blk) {
-          const int koff = kabs + blk * 64;
-          if (koff < p.k) {  // uniform across the warp
-            const uint4 wq = gv_lds128(tile_s + g * GV_TILE_PITCH + blk * 64 + t * 16);
-            const uint32_t xa_addr = x_s + (uint32_t)(koff + t * 16);
-            const uint4 xa = gv_lds128(xa_addr + g * p.xpitch);
-            if constexpr (MP == 16) {
-              const uint4 xb = gv_lds128(xa_addr + (g + 8) * p.xpitch);
-              gv_mma(acc, xa.x, xb.x, xa.y, xb.y, wq.x, wq.y);
-              gv_mma(acc, xa.z, xb.z, xa.w, xb.w, wq.z, wq.w);
-            } else {
-              gv_mma(acc, xa.x, 0u, xa.y, 0u, wq.x, wq.y);
-              gv_mma(acc, xa.z, 0u, xa.w, 0u, wq.z, wq.w);
-            }
-          }
-        }
-        __syncwarp();  // every lane has read the tile before the next step overwrites it
-        if (kabs < p.k) {
-          // lane (g, t) holds D[g][2t], D[g][2t+1], D[g+8][2t], D[g+8][2t+1]: activation row x weight row
-          atomicAdd(sums + (2 * t) * MP + g, acc[0]);
-          atomicAdd(sums + (2 * t + 1) * MP + g, acc[1]);
+        for (int u = 0; u < 4; ++u) swap_words(va[u], vb[u], up16, 16);
+        int32_t d[4] = {0, 0, 0, 0};
+        auto fma_slot = [&](const uint4 &w, int j) {
           if constexpr (MP == 16) {
-            atomicAdd(sums + (2 * t) * MP + g + 8, acc[2]);
-            atomicAdd(sums + (2 * t + 1) * MP + g + 8, acc[3]);
+            const uint4 a = gv_lds128(xw + (uint32_t)((2 * j) * 32 * ENTRY));
+            const uint4 c = gv_lds128(xw + (uint32_t)((2 * j + 1) * 32 * ENTRY));
+            gv_mma(d, a.x, a.y, a.z, a.w, w.x, w.y);
+            gv_mma(d, c.x, c.y, c.z, c.w, w.z, w.w);
+          } else {
+            const uint2 a = gv_lds64(xw + (uint32_t)((2 * j) * 32 * ENTRY));
+            const uint2 c = gv_lds64(xw + (uint32_t)((2 * j + 1) * 32 * ENTRY));
+            gv_mma(d, a.x, 0u, a.y, 0u, w.x, w.y);
+            gv_mma(d, c.x, 0u, c.y, 0u, w.z, w.w);
           }
+        };
+#pragma unroll
+        for (int u = 0; u < 4; ++u) fma_slot(va[u], u);
+        if (more) request(va, 0, l_next, seg_next);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) fma_slot(vb[u], 4 + u);
+        if (more) request(vb, 1, l_next, seg_next);
+        advance();
+        // lane (g, t) holds the sums of activation rows g, g + 8 with weight rows 2 t, 2 t + 1 of the group
+        atomicAdd(sums + (2 * t) * MP + g, d[0]);
+        atomicAdd(sums + (2 * t + 1) * MP + g, d[1]);
+        if constexpr (MP == 16) {
+          atomicAdd(sums + (2 * t) * MP + g + 8, d[2]);
+          atomicAdd(sums + (2 * t + 1) * MP + g + 8, d[3]);
         }
       }
     }
@@ -455,8 +505,20 @@ constexpr size_t GV_RED_MAX = 8 * 1024;  // shared memory for one round's sums; 
 
 // Activation rows the kernel variant for m carries (dp4a: m itself; mma: 8 or 16).
 inline int padded_m(int m) { return m <= 2 ? m : (m <= 8 ? 8 : 16); }
-inline int x_pitch(int k) { return ((k + 63) / 128) * 128 + 64; }
-inline size_t tile_bytes(int m) { return m <= 2 ? 0 : (size_t)GV_WARPS * GV_G * GV_TILE_PITCH; }
+// k split: a warp takes 512 bytes of k; KS = 2^result warps (at most 8) share a group of 8 rows and cover a segment
+// of KS * 512 bytes, longer k is walked segment by segment; the other warps take further groups of the piece.
+inline int k_split_log2(int k) {
+  const int kseg = k < GV_KSEG ? k : GV_KSEG;
+  int s = 0;
+  while ((GV_KW << s) < kseg) ++s;  // 0..3
+  return s;
+}
+// Shared memory of the activation fragments (mma variant): k rounded up to whole segments, times the rows carried.
+inline size_t xfrag_bytes(int m, int k) {
+  if (m <= 2) return 0;
+  const int seg = GV_KW << k_split_log2(k);
+  return (size_t)((k + seg - 1) / seg) * seg * padded_m(m);
+}
 
 }  // namespace
 }  // namespace sklb
@@ -471,16 +533,14 @@ extern "C" int skl_b200_gemv_i8_supported(const skl_b200_gemm_args *g) {
   if ((g->k0 & 15) != 0 || g->k0 > (1u << 20) || g->n0 > (1u << 30)) return 0;
   if (!al16(g->a) || !al16(g->b)) return 0;
   if ((g->m0 > 1 && (g->rsa0 & 15) != 0) || (g->n0 > 1 && (g->csb0 & 15) != 0)) return 0;
-  // the activations, one round of sums and (mma variant) the warps' tiles must fit in shared memory
-  const int mp = padded_m((int)g->m0);
-  if ((g->m0 <= 2 ? 0 : (size_t)mp * x_pitch((int)g->k0)) + 2 * GV_RED_MAX + 64 + tile_bytes((int)g->m0) > GV_SMEM_MAX) return 0;
+  // the activation fragments (m >= 3) and one round of sums must fit in shared memory
+  if (xfrag_bytes((int)g->m0, (int)g->k0) + 2 * GV_RED_MAX + 64 > GV_SMEM_MAX) return 0;
   if (g->epilogue == SKL_EPI_INT && g->tc != SKL_DT_I32) return 0;
   if (g->epilogue == SKL_EPI_FLOAT && g->tc == SKL_DT_I32) return 0;
   return 1;
 }
 
 extern "C" int skl_b200_launch_gemv_i8(const skl_b200_gemm_args *g, uint32_t *dev_status, void *stream) {
-  (void)dev_status;  // no device-side waits in this kernel
   GemvParams p;
   p.x = (const int8_t *)g->a;
   p.w = (const int8_t *)g->b;
@@ -506,16 +566,11 @@ extern "C" int skl_b200_launch_gemv_i8(const skl_b200_gemm_args *g, uint32_t *de
   p.act_param = g->act_param;
   p.overlap = g->b_static ? 1 : 0;
 
-  // k split: a warp takes 512 bytes of k; KS warps (a power of two, at most 8) share a group of 8 rows and cover a
-  // segment of KS * 512 bytes, longer k is walked segment by segment; the other warps take further groups of the piece.
-  const int kseg = p.k < GV_KSEG ? p.k : GV_KSEG;
-  int ks_log2 = 0;
-  while ((GV_KW << ks_log2) < kseg) ++ks_log2;  // 0..3
+  const int ks_log2 = k_split_log2(p.k);
   const int KS = 1 << ks_log2;
   p.ksplit_log2 = ks_log2;
   p.nseg = (p.k + KS * GV_KW - 1) / (KS * GV_KW);
   p.piece_rows = GV_G * (GV_WARPS / KS);
-  p.xpitch = x_pitch(p.k);
   const int mp = padded_m(p.m);
 
   int grid = num_sms();
@@ -536,7 +591,7 @@ extern "C" int skl_b200_launch_gemv_i8(const skl_b200_gemm_args *g, uint32_t *de
   if (round < 1) round = 1;  // 256 rows x 16 activations: one piece fills 16 KiB
   if (round > p.layers) round = p.layers;
   p.round = round;
-  const size_t smem = (p.m <= 2 ? 0 : (size_t)mp * p.xpitch) + (size_t)round * p.piece_rows * (mp * 4 + 8) + 64 + tile_bytes(p.m);
+  const size_t smem = xfrag_bytes(p.m, p.k) + (size_t)round * p.piece_rows * (mp * 4 + 8) + 64;
   if (smem > GV_SMEM_MAX) return (int)cudaErrorInvalidValue;
 
   cudaStream_t s = (cudaStream_t)stream;
