@@ -304,6 +304,25 @@ def make_workloads(torch, S, lib):
             return call, 2.0 * m * n * k, "tflops8", 10
         return build
 
+    def int8_packed_te(out_blocked):
+        def build():
+            # the matrix-engine packed entry point on operands packed ahead of time: A in TE x 1 panels (element (i, kk)
+            # at (i / TE) * TE * K + kk * TE + i % TE), B in 1 x TE panels, C in TE x TE blocks (or row-major when
+            # not out_blocked: rsc0 = N, csc0 = 1, blocks side by side); the kernel reads the panels in place
+            m = n = k = 4096
+            te = int(lib.skl_b200_te())
+            m1, n1 = m // te, n // te
+            a = torch.randint(-128, 128, (m * k,), dtype=torch.int8, device=dev, generator=g)
+            b = torch.randint(-128, 128, (k * n,), dtype=torch.int8, device=dev, generator=g)
+            c = torch.empty((m * n,), dtype=torch.int32, device=dev)
+            cstr = (te, 1, n1 * te * te, te * te) if out_blocked else (n, 1, te * n, te)
+
+            def call():
+                lib.skl_gemm_i8rcptex1c_i8rcp1xte_i32rcptexterc_sm100a(m1, n1, k, 1, a.data_ptr(), te * k, te, b.data_ptr(),
+                                                                       te, te * k, 0, c.data_ptr(), *cstr)
+            return call, 2.0 * m * n * k, "tflops8", 20
+        return build
+
     def fp8(ta):
         def build():
             # config 3 as configured: fp32 N(0,1) operands narrowed by the library's saturating cvt with the
@@ -421,7 +440,9 @@ def make_workloads(torch, S, lib):
 
     W["int8_8192_i32out"] = int8_8192
     W["c5_static_weights"] = c5_static
-    W["int8_4096_packed_i32out"] = int8_packed(False)
+    W["int8_4096_packed_i32out"] = int8_packed_te(True)
+    W["int8_4096_packed_rowmajor_i32out"] = int8_packed_te(False)
+    W["int8_4096_packed_16x16x8_i32out"] = int8_packed(False)
     W["int8_1024_packed_i32out_simt_kernel"] = int8_packed(True)
     W["fp8_e4m3xe4m3_8192_bf16out"] = fp8(S.F8E4M3)
     W["fp8_e5m2xe4m3_8192_bf16out"] = fp8(S.F8E5M2)
