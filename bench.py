@@ -37,7 +37,7 @@ if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
 M_C5, K_C5, N_C5 = 16384, 4096, 14336
-C5_DRAM_BYTES_PER_LAUNCH_1GPU = 697.0e6 + 452.0e6
+C5_DRAM_BYTES_PER_LAUNCH_1GPU = 625.3e6 + 456.4e6  # dram__bytes_read + dram__bytes_write, one launch of this build
 
 
 def measured_peaks():
