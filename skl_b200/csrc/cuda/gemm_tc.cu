@@ -92,6 +92,12 @@ struct TcParams {
   uint32_t *status;
   uint64_t wait_ns;  // bound of every mbarrier wait
   int skip_loads;    // testing aid: the producer announces its loads but never issues them
+  // One-CTA kernel, k-major A: rows of A per tile (<= 128).  Fewer than 128 when that makes the number of tiles a
+  // whole number of rounds of the grid (a tall-skinny problem is a stream of A, so every SM must have a tile): the
+  // TMA box holds bm_rows rows, the MMA still reads 128 (the accumulator lanes past bm_rows hold garbage that the
+  // epilogue never stores).
+  int bm_rows;
+  uint32_t a_tx;     // bytes of A per stage = bm_rows * 128
 };
 
 // ------------------------------------------------------------------ PTX wrappers
@@ -283,7 +289,7 @@ __device__ __forceinline__ bool get_unit(const TcParams &p, int it, TileUnit &u)
   int mi, ni;
   if (t < p.main_tiles) {
     tile_coords(t, p.tiles_m, p.tiles_n, p.raster_gm, mi, ni);
-    u.m0 = mi * BM;
+    u.m0 = mi * p.bm_rows;
     u.n0 = ni * p.bn_main;
     u.ncols = p.bn_main;
     u.idesc = p.idesc;
@@ -293,7 +299,7 @@ __device__ __forceinline__ bool get_unit(const TcParams &p, int it, TileUnit &u)
     const int tt = p.main_tiles + (int)blockIdx.x / p.tail_split, sub = (int)blockIdx.x % p.tail_split;
     tile_coords(tt, p.tiles_m, p.tiles_n, p.raster_gm, mi, ni);
     u.ncols = p.bn_main / p.tail_split;
-    u.m0 = mi * BM;
+    u.m0 = mi * p.bm_rows;
     u.n0 = ni * p.bn_main + sub * u.ncols;
     u.idesc = p.idesc_tail;
     return true;
@@ -733,7 +739,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         const int m0 = u.m0, n0 = u.n0;
         // a tail strip loads only its own columns of B: a narrower box (k-major, through tmBs) or fewer boxes
         const bool strip = u.ncols != p.bn_main;
-        const uint32_t stage_tx = Cfg::A_BYTES + (strip ? p.tail_b_bytes : p.main_b_bytes);
+        const uint32_t stage_tx = p.a_tx + (strip ? p.tail_b_bytes : p.main_b_bytes);
         const int b_boxes = strip ? p.tail_b_atoms : p.main_b_atoms;
         // The k loop exists twice: plain operands (2-D maps, box coordinates known without arithmetic) and panelled ones
         // (3-D maps).  The producer thread issues up to five loads per stage and is close to being the bottleneck for
@@ -853,9 +859,10 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
     for (int it = 0; get_unit<BN>(p, it, u); ++it) {
       const int m0 = u.m0, n0 = u.n0;
       const int row = m0 + quad * 32 + lane;
+      const bool row_ok = quad * 32 + lane < p.bm_rows && row < p.M;
       EpiVectors<BN>::fill(p, cs, bs, n0, u.ncols, lane);
-      const float rs = (p.row_scale && row < p.M) ? __ldg(p.row_scale + row) : 1.0f;
-      const float row_bias = (p.bias && p.bias_per_row && row < p.M) ? __ldg(p.bias + row) : 0.0f;
+      const float rs = (p.row_scale && row_ok) ? __ldg(p.row_scale + row) : 1.0f;
+      const float row_bias = (p.bias && p.bias_per_row && row_ok) ? __ldg(p.bias + row) : 0.0f;
       if (!mbar_wait(tfull_bar + 8 * acc, acc_phase, abort_flag, p.status, ERR_WAIT_TMEM_FULL, p.wait_ns)) break;
       tc_fence_after();
       const uint32_t taddr = tmem_base + acc * BN + ((uint32_t)(quad * 32) << 16);
@@ -867,7 +874,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
           tmem_ld32(taddr + c0, r);
         else
           tmem_ld16(taddr + c0, r);
-        tile_max = fmaxf(tile_max, epilogue_chunk<KIND == KIND_I8, ACT>(p, r, row, row < p.M, n0 + c0,
+        tile_max = fmaxf(tile_max, epilogue_chunk<KIND == KIND_I8, ACT>(p, r, row, row_ok, n0 + c0,
                                                                         has_cs ? cs + c0 : nullptr,
                                                                         has_bs ? bs + c0 : nullptr, rs, row_bias, st, lane));
       }
@@ -1539,15 +1546,35 @@ extern "C" int skl_b200_launch_gemm_tc(const skl_b200_gemm_args *g, uint32_t *de
     }
   }
 
+  // Tall-skinny problems (the 16-column tile) are a stream of A: when the 128-row tiles make more than one round of
+  // the grid, shorten them so that their number fills whole rounds, e.g. 57344 rows = 448 tiles = 3.03 rounds of 148 SMs
+  // become 592 tiles of 97 rows = 4 rounds (measured 48.6 -> 42.6 us at 16 columns; 28672 rows 27.1 -> 24.6 us).  A
+  // single round gains nothing from it (14336 rows: 15.5 us with 112 tiles of 128 rows, 15.9 us with 148 of 97): there
+  // the time is the chain of a tile's 4 K / 128 k blocks, about 0.28 us each on the MMA thread, not the bandwidth.
+  int bm_rows = BM;
+  if (!pair && bn == 16 && !va.mn_major && !va.panel_form && !blocked_c) {
+    static const bool off = [] {
+      const char *e = getenv("SKL_B200_TC_SHORT_TILES");  // tuning override
+      return e && atoi(e) == 0;
+    }();
+    const int64_t tm = (M + BM - 1) / BM, tn = (N + bn_main - 1) / bn_main, sms = sm_count();
+    const int64_t rounds = (tm * tn + sms - 1) / sms, want_m = rounds * sms / tn;
+    if (!off && want_m > tm && tm * tn > sms) {
+      const int64_t r = (M + want_m - 1) / want_m;
+      if (r >= 32 && r < BM) bm_rows = (int)r;
+    }
+  }
   CUtensorMap tmA, tmB;
-  if (!make_map(&tmA, kind, g->ta, g->a, va, M, K, BM)) return (int)cudaErrorInvalidValue;
+  if (!make_map(&tmA, kind, g->ta, g->a, va, M, K, bm_rows)) return (int)cudaErrorInvalidValue;
   if (!make_map(&tmB, kind, g->tb, g->b, vb, N, K, pair ? bn / 2 : bn_main)) return (int)cudaErrorInvalidValue;
 
   TcParams p;
   p.M = (int)M;
   p.N = (int)N;
   p.K = (int)K;
-  p.tiles_m = (int)((M + tile_rows - 1) / tile_rows);
+  p.tiles_m = (int)((M + (pair ? tile_rows : bm_rows) - 1) / (pair ? tile_rows : bm_rows));
+  p.bm_rows = bm_rows;
+  p.a_tx = (uint32_t)bm_rows * SLAB_BYTES;
   p.tiles_n = (int)((N + bn_main - 1) / bn_main);
   p.bn_main = bn_main;
   const int bke = SLAB_BYTES / es;
@@ -1628,7 +1655,7 @@ extern "C" int skl_b200_launch_gemm_tc(const skl_b200_gemm_args *g, uint32_t *de
     const char *e = getenv("SKL_B200_TC_TMA_STORE");
     // The row length must be a whole number of 16-byte units: a store box that crosses the matrix edge inside
     // such a unit was observed to write the unit's remaining bytes.
-    if (!blocked_c && p.c_vec_ok && (N * cs) % 16 == 0 && !(e && atoi(e) == 0) &&
+    if (!blocked_c && bm_rows == BM && p.c_vec_ok && (N * cs) % 16 == 0 && !(e && atoi(e) == 0) &&
         make_c_map(&tmC, g->c, M, N, g->rsc0, cs))
       p.c_tma = 1;
   }

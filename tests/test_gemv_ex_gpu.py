@@ -15,7 +15,10 @@ P = orc._p
 def test_gemv_int32_bit_exact(skl, m):
     """Weights "[N][K]" (layout 'k'), activations row-major; int32 out with alpha/beta."""
     for (n, k, alpha, beta) in [(14336, 4096, 1, 0), (1000, 512, 2, 3), (5, 16, 1, 0), (257, 4096, 1, 1),
-                                (4099, 1024, 1, 0)]:
+                                (4099, 1024, 1, 0),
+                                # row counts whose 128-row tiles make a ragged last round of the grid: the
+                                # tensor-core route cuts shorter tiles (68 and 91 rows here)
+                                (5000, 512, 2, 3), (20000, 256, 1, 1), (40000, 128, 2, 0)]:
         # the dp4a streaming kernel, for every m it accepts
         used = check_gemm_rc(skl, H.I8, m, n, k, "rkr", alpha, beta, where="device", seed=m, path=S.PATH_GEMV)
         assert used == S.PATH_GEMV
