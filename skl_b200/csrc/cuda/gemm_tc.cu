@@ -44,6 +44,9 @@ namespace {
 constexpr int BM = 128;
 constexpr int SLAB_BYTES = 128;  // bytes of K per stage row = one swizzle atom
 constexpr int NUM_THREADS = 192;
+#ifndef TC_SKINNY_ISSUERS
+#define TC_SKINNY_ISSUERS 2
+#endif
 constexpr int KIND_F16 = 0, KIND_F8 = 1, KIND_I8 = 2;
 constexpr int PLAIN_PANEL = 0x7fffffff;  // TcParams::a_panel / b_panel of a plain (unpanelled) MN-major matrix
 
@@ -471,7 +474,12 @@ struct TcConfig {
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int STAGES_RAW = (220 * 1024) / STAGE_BYTES;
   static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
-  static constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;
+  // The 16-column tile (tall-skinny problems) has ISSUERS threads issuing MMAs, each for every ISSUERS-th k block
+  // and into its own accumulator, which the epilogue adds up (see the MMA issuer's comment).
+  static constexpr int ISSUERS = BN == 16 ? TC_SKINNY_ISSUERS : 1;
+  static constexpr int THREADS = NUM_THREADS + 32 * (ISSUERS - 1);
+  static constexpr int ACC_COLS = BN * ISSUERS;
+  static constexpr int TMEM_COLS = 2 * ACC_COLS < 32 ? 32 : 2 * ACC_COLS;
   static constexpr int SMEM_BYTES =
       STAGES * STAGE_BYTES + 1024 /*align*/ + 4 * EPI_STAGE_BYTES + 256 /*barriers*/ + EpiVectors<BN>::BYTES;
   static_assert(SMEM_BYTES <= 227 * 1024, "exceeds the shared memory one CTA can have");
@@ -669,7 +677,7 @@ __device__ __forceinline__ float epilogue_chunk(const TcParams &p, const uint32_
 
 // ------------------------------------------------------------------ the kernel
 template <int BN, int KIND, bool ACT>
-__global__ void __launch_bounds__(NUM_THREADS, 1)
+__global__ void __launch_bounds__(TcConfig<BN>::THREADS, 1)
     gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                    const __grid_constant__ CUtensorMap tmBs, const __grid_constant__ CUtensorMap tmC,
                    const TcParams p) {
@@ -703,7 +711,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
       mbar_init(empty_bar + 8 * s, 1);
     }
     for (int b = 0; b < 2; ++b) {
-      mbar_init(tfull_bar + 8 * b, 1);
+      mbar_init(tfull_bar + 8 * b, Cfg::ISSUERS);
       mbar_init(tempty_bar + 8 * b, 128);
     }
     *abort_flag = 0u;
@@ -807,9 +815,14 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         }
       }
     }
-  } else if (warp == 1) {
-    // ---------------------------------------------------------------- MMA issuer
+  } else if (warp == 1 || warp >= 6) {
+    // ---------------------------------------------------------------- MMA issuer(s)
+    // One thread issues all MMAs, except for the 16-column tile: there a k block's 4 MMAs take the issuing thread
+    // about 0.28 us whatever the width, which bounds a tall-skinny problem (a stream of A) well below the memory
+    // rate.  So warps 6.. each hold one more issuing thread; issuer i takes the k blocks with kb % ISSUERS == i and
+    // accumulates into its own columns.  A stage is read by exactly one issuer, whose commit hands it back.
     if (lane == 0) {
+      const int me = warp == 1 ? 0 : warp - 5;
       int stage = 0;
       uint32_t phase = 0, acc = 0, acc_phase = 0;
       bool ok = true;
@@ -822,20 +835,22 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         if (!mbar_wait(tempty_bar + 8 * acc, acc_phase ^ 1u, abort_flag, p.status, ERR_WAIT_TMEM_EMPTY, p.wait_ns))
           break;
         tc_fence_after();
-        const uint32_t d_tmem = tmem_base + acc * BN;
+        const uint32_t d_tmem = tmem_base + acc * Cfg::ACC_COLS + (uint32_t)(me * BN);
         for (int kb = 0; kb < p.num_kb; ++kb) {
-          if (!mbar_wait(full_bar + 8 * stage, phase, abort_flag, p.status, ERR_WAIT_FULL, p.wait_ns)) {
-            ok = false;
-            break;
-          }
-          tc_fence_after();
-          const uint32_t sa = tiles + stage * Cfg::STAGE_BYTES, sb = sa + Cfg::A_BYTES;
-          const uint64_t da = make_smem_desc(sa, a_lbo, 1024), db = make_smem_desc(sb, b_lbo, 1024);
+          if (Cfg::ISSUERS == 1 || kb % Cfg::ISSUERS == me) {
+            if (!mbar_wait(full_bar + 8 * stage, phase, abort_flag, p.status, ERR_WAIT_FULL, p.wait_ns)) {
+              ok = false;
+              break;
+            }
+            tc_fence_after();
+            const uint32_t sa = tiles + stage * Cfg::STAGE_BYTES, sb = sa + Cfg::A_BYTES;
+            const uint64_t da = make_smem_desc(sa, a_lbo, 1024), db = make_smem_desc(sb, b_lbo, 1024);
 #pragma unroll
-          for (int k = 0; k < SLAB_BYTES / 32; ++k)
-            umma<KIND>(d_tmem, da + (uint64_t)(k * a_adv), db + (uint64_t)(k * b_adv), u.idesc,
-                       (uint32_t)((kb | k) != 0));
-          umma_commit(empty_bar + 8 * stage);
+            for (int k = 0; k < SLAB_BYTES / 32; ++k)
+              umma<KIND>(d_tmem, da + (uint64_t)(k * a_adv), db + (uint64_t)(k * b_adv), u.idesc,
+                         (uint32_t)((kb >= Cfg::ISSUERS) || k != 0));
+            umma_commit(empty_bar + 8 * stage);
+          }
           if (++stage == Cfg::STAGES) {
             stage = 0;
             phase ^= 1u;
@@ -865,15 +880,26 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
       const float row_bias = (p.bias && p.bias_per_row && row_ok) ? __ldg(p.bias + row) : 0.0f;
       if (!mbar_wait(tfull_bar + 8 * acc, acc_phase, abort_flag, p.status, ERR_WAIT_TMEM_FULL, p.wait_ns)) break;
       tc_fence_after();
-      const uint32_t taddr = tmem_base + acc * BN + ((uint32_t)(quad * 32) << 16);
+      const uint32_t taddr = tmem_base + acc * Cfg::ACC_COLS + ((uint32_t)(quad * 32) << 16);
 #pragma unroll 1
       for (int c0 = 0; c0 < u.ncols; c0 += 32) {
         if (n0 + c0 >= p.N) break;  // uniform across the warp
         uint32_t r[32];
-        if (BN >= 32)
+        if (BN >= 32) {
           tmem_ld32(taddr + c0, r);
-        else
+        } else {
           tmem_ld16(taddr + c0, r);
+          // add the other issuers' partial sums (exact for int32); an issuer that had no k block left its columns unwritten
+#pragma unroll 1
+          for (int a = 1; a < Cfg::ISSUERS && a < p.num_kb; ++a) {
+            uint32_t r2[32];
+            tmem_ld16(taddr + (uint32_t)(a * BN) + c0, r2);
+#pragma unroll
+            for (int i = 0; i < 16; ++i)
+              r[i] = KIND == KIND_I8 ? r[i] + r2[i]
+                                     : __float_as_uint(__fadd_rn(__uint_as_float(r[i]), __uint_as_float(r2[i])));
+          }
+        }
         tile_max = fmaxf(tile_max, epilogue_chunk<KIND == KIND_I8, ACT>(p, r, row, row_ok, n0 + c0,
                                                                         has_cs ? cs + c0 : nullptr,
                                                                         has_bs ? bs + c0 : nullptr, rs, row_bias, st, lane));
@@ -1359,7 +1385,7 @@ int launch_cfg_act(const CUtensorMap &ta, const CUtensorMap &tb, const CUtensorM
   if (grid > sm_count()) grid = sm_count();
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)grid);
-  cfg.blockDim = dim3(NUM_THREADS);
+  cfg.blockDim = dim3(Cfg::THREADS);
   cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
   cfg.stream = s;
   cudaLaunchAttribute attr[1];
