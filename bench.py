@@ -323,6 +323,21 @@ def make_workloads(torch, S, lib):
             return call, 2.0 * m * n * k, "tflops8", 20
         return build
 
+    def mxf4():
+        # block-scaled E2M1 operands (one E8M0 scale per 32 k), uniform random codes, scales 2^-4 .. 2^4; one call =
+        # two widening passes to bf16 + the bf16 tensor-core GEMM
+        m = n = k = 8192
+        a = torch.randint(0, 256, (m, k // 2), dtype=torch.uint8, device=dev, generator=g)
+        b = torch.randint(0, 256, (n, k // 2), dtype=torch.uint8, device=dev, generator=g)
+        sa = torch.randint(123, 132, (m, k // 32), dtype=torch.uint8, device=dev, generator=g)
+        sb = torch.randint(123, 132, (n, k // 32), dtype=torch.uint8, device=dev, generator=g)
+        c = torch.empty((m, n), dtype=torch.float32, device=dev)
+
+        def call():
+            lib.skl_gemm_mxf4e2m1_mxf4e2m1_f32_sm100a(m, n, k, 1.0, a.data_ptr(), k // 2, sa.data_ptr(), k // 32, b.data_ptr(),
+                                                      k // 2, sb.data_ptr(), k // 32, 0.0, c.data_ptr(), n)
+        return call, 2.0 * m * n * k, "tflops", 10
+
     def fp8(ta):
         def build():
             # config 3 as configured: fp32 N(0,1) operands narrowed by the library's saturating cvt with the
@@ -446,6 +461,7 @@ def make_workloads(torch, S, lib):
     W["int8_1024_packed_i32out_simt_kernel"] = int8_packed(True)
     W["fp8_e4m3xe4m3_8192_bf16out"] = fp8(S.F8E4M3)
     W["fp8_e5m2xe4m3_8192_bf16out"] = fp8(S.F8E5M2)
+    W["mxf4_8192_f32out_via_bf16"] = mxf4
     W["bf16_4096_bf16out"] = half(torch.bfloat16, S.BF16)
     W["fp16_4096_fp16out"] = half(torch.float16, S.F16)
     W["bf16_4096_kmajor_randn"] = bf16_pair(4096, 4096, 4096, False)

@@ -267,6 +267,21 @@ SKL_FUNC void skl_gemm_f32rcptex1c_f32rcp1xte_f32rcptexterc_sm100a(
     size_t m1, size_t n1, size_t k, float alpha, const float *a, size_t rsa1, size_t csa1, const float *b,
     size_t rsb1, size_t csb1, float beta, float *c, size_t rsc0, size_t csc0, size_t rsc1, size_t csc1);
 
+/* ------------------------------------------------------------------ GEMM, OCP MX-FP4 operands (no SKL counterpart)
+ * SKL stops at the conversion of E2M1 to E4M3 (src/cvt/cvt_f4_f8_zvfofp4min.c:15-41, ref/cvt/cvt_ofp4.c:18-72); this
+ * entry multiplies block-scaled E2M1 matrices.  Element (i, kk) of A is the E2M1 value of nibble kk of row i (two per
+ * byte, low nibble first, as in SKL's cvt; row i starts at a + i*rsa bytes) times 2^(sa[i*rssa + kk/32] - 127): one
+ * E8M0 scale byte per 32 consecutive k, 255 meaning NaN (OCP Microscaling Formats v1.0).  B is given one output column
+ * per row of k ("[N][K]"): column j starts at b + j*csb bytes, its scales at sb + j*cssb.  k must be a multiple of 32.
+ *     C[i, j] = beta * C[i, j] + alpha * sum_k A[i, k] * B[k, j]      (C row-major fp32, row stride rsc elements)
+ * with SKL's float-GEMM conventions: products and sum in fp32 (ref/gemm/gemm_bf16rc_bf16rc_f32rc.c:9-24 with the
+ * scaled elements as operands).  Both operands are widened exactly to bf16 and run on the bf16 tensor-core kernel; the
+ * hardware's block-scaled MMA kinds are not used.  Results are within the forward bound of the reference's GEMM tests. */
+SKL_FUNC void skl_gemm_mxf4e2m1_mxf4e2m1_f32_sm100a(size_t m, size_t n, size_t k, float alpha, const uint8_t *a,
+                                                    size_t rsa, const uint8_t *sa, size_t rssa, const uint8_t *b,
+                                                    size_t csb, const uint8_t *sb, size_t cssb, float beta, float *c,
+                                                    size_t rsc);
+
 /* ------------------------------------------------------------------ GEMM, int8 with 4-deep k blocks
  * Same parameter list as skl_gemm_i8rcp1x4_i8p4x1c_i32_xsfvqdotq
  * (src/gemm/gemm_i8rcp1x4_i8p4x1c_i32_xsfvqdotq.h:70-75): A in 1 x 4 blocks (element (i, k) at

@@ -73,6 +73,9 @@ def port():
         lib.orc_cvt_bf16_f8.argtypes = [_VP, _VP, _F, _SZ, _I, _I]
         lib.orc_cvt_f8_bf16.argtypes = [_VP, _VP, _SZ, _I]
         lib.orc_cvt_f4e2m1_f8e4m3.argtypes = [_VP, _VP, _SZ]
+        lib.orc_mxf4_element.restype = _F
+        lib.orc_mxf4_element.argtypes = [C.c_uint8, C.c_uint8]
+        lib.orc_gemm_mxf4.argtypes = [_SZ, _SZ, _SZ, _F, _VP, _SZ, _VP, _SZ, _VP, _SZ, _VP, _SZ, _F, _VP, _SZ]
         lib.orc_gemm_i8_i32.argtypes = [_SZ, _SZ, _SZ, C.c_int32, _VP, _SZ, _SZ, _VP, _SZ, _SZ,
                                         C.c_int32, _VP, _SZ, _SZ]
         lib.orc_gemm_fp_f32.argtypes = [_SZ, _SZ, _SZ, _F, _I, _VP, _SZ, _SZ, _I, _VP, _SZ, _SZ, _F,

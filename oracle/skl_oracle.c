@@ -595,3 +595,49 @@ void orc_transpose(size_t esize, size_t m, size_t n, const void *a, size_t rsa, 
     }
   }
 }
+
+/* ------------------------------------------------------------------ MX-FP4 GEMM (no reference routine)
+ * Restates the published format (OCP Microscaling Formats v1.0: E2M1 elements, one E8M0 scale 2^(s - 127) per 32
+ * consecutive k, s = 255 meaning NaN) on top of the reference's E2M1 value table (ref/cvt/cvt_ofp4.c:18-60) and the
+ * reference's float GEMM loop (ref/gemm/gemm_bf16rc_bf16rc_f32rc.c:9-24): fp32 products of the scaled elements, one fp32
+ * accumulator, k ascending, c = beta * c + alpha * acc.  Parity of the GEMM itself is unpinned (the reference has no
+ * such routine); the element decode is pinned through orc_f4e2m1_to_f8e4m3 / orc_f8e4m3_to_f32. */
+float orc_mxf4_element(uint8_t nibble, uint8_t scale) {
+  volatile float v = orc_f8e4m3_to_f32(orc_f4e2m1_to_f8e4m3(nibble & 0xFu));
+  volatile float f;
+  if (scale == 255u) {
+    union { uint32_t u; float f; } nan = {0x7FC00000u};
+    f = nan.f;
+  } else {
+    union { uint32_t u; float f; } p2 = {scale == 0u ? 0x00400000u : (uint32_t)scale << 23};
+    f = p2.f;
+  }
+  volatile float r = v * f;
+  return r;
+}
+
+void orc_gemm_mxf4(size_t m, size_t n, size_t k, float alpha, const uint8_t *a, size_t rsa, const uint8_t *sa,
+                   size_t rssa, const uint8_t *b, size_t csb, const uint8_t *sb, size_t cssb, float beta, float *c,
+                   size_t rsc) {
+  for (size_t i = 0; i < m; ++i) {
+    for (size_t j = 0; j < n; ++j) {
+      float acc = 0.0f;
+      for (size_t kk = 0; kk < k; ++kk) {
+        const uint8_t ab = a[i * rsa + kk / 2], bb = b[j * csb + kk / 2];
+        const float av = orc_mxf4_element((kk & 1u) ? (uint8_t)(ab >> 4) : (uint8_t)(ab & 0xFu), sa[i * rssa + kk / 32]);
+        const float bv = orc_mxf4_element((kk & 1u) ? (uint8_t)(bb >> 4) : (uint8_t)(bb & 0xFu), sb[j * cssb + kk / 32]);
+        volatile float prod = av * bv;
+        acc += prod;
+      }
+      volatile float scaled = alpha * acc;
+      float *cp = c + i * rsc + j;
+      if (beta == 0.0f) {
+        *cp = scaled;
+      } else {
+        volatile float old = beta * *cp;
+        *cp = old + scaled;
+      }
+    }
+  }
+}
+

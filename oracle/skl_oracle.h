@@ -137,4 +137,10 @@ void orc_transpose(size_t esize, size_t m, size_t n, const void *a, size_t rsa, 
 #ifdef __cplusplus
 }
 #endif
+/* MX-FP4 (OCP Microscaling v1.0) on the reference's E2M1 table and float-GEMM loop; no reference routine exists */
+float orc_mxf4_element(uint8_t nibble, uint8_t scale);
+void orc_gemm_mxf4(size_t m, size_t n, size_t k, float alpha, const uint8_t *a, size_t rsa, const uint8_t *sa,
+                   size_t rssa, const uint8_t *b, size_t csb, const uint8_t *sb, size_t cssb, float beta, float *c,
+                   size_t rsc);
+
 #endif /* SKL_ORACLE_H */

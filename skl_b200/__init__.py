@@ -68,6 +68,7 @@ SIGNATURES = {
     "skl_gemm_f8e4m3c_f8e4m3_f32_sm100a": (_GEMM_R_F, None),
     "skl_gemm_f8e5m2c_f8e5m2_f32_sm100a": (_GEMM_R_F, None),
     "skl_b200_te": ([], _SZ),
+    "skl_gemm_mxf4e2m1_mxf4e2m1_f32_sm100a": ([_SZ, _SZ, _SZ, _F, _VP, _SZ, _VP, _SZ, _VP, _SZ, _VP, _SZ, _F, _VP, _SZ], None),
     "skl_gemm_i8rcptex1c_i8rcp1xte_i32rcptexterc_sm100a": (_GEMM_TE_I, None),
     "skl_gemm_bf16rcptex1c_bf16rcp1xte_f32rcptexterc_sm100a": (_GEMM_TE_F, None),
     "skl_gemm_f16rcptex1c_f16rcp1xte_f32rcptexterc_sm100a": (_GEMM_TE_F, None),

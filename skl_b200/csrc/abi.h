@@ -111,6 +111,9 @@ int skl_b200_launch_cvt_f8_to_bf16(void *dst, const void *src, int src_fmt, size
 int skl_b200_launch_cvt_f8_to_bf16_2d(void *dst, size_t ld_dst, const void *src, size_t ld_src,
                                       int src_fmt, size_t rows, size_t cols, void *stream);
 int skl_b200_launch_cvt_f4_to_f8e4m3(void *dst, const void *src, size_t n, void *stream);
+/* MX-FP4 rows (16 bytes + one E8M0 scale per block of 32 elements) -> bf16 rows; ld_* in elements of dst / bytes of src / scale bytes */
+int skl_b200_launch_cvt_mxf4_to_bf16(void *dst, size_t ld_dst, const void *src, size_t ld_src, const void *scales,
+                                     size_t ld_scales, size_t rows, size_t kblocks, void *stream);
 /* Device-side self check: counts inputs in [first, first+count) (fp32 bit patterns) for which the
  * hardware-assisted encoder and the integer encoder disagree; *mismatches is a device uint64. */
 /* dst[c][r] = widen(src[r][c]): rows x cols fp8 (unit stride along cols) into cols x rows bf16 (unit stride along

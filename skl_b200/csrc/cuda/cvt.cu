@@ -406,6 +406,58 @@ extern "C" int skl_b200_launch_cvt_f8_to_bf16_2d_transposed(void *dst, size_t ld
   return (int)cudaGetLastError();
 }
 
+// OCP MX-FP4 -> bf16: element = E2M1 value (ref/cvt/cvt_ofp4.c:18-60) x 2^(scale - 127), one E8M0 scale byte per 32
+// consecutive k (scale 255 = NaN).  The result has at most 2 significant bits and bf16 has fp32's exponent range, so
+// the widening is exact wherever the fp32 product is.  One thread per block of 32 elements: 16 bytes in, 64 out.
+__global__ void __launch_bounds__(CVT_THREADS)
+    cvt_mxf4_to_bf16_kernel(uint16_t *__restrict__ dst, size_t ld_dst, const uint8_t *__restrict__ src, size_t ld_src,
+                            const uint8_t *__restrict__ scales, size_t ld_scales, uint32_t rows, uint32_t kblocks) {
+  const uint64_t total = (uint64_t)rows * kblocks, stride = (uint64_t)gridDim.x * blockDim.x;
+  for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const uint32_t r = (uint32_t)(i / kblocks), kb = (uint32_t)(i - (uint64_t)r * kblocks);
+    const uint8_t *sp = src + (size_t)r * ld_src + (size_t)kb * 16;
+    const uint32_t sc = scales[(size_t)r * ld_scales + kb];
+    // 2^(sc - 127) as fp32 bits: sc = 0 is the subnormal 2^-127, sc = 255 NaN
+    const float f = sc == 255u ? __uint_as_float(0x7FC00000u) : (sc == 0u ? __uint_as_float(0x00400000u) : __uint_as_float(sc << 23));
+    uint32_t w[4];
+    if ((reinterpret_cast<uintptr_t>(sp) & 15u) == 0) {
+      const uint4 v = *reinterpret_cast<const uint4 *>(sp);
+      w[0] = v.x; w[1] = v.y; w[2] = v.z; w[3] = v.w;
+    } else {
+#pragma unroll
+      for (int q = 0; q < 4; ++q) w[q] = sp[4 * q] | (sp[4 * q + 1] << 8) | (sp[4 * q + 2] << 16) | ((uint32_t)sp[4 * q + 3] << 24);
+    }
+    uint16_t *dp = dst + (size_t)r * ld_dst + (size_t)kb * 32;
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+#pragma unroll
+      for (int e = 0; e < 8; e += 2) {  // nibbles low first
+        const uint32_t n0 = (w[q] >> (4 * e)) & 0xFu, n1 = (w[q] >> (4 * e + 4)) & 0xFu;
+        // magnitudes 0, .5, 1, 1.5, 2, 3, 4, 6 as bf16 bit patterns of the fp32 value's upper half
+        const uint64_t lut_lo = 0x3FC03F803F000000ull, lut_hi = 0x40C0408040404000ull;
+        auto val = [&](uint32_t nib) {
+          const uint32_t m = nib & 7u;
+          const uint32_t hi16 = (uint32_t)((m < 4 ? lut_lo >> (16 * m) : lut_hi >> (16 * (m - 4))) & 0xFFFFu);
+          const float x = __uint_as_float((hi16 << 16) | ((nib & 8u) << 28));
+          return __float_as_uint(__fmul_rn(x, f)) >> 16;  // exact: the low 16 bits of the product are zero
+        };
+        const uint32_t pair = val(n0) | (val(n1) << 16);
+        *reinterpret_cast<uint32_t *>(dp + 8 * q + e) = pair;
+      }
+    }
+  }
+}
+
+extern "C" int skl_b200_launch_cvt_mxf4_to_bf16(void *dst, size_t ld_dst, const void *src, size_t ld_src, const void *scales,
+                                                size_t ld_scales, size_t rows, size_t kblocks, void *stream) {
+  if (rows == 0 || kblocks == 0) return 0;
+  cvt_mxf4_to_bf16_kernel<<<cvt_grid(rows * kblocks, 1), CVT_THREADS, 0, (cudaStream_t)stream>>>(
+      (uint16_t *)dst, ld_dst, (const uint8_t *)src, ld_src, (const uint8_t *)scales, ld_scales, (uint32_t)rows,
+      (uint32_t)kblocks);
+  SKLB_COUNT_LAUNCH();
+  return (int)cudaGetLastError();
+}
+
 extern "C" int skl_b200_launch_cvt_f4_to_f8e4m3(void *dst, const void *src, size_t n, void *stream) {
   if (n == 0) return 0;
   cvt_f4_to_f8_kernel<<<cvt_grid(n, 1), CVT_THREADS, 0, (cudaStream_t)stream>>>(

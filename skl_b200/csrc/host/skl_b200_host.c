@@ -1188,6 +1188,52 @@ void skl_cvt_f4e2m1_f8e4m3_sm100a(uint8_t *pDst, const uint8_t *pSrc, size_t n) 
   run_cvt_widen(pDst, pSrc, 1, 0, n);
 }
 
+/* ------------------------------------------------------------------ MX-FP4 GEMM (block-scaled E2M1) */
+
+/* Both operands are widened exactly to bf16 (element x 2^(scale - 127)) into workspaces and multiplied by the bf16
+ * tensor-core path with fp32 accumulation. */
+void skl_gemm_mxf4e2m1_mxf4e2m1_f32_sm100a(size_t m, size_t n, size_t k, float alpha, const uint8_t *a, size_t rsa,
+                                           const uint8_t *sa, size_t rssa, const uint8_t *b, size_t csb,
+                                           const uint8_t *sb, size_t cssb, float beta, float *c, size_t rsc) {
+  if (!begin_call()) return;
+  do {
+    if ((k & 31u) != 0 || rsa < k / 2 || csb < k / 2 || rssa < k / 32 || cssb < k / 32 || m >= (1ull << 31) ||
+        n >= (1ull << 31) || k >= (1ull << 31)) {
+      set_err(SKL_B200_ERR_INVALID_ARGUMENT);
+      break;
+    }
+    if (m == 0 || n == 0) break;
+    const size_t kb = k / 32;
+    void *wa = 0, *wb = 0;
+    if (k > 0) {
+      const void *da = a, *dsa = sa, *db = b, *dsb = sb;
+      if (!on_device(a)) da = stage_in(WS_A, a, (m - 1) * rsa + k / 2);
+      if (!on_device(sa)) dsa = stage_in(WS_ROW, sa, (m - 1) * rssa + kb);
+      if (!on_device(b)) db = stage_in(WS_B, b, (n - 1) * csb + k / 2);
+      if (!on_device(sb)) dsb = stage_in(WS_COL, sb, (n - 1) * cssb + kb);
+      if (!da || !dsa || !db || !dsb) break;
+      wa = workspace(WS_PLAIN_A, m * k * 2);
+      wb = wa ? workspace(WS_PLAIN_B, n * k * 2) : 0;
+      if (!wb) break;
+      if (!cuda_ok((cudaError_t)skl_b200_launch_cvt_mxf4_to_bf16(wa, k, da, rsa, dsa, rssa, m, kb, g_ctx.stream))) break;
+      if (!cuda_ok((cudaError_t)skl_b200_launch_cvt_mxf4_to_bf16(wb, k, db, csb, dsb, cssb, n, kb, g_ctx.stream))) break;
+    }
+    skl_b200_gemm_args g;
+    memset(&g, 0, sizeof g);
+    g.m0 = m; g.n0 = n; g.k0 = k;
+    g.m1 = 1; g.n1 = 1; g.k1 = 1;
+    g.ta = SKL_DT_BF16; g.tb = SKL_DT_BF16; g.tc = SKL_DT_F32;
+    g.epilogue = SKL_EPI_FLOAT;
+    g.a = wa; g.b = wb; g.c = c;
+    g.rsa0 = (int64_t)k; g.csa0 = 1;
+    g.rsb0 = 1; g.csb0 = (int64_t)k;
+    g.rsc0 = (int64_t)rsc; g.csc0 = 1;
+    g.alpha_f = alpha; g.beta_f = beta;
+    run_gemm_body(&g);
+  } while (0);
+  leave_call();
+}
+
 /* ------------------------------------------------------------------ pack / unpack / transpose */
 
 /* op: 0 pack, 1 unpack, 2 transpose.  `plain` is the 2-D side, `blk` the blocked side. */

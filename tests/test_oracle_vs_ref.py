@@ -234,3 +234,19 @@ def test_fp8_encoders_against_the_reference_on_a_sample_of_all_inputs():
     assert out.returncode == 0, out.stdout + out.stderr
     assert "decode mismatches: 0" in out.stdout
     assert "flavours: 0" in out.stdout
+
+
+def test_mxf4_element_decode_is_the_reference_f4_table_times_a_power_of_two():
+    """The MX-FP4 GEMM has no reference routine; its element decode is pinned: E2M1 value = the reference's
+    skl_cvt_f4e2m1_f8e4m3 followed by its E4M3 decode (ref/cvt/cvt_ofp4.c:18-72, cvt_ofp8.c:18-52), scale = 2^(s - 127)."""
+    ref, port = orc.ref(), orc.port()
+    src = np.array([lo | (hi << 4) for lo, hi in zip(range(0, 16, 2), range(1, 16, 2))], np.uint8)
+    f8 = np.zeros(16, np.uint8)
+    ref.skl_cvt_f4e2m1_f8e4m3_ref(P(f8), P(src), 16)
+    for code in range(16):
+        base = port.orc_f8e4m3_to_f32(int(f8[code]))
+        for s in (0, 1, 100, 127, 128, 200, 254):
+            want = np.float32(base) * np.float32(2.0) ** np.float32(s - 127) if s else np.float32(base) * np.float32(2.0 ** -127)
+            got = np.float32(port.orc_mxf4_element(code, s))
+            assert got.view(np.uint32) == np.float32(want).view(np.uint32), (code, s)
+        assert np.isnan(port.orc_mxf4_element(code, 255))
