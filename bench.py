@@ -263,25 +263,27 @@ def make_workloads(torch, S, lib):
             lib.skl_gemm_i8_i8_i32_sm100a(m, n, k, 1, a.data_ptr(), k, b.data_ptr(), n, 0, c.data_ptr(), n)
         return call, 2.0 * m * n * k, "tflops8", 20
 
-    def c5_static():
-        # the headline shape and operand distributions (X ~ N(0,1); W ~ N(0, 0.02) quantised per column with scale
-        # amax/448) with the weights declared static: W is widened by the first call only
-        m, k, n = M_C5, K_C5, N_C5
-        x = (torch.randn((m, k), device=dev, generator=g)).to(torch.bfloat16)
-        w32 = torch.randn((k, n), device=dev, generator=g) * 0.02
-        sc = (w32.abs().amax(dim=0) / 448.0).clamp_min(1e-30).contiguous()
-        w32 /= sc[None, :]
-        w = torch.empty((k, n), dtype=torch.uint8, device=dev)
-        lib.skl_cvt_sat_f32_f8e4m3_sm100a(w.data_ptr(), w32.data_ptr(), 1.0, k * n)
-        del w32
-        c = torch.empty((m, n), dtype=torch.bfloat16, device=dev)
+    def c5_like(parts, static):
+        def build():
+            # the headline shape and operand distributions (X ~ N(0,1); W ~ N(0, 0.02) quantised per column with scale
+            # amax/448); static: the weights are declared static, so W is widened by the first call only
+            m, k, n = M_C5, K_C5, N_C5 // parts  # one rank's column shard when parts > 1
+            x = (torch.randn((m, k), device=dev, generator=g)).to(torch.bfloat16)
+            w32 = torch.randn((k, n), device=dev, generator=g) * 0.02
+            sc = (w32.abs().amax(dim=0) / 448.0).clamp_min(1e-30).contiguous()
+            w32 /= sc[None, :]
+            w = torch.empty((k, n), dtype=torch.uint8, device=dev)
+            lib.skl_cvt_sat_f32_f8e4m3_sm100a(w.data_ptr(), w32.data_ptr(), 1.0, k * n)
+            del w32
+            c = torch.empty((m, n), dtype=torch.bfloat16, device=dev)
 
-        def call():
-            lib.skl_b200_set_static_weights(1)
-            lib.skl_gemm_ex_sm100a(m, n, k, S.BF16, x.data_ptr(), k, 1, S.F8E4M3, w.data_ptr(), n, 1, 1.0, None,
-                                   sc.data_ptr(), 0.0, S.BF16, c.data_ptr(), n, 1)
-            lib.skl_b200_set_static_weights(0)
-        return call, 2.0 * m * n * k, "tflops", 20
+            def call():
+                lib.skl_b200_set_static_weights(1 if static else 0)
+                lib.skl_gemm_ex_sm100a(m, n, k, S.BF16, x.data_ptr(), k, 1, S.F8E4M3, w.data_ptr(), n, 1, 1.0, None,
+                                       sc.data_ptr(), 0.0, S.BF16, c.data_ptr(), n, 1)
+                lib.skl_b200_set_static_weights(0)
+            return call, 2.0 * m * n * k, "tflops", 20
+        return build
 
     def int8_packed(force_simt):
         def build():
@@ -454,7 +456,9 @@ def make_workloads(torch, S, lib):
         return call, 4.0 * m * n, "gbs", 10
 
     W["int8_8192_i32out"] = int8_8192
-    W["c5_static_weights"] = c5_static
+    W["c5_static_weights"] = c5_like(1, True)
+    # one rank's share of the 2- / 4- / 8-GPU runs on this GPU alone (widening pass included, nothing static)
+    W["c5_shard_of_2"], W["c5_shard_of_4"], W["c5_shard_of_8"] = c5_like(2, False), c5_like(4, False), c5_like(8, False)
     W["int8_4096_packed_i32out"] = int8_packed_te(True)
     W["int8_4096_packed_rowmajor_i32out"] = int8_packed_te(False)
     W["int8_4096_packed_16x16x8_i32out"] = int8_packed(False)
