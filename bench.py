@@ -588,7 +588,8 @@ def main() -> None:
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: the library has no CPU path")
     torch.cuda.set_device(local_rank)
-    local_cpus = bind_to_gpu_cpus(local_rank) if world > 1 else None
+    all_cpus = os.sched_getaffinity(0)
+    local_cpus = bind_to_gpu_cpus(local_rank)  # pinned buffers get first-touched on the GPU's NUMA node
     dist = None
     if world > 1:
         import torch.distributed as dist_mod
@@ -767,7 +768,7 @@ def main() -> None:
     ms_e2e = float(t.item()) / e2e_steps
     e2e_value = flops_step / (ms_e2e * 1e-3) / 1e12
     same = bool(torch.equal(ch.cuda(), c))
-    phases = None
+    phases = {"cpus_bound_to": local_cpus} if local_cpus else None
     if gather_x:
         # device time of the last step's phases on this rank (max over ranks): upload of the rank's rows of X, the
         # all-gather of X over NVLink, the library call (upload of the W shard and scales, widening, row-chunk GEMM
@@ -821,6 +822,7 @@ def main() -> None:
         line["also"] = also_configs(torch, S, lib, peaks)
         lib.skl_b200_synchronize()
         lib.skl_b200_set_async(0)
+        os.sched_setaffinity(0, all_cpus)  # the CPU baseline uses every host core again
         threads = os.cpu_count() or 1
         tf, secs, rows, kind, rpt = cpu_reference_sample(None, 3.0, threads)
         line["cpu_baseline"] = {"value": tf, "unit": "TFLOP/s", "cores": threads, "kind": kind,
