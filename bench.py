@@ -239,7 +239,7 @@ def time_steps(torch, fn, steps: int, barrier=None):
 def make_workloads(torch, S, lib):
     """Named device-resident workloads besides c5: name -> builder returning (call, work, kind, reps).
 
-    kind "tflops" / "tflops8" (8-bit operands): work = operations per call; kind "gbs": work = algorithmic
+    kind "tflops" / "tflops8" (8-bit operands) / "tflops4" (4-bit operands): work = operations per call; kind "gbs": work = algorithmic
     bytes per call."""
     dev = "cuda"
     g = torch.Generator(device=dev)
@@ -327,7 +327,7 @@ def make_workloads(torch, S, lib):
 
     def mxf4():
         # block-scaled E2M1 operands (one E8M0 scale per 32 k), uniform random codes, scales 2^-4 .. 2^4; one call =
-        # two widening passes to bf16 + the bf16 tensor-core GEMM
+        # one launch of the kernel on the block-scaled tensor-core instruction
         m = n = k = 8192
         a = torch.randint(0, 256, (m, k // 2), dtype=torch.uint8, device=dev, generator=g)
         b = torch.randint(0, 256, (n, k // 2), dtype=torch.uint8, device=dev, generator=g)
@@ -338,7 +338,7 @@ def make_workloads(torch, S, lib):
         def call():
             lib.skl_gemm_mxf4e2m1_mxf4e2m1_f32_sm100a(m, n, k, 1.0, a.data_ptr(), k // 2, sa.data_ptr(), k // 32, b.data_ptr(),
                                                       k // 2, sb.data_ptr(), k // 32, 0.0, c.data_ptr(), n)
-        return call, 2.0 * m * n * k, "tflops", 10
+        return call, 2.0 * m * n * k, "tflops4", 10
 
     def fp8(ta):
         def build():
@@ -465,7 +465,7 @@ def make_workloads(torch, S, lib):
     W["int8_1024_packed_i32out_simt_kernel"] = int8_packed(True)
     W["fp8_e4m3xe4m3_8192_bf16out"] = fp8(S.F8E4M3)
     W["fp8_e5m2xe4m3_8192_bf16out"] = fp8(S.F8E5M2)
-    W["mxf4_8192_f32out_via_bf16"] = mxf4
+    W["mxf4_8192_f32out"] = mxf4
     W["bf16_4096_bf16out"] = half(torch.bfloat16, S.BF16)
     W["fp16_4096_fp16out"] = half(torch.float16, S.F16)
     W["bf16_4096_kmajor_randn"] = bf16_pair(4096, 4096, 4096, False)
@@ -525,12 +525,15 @@ def run_workload(torch, S, lib, peaks, build, warmup=3, reps=None):
     ms = time_steps(torch, call, reps) / reps
     lib.skl_b200_synchronize()
     S.check()
-    if kind in ("tflops", "tflops8"):
+    if kind in ("tflops", "tflops8", "tflops4"):
         tf = work / (ms * 1e-3) / 1e12
         out = {"tflops": round(tf, 1), "ms": round(ms, 4)}
         if kind == "tflops8":  # 8-bit operands: against the datasheet's dense peak and against twice the measured bf16 rate
             out["frac_of_4500_datasheet"] = round(tf / 4500.0, 3)
             out["frac_of_2x_measured_bf16_burst"] = round(tf / (2.0 * peaks["bf16_burst"]), 3)
+        elif kind == "tflops4":  # 4-bit operands: datasheet dense peak 9 P; four times the measured bf16 rate
+            out["frac_of_9000_datasheet"] = round(tf / 9000.0, 3)
+            out["frac_of_4x_measured_bf16_burst"] = round(tf / (4.0 * peaks["bf16_burst"]), 3)
         else:
             out["frac_of_measured_bf16_burst"] = round(tf / peaks["bf16_burst"], 3)
         return out

@@ -1159,6 +1159,212 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
   }
 }
 
+// ====================================================================== MX-FP4 (block-scaled E2M1) GEMM
+// C[m, n] (fp32, row-major) = beta * C + alpha * sum_k A[m, k] * B[n, k], A and B packed E2M1 (two per byte, k
+// contiguous) with one E8M0 scale per 32 consecutive k, on tcgen05.mma.kind::mxf4.block_scale (K = 64 per instruction,
+// two scales per row and instruction).  One 128 x 128 tile per CTA.  A stage holds 256 elements of k: a 128 x 128-byte
+// box of A and of B (TMA, 128-byte swizzle) and the stage's 8 scales per row of A and of B in the layout the
+// smem -> TMEM scale copy expects (per chunk of 4 scales: row r at (r % 32) * 16 + (r / 32) * 4; tcgen05.cp
+// 32x128b.warpx4 spreads it over the four lane quarters).  Warp 0 issues TMA, warp 1 the scale copies and MMAs,
+// warps 2..5 fetch the scales with plain loads during the main loop and run the epilogue afterwards.  The scale bytes
+// of an instruction are picked by the scale-factor id in the instruction descriptor (0 or 2 inside the 4-byte column).
+namespace mx {
+constexpr int BM = 128, BN = 128, STAGE_K_BYTES = 128, STAGES = 3;  // 3 stages: two CTAs fit on an SM
+constexpr int A_BYTES = BM * STAGE_K_BYTES, B_BYTES = BN * STAGE_K_BYTES, SF_BYTES = 2 * 512;
+constexpr int STAGE_BYTES = A_BYTES + B_BYTES + 2 * SF_BYTES;
+constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + 256;
+constexpr int THREADS = 192;
+constexpr uint32_t ERR_EMPTY = 0x301, ERR_FULL = 0x302, ERR_DONE = 0x303;
+
+struct Params {
+  const uint8_t *sa, *sb;  // scales, row i at sa + i * rssa
+  int64_t rssa, rssb;
+  float *c;
+  int64_t rsc;
+  int M, N, kblocks;       // kblocks = K / 32
+  float alpha, beta;
+  uint64_t wait_ns;
+  uint32_t *status;
+  int sf_vec;              // the scale rows are 8-byte aligned: a stage's 8 scales of a row are one load
+};
+
+// no-swizzle k-major descriptor of a 32-row x 16-byte scale chunk: 8-row groups 128 bytes apart
+__device__ __forceinline__ uint64_t sf_desc(uint32_t saddr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr >> 4) & 0x3FFFu);
+  d |= (uint64_t)(128u >> 4) << 32;
+  d |= 1ull << 46;
+  return d;
+}
+
+__global__ void __launch_bounds__(THREADS, 2)
+    gemm_mxf4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const Params p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t tiles = (raw + 1023u) & ~1023u;
+  const uint32_t bars = tiles + STAGES * STAGE_BYTES;
+  const uint32_t full_bar = bars, empty_bar = bars + 8 * STAGES, done_bar = bars + 16 * STAGES;
+  uint8_t *gen = smem_raw + (bars - raw);
+  volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(gen + 16 * STAGES + 16);
+  volatile uint32_t *abort_flag = tmem_slot + 1;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m0 = (int)blockIdx.y * BM, n0 = (int)blockIdx.x * BN;
+  const int num_kb = (p.kblocks + 7) / 8;  // stages of 256 elements
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full_bar + 8 * s, 1 + 4);  // the TMA thread's expect_tx arrival + one per scale-loading warp
+      mbar_init(empty_bar + 8 * s, 1);
+    }
+    mbar_init(done_bar, 1);
+    *abort_flag = 0u;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 256;" ::"r"(
+                     smem_u32((const void *)tmem_slot))
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      for (int kb = 0; kb < num_kb; ++kb) {
+        const int stage = kb % STAGES;
+        if (kb >= STAGES &&
+            !mbar_wait(empty_bar + 8 * stage, (uint32_t)(kb / STAGES - 1) & 1u, abort_flag, p.status, ERR_EMPTY, p.wait_ns))
+          break;
+        const uint32_t sa = tiles + stage * STAGE_BYTES, sb = sa + A_BYTES, fb = full_bar + 8 * stage;
+        mbar_expect_tx(fb, A_BYTES + B_BYTES);
+        tma_load_2d(sa, &tmA, fb, kb * STAGE_K_BYTES, m0);
+        tma_load_2d(sb, &tmB, fb, kb * STAGE_K_BYTES, n0);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      for (int kb = 0; kb < num_kb; ++kb) {
+        const int stage = kb % STAGES;
+        if (!mbar_wait(full_bar + 8 * stage, (uint32_t)(kb / STAGES) & 1u, abort_flag, p.status, ERR_FULL, p.wait_ns)) break;
+        tc_fence_after();
+        const uint32_t sa = tiles + stage * STAGE_BYTES, sb = sa + A_BYTES, sfa = sb + B_BYTES, sfb = sfa + SF_BYTES;
+        // scales of this stage -> TMEM columns 128.. (two regions used in turn): A chunks at +0, +4, B chunks at +8, +12
+        const uint32_t tsf = tmem_base + 128u + (uint32_t)(kb & 1) * 16u;
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(tsf + 4u * c), "l"(sf_desc(sfa + 512u * c)) : "memory");
+          asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(tsf + 8u + 4u * c), "l"(sf_desc(sfb + 512u * c)) : "memory");
+        }
+        const uint64_t da = make_smem_desc(sa, 16, 1024), db = make_smem_desc(sb, 16, 1024);
+        const int left = p.kblocks - kb * 8;               // scale blocks left from this stage on
+        const int mmas = left >= 8 ? 4 : (left + 1) / 2;   // 64 elements = 2 scale blocks per instruction
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          if (j < mmas) {
+            const uint32_t sf_id = (uint32_t)(j & 1) * 2u;
+            // E2M1 x E2M1, E8M0 scales, N = 128, M = 128, K = 64
+            const uint32_t idesc = (sf_id << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | (1u << 23) |
+                                   ((uint32_t)(BM >> 4) << 24) | (sf_id << 29);
+            const uint32_t acc = (uint32_t)((kb | j) != 0);
+            asm volatile(
+                "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                "tcgen05.mma.cta_group::1.kind::mxf4.block_scale.scale_vec::2X [%0], %1, %2, %3, [%5], [%6], p;\n\t}" ::"r"(
+                    tmem_base),
+                "l"(da + (uint64_t)(2 * j)), "l"(db + (uint64_t)(2 * j)), "r"(idesc), "r"(acc),
+                "r"(tsf + 4u * (uint32_t)(j >> 1)), "r"(tsf + 8u + 4u * (uint32_t)(j >> 1))
+                : "memory");
+          }
+        }
+        umma_commit(empty_bar + 8 * stage);
+      }
+      umma_commit(done_bar);
+    }
+  } else {
+    // ---- scale loaders, then epilogue.  Thread t of the 128 = row t of the tile (A) and column t (B).
+    const int quad = warp & 3, t = quad * 32 + lane;
+    const int row = m0 + t, col = n0 + t;
+    const uint32_t off = (uint32_t)((t & 31) * 16 + (t >> 5) * 4);
+    bool ok = true;
+    // the 8 scales of this thread's row of A and column of B for stage kb (1.0 where there is no row / no k)
+    auto fetch = [&](int kb, uint32_t (&wa)[2], uint32_t (&wb)[2]) {
+      wa[0] = wa[1] = wb[0] = wb[1] = 0x7F7F7F7Fu;
+      if (p.sf_vec && kb * 8 + 8 <= p.kblocks) {
+        if (row < p.M) {
+          const uint2 v = __ldg(reinterpret_cast<const uint2 *>(p.sa + (int64_t)row * p.rssa + kb * 8));
+          wa[0] = v.x;
+          wa[1] = v.y;
+        }
+        if (col < p.N) {
+          const uint2 v = __ldg(reinterpret_cast<const uint2 *>(p.sb + (int64_t)col * p.rssb + kb * 8));
+          wb[0] = v.x;
+          wb[1] = v.y;
+        }
+      } else {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          const int blk = kb * 8 + e;
+          if (blk < p.kblocks) {
+            const uint32_t sh = 8u * (uint32_t)(e & 3);
+            if (row < p.M) wa[e >> 2] = (wa[e >> 2] & ~(0xFFu << sh)) | ((uint32_t)__ldg(p.sa + (int64_t)row * p.rssa + blk) << sh);
+            if (col < p.N) wb[e >> 2] = (wb[e >> 2] & ~(0xFFu << sh)) | ((uint32_t)__ldg(p.sb + (int64_t)col * p.rssb + blk) << sh);
+          }
+        }
+      }
+    };
+    uint32_t wa[2], wb[2], na[2], nb[2];
+    if (num_kb > 0) fetch(0, wa, wb);
+    for (int kb = 0; kb < num_kb && ok; ++kb) {
+      const int stage = kb % STAGES;
+      if (kb + 1 < num_kb) fetch(kb + 1, na, nb);  // in flight while this stage's buffer is waited for
+      if (kb >= STAGES)
+        ok = mbar_wait(empty_bar + 8 * stage, (uint32_t)(kb / STAGES - 1) & 1u, abort_flag, p.status, ERR_EMPTY, p.wait_ns);
+      if (!ok) break;
+      const uint32_t sfa = tiles + stage * STAGE_BYTES + A_BYTES + B_BYTES, sfb = sfa + SF_BYTES;
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        asm volatile("st.shared.u32 [%0], %1;" ::"r"(sfa + 512u * c + off), "r"(wa[c]) : "memory");
+        asm volatile("st.shared.u32 [%0], %1;" ::"r"(sfb + 512u * c + off), "r"(wb[c]) : "memory");
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive(full_bar + 8 * stage);
+      wa[0] = na[0]; wa[1] = na[1]; wb[0] = nb[0]; wb[1] = nb[1];
+    }
+    if (ok && mbar_wait(done_bar, 0u, abort_flag, p.status, ERR_DONE, p.wait_ns)) {
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16);
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        uint32_t r[32];
+        tmem_ld32(taddr + c0, r);
+        if (row < p.M) {
+          float *cp = p.c + (int64_t)row * p.rsc + n0 + c0;
+#pragma unroll
+          for (int e = 0; e < 32; ++e) {
+            if (n0 + c0 + e < p.N) {
+              float v = __fmul_rn(p.alpha, __uint_as_float(r[e]));
+              if (p.beta != 0.0f) v = __fadd_rn(__fmul_rn(p.beta, cp[e]), v);
+              cp[e] = v;
+            }
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 256;" ::"r"(tmem_base) : "memory");
+  }
+}
+}  // namespace mx
+
+
 // ------------------------------------------------------------------ host side
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *,
@@ -1725,4 +1931,61 @@ extern "C" int skl_b200_launch_gemm_tc(const skl_b200_gemm_args *g, uint32_t *de
     return launch_cfg<64, KIND_F16>(tmA, tmB, tmBs, tmC, p, s);
   }
 #undef TC_DISPATCH
+}
+
+// ---- MX-FP4 on the block-scaled MMA: 16-byte aligned packed rows, k a positive multiple of 32
+extern "C" int skl_b200_gemm_mxf4_supported(const void *a, int64_t rsa, const void *b, int64_t csb, int64_t m, int64_t n,
+                                            int64_t k) {
+  if (m < 1 || n < 1 || k < 32 || (k & 31) != 0) return 0;
+  if (m >= (1ll << 31) - 256 || n >= (1ll << 31) - 256 || k >= (1ll << 31)) return 0;
+  if ((reinterpret_cast<uintptr_t>(a) & 15u) || (reinterpret_cast<uintptr_t>(b) & 15u)) return 0;
+  if ((m > 1 && (rsa & 15)) || (n > 1 && (csb & 15))) return 0;
+  return encode_fn() != nullptr;
+}
+
+extern "C" int skl_b200_launch_gemm_mxf4(const void *a, int64_t rsa, const void *sa, int64_t rssa, const void *b,
+                                         int64_t csb, const void *sb, int64_t cssb, float *c, int64_t rsc, int64_t m,
+                                         int64_t n, int64_t k, float alpha, float beta, uint32_t wait_limit_ms,
+                                         uint32_t *dev_status, void *stream) {
+  EncodeTiledFn enc = encode_fn();
+  if (!enc) return (int)cudaErrorNotSupported;
+  CUtensorMap tmA, tmB;
+  const cuuint32_t box[2] = {(cuuint32_t)mx::STAGE_K_BYTES, (cuuint32_t)mx::BM}, estr[2] = {1, 1};
+  for (int which = 0; which < 2; ++which) {
+    const cuuint64_t rows = (cuuint64_t)(which ? n : m);
+    cuuint64_t dims[2] = {(cuuint64_t)(k / 2), rows}, strides[1];
+    int64_t ld = which ? csb : rsa;
+    if (rows <= 1) ld = (k / 2 + 15) / 16 * 16;  // stride unused; keep it legal
+    strides[0] = (cuuint64_t)ld;
+    if (enc(which ? &tmB : &tmA, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(which ? b : a), dims, strides, box,
+            estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+      return (int)cudaErrorInvalidValue;
+  }
+  mx::Params p;
+  p.sa = (const uint8_t *)sa;
+  p.sb = (const uint8_t *)sb;
+  p.rssa = rssa;
+  p.rssb = cssb;
+  p.c = c;
+  p.rsc = rsc;
+  p.M = (int)m;
+  p.N = (int)n;
+  p.kblocks = (int)(k / 32);
+  p.alpha = alpha;
+  p.beta = beta;
+  p.wait_ns = (uint64_t)(wait_limit_ms ? wait_limit_ms : 2000u) * 1000000ull;
+  p.status = dev_status;
+  p.sf_vec = ((reinterpret_cast<uintptr_t>(sa) | reinterpret_cast<uintptr_t>(sb) | (uintptr_t)rssa | (uintptr_t)cssb) & 7u) == 0;
+  static bool attr_set[64] = {};
+  const int dev = current_device();
+  if (!attr_set[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(mx::gemm_mxf4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, mx::SMEM_BYTES);
+    if (e != cudaSuccess) return (int)e;
+    attr_set[dev] = true;
+  }
+  const dim3 grid((unsigned)((n + mx::BN - 1) / mx::BN), (unsigned)((m + mx::BM - 1) / mx::BM));
+  mx::gemm_mxf4_kernel<<<grid, mx::THREADS, mx::SMEM_BYTES, (cudaStream_t)stream>>>(tmA, tmB, p);
+  SKLB_COUNT_LAUNCH();
+  return (int)cudaGetLastError();
 }

@@ -1212,6 +1212,24 @@ void skl_gemm_mxf4e2m1_mxf4e2m1_f32_sm100a(size_t m, size_t n, size_t k, float a
       if (!on_device(b)) db = stage_in(WS_B, b, (n - 1) * csb + k / 2);
       if (!on_device(sb)) dsb = stage_in(WS_COL, sb, (n - 1) * cssb + kb);
       if (!da || !dsa || !db || !dsb) break;
+      /* the block-scaled tensor-core instruction, when the packed rows are TMA-compatible and C is on the device */
+      {
+        const char *e = getenv("SKL_B200_MXF4_NATIVE"); /* 0: always widen to bf16 */
+        const int native = !(e && atoi(e) == 0) && g_ctx.force_path != SKL_B200_PATH_GENERIC && on_device(c) &&
+                           skl_b200_gemm_mxf4_supported(da, (int64_t)rsa, db, (int64_t)csb, (int64_t)m, (int64_t)n, (int64_t)k);
+        if (native) {
+          uint32_t *st = device_status_words();
+          if (!st) break;
+          if (cuda_ok((cudaError_t)skl_b200_launch_gemm_mxf4(da, (int64_t)rsa, dsa, (int64_t)rssa, db, (int64_t)csb, dsb,
+                                                              (int64_t)cssb, c, (int64_t)rsc, (int64_t)m, (int64_t)n,
+                                                              (int64_t)k, alpha, beta, g_ctx.wait_limit_ms, st,
+                                                              g_ctx.stream))) {
+            g_ctx.last_path = SKL_B200_PATH_TCGEN05;
+            finish(!on_device(a) || !on_device(b) || !on_device(sa) || !on_device(sb));
+          }
+          break;
+        }
+      }
       wa = workspace(WS_PLAIN_A, m * k * 2);
       wb = wa ? workspace(WS_PLAIN_B, n * k * 2) : 0;
       if (!wb) break;

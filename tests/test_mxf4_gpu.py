@@ -59,11 +59,18 @@ def case(skl, m, n, k, alpha, beta, where, seed, pad=0, lo=117, hi=137):
     return got[:, :n], want[:, :n]
 
 
-@pytest.mark.parametrize("where", ["device", "host"])
-def test_mxf4_gemm_within_the_forward_bound(skl, where):
+@pytest.mark.parametrize("where,native", [("device", "1"), ("device", "0"), ("host", "1")])
+def test_mxf4_gemm_within_the_forward_bound(skl, where, native, monkeypatch):
+    """Device operands with TMA-compatible rows run on the block-scaled tensor-core instruction (native = 1); host C
+    or SKL_B200_MXF4_NATIVE=0 take the exact widening to bf16 followed by the bf16 kernel."""
+    monkeypatch.setenv("SKL_B200_MXF4_NATIVE", native)
     for i, (m, n, k, alpha, beta, pad) in enumerate([(256, 512, 1024, 1.0, 0.0, 0), (100, 300, 64, 0.5, 2.0, 3),
                                                       (1, 7, 32, 1.0, 1.0, 1), (130, 129, 4096, 2.0, 0.0, 0)]):
         case(skl, m, n, k, alpha, beta, where, 10 * i + (where == "host"), pad)
+        # pad = 0 keeps the packed rows 16-byte aligned: one launch on the block-scaled instruction; otherwise two
+        # widening launches and the bf16 GEMM
+        native_here = where == "device" and native == "1" and pad == 0
+        assert skl.skl_b200_last_launch_count() == (1 if native_here else 3), (m, n, k, where, native)
     assert skl.skl_b200_last_path() in (S.PATH_TCGEN05, S.PATH_GENERIC)
 
 
@@ -73,6 +80,35 @@ def test_mxf4_gemm_runs_on_the_tensor_cores_and_is_exact_on_exact_sums(skl):
     got, want = case(skl, 256, 256, 32, 1.0, 0.0, "device", 77, lo=127, hi=128)
     assert skl.skl_b200_last_path() == S.PATH_TCGEN05
     assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+
+
+def test_mxf4_native_scale_placement(skl):
+    """All elements 1.0; the scale of one (row, k block) of A and one (column, k block) of B set to 2^3 resp. 2^5: every
+    output is then an exact small integer that names the row, column and block the hardware applied each scale to."""
+    import torch
+
+    m, n, k = 256, 384, 512
+    fn = skl.skl_gemm_mxf4e2m1_mxf4e2m1_f32_sm100a
+    for (ri, kbi, cj, kbj) in [(0, 0, 0, 0), (37, 5, 200, 5), (129, 15, 383, 2), (255, 9, 31, 9), (64, 3, 96, 12)]:
+        a = np.full((m, k // 2), 0x22, np.uint8)
+        b = np.full((n, k // 2), 0x22, np.uint8)
+        sa = np.full((m, k // 32), 127, np.uint8)
+        sb = np.full((n, k // 32), 127, np.uint8)
+        sa[ri, kbi] = 130
+        sb[cj, kbj] = 132
+        want = np.full((m, n), float(k), np.float32)
+        want[ri, :] += 32 * 7
+        want[:, cj] += 32 * 31
+        if kbi == kbj:
+            want[ri, cj] += 32 * (8 * 32 - 8 - 32 + 1)
+        da, dsa, db, dsb = (DeviceBuf(x.reshape(-1)) for x in (a, sa, b, sb))
+        dc = torch.zeros((m, n), dtype=torch.float32, device="cuda")
+        fn(m, n, k, 1.0, da.ptr(0), k // 2, dsa.ptr(0), k // 32, db.ptr(0), k // 2, dsb.ptr(0), k // 32, 0.0,
+           dc.data_ptr(), n)
+        S.check()
+        assert skl.skl_b200_last_launch_count() == 1
+        got = dc.cpu().numpy()
+        assert np.array_equal(got, want), (ri, kbi, cj, kbj, np.argwhere(got != want)[:4])
 
 
 def test_mxf4_gemm_argument_checks_and_nan_scale(skl):
