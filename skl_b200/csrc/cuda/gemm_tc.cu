@@ -1186,6 +1186,7 @@ struct Params {
   uint64_t wait_ns;
   uint32_t *status;
   int sf_vec;              // the scale rows are 8-byte aligned: a stage's 8 scales of a row are one load
+  int c_vec;               // the rows of C are 16-byte aligned
 };
 
 // no-swizzle k-major descriptor of a 32-row x 16-byte scale chunk: 8-row groups 128 bytes apart
@@ -1343,12 +1344,28 @@ __global__ void __launch_bounds__(THREADS, 2)
         tmem_ld32(taddr + c0, r);
         if (row < p.M) {
           float *cp = p.c + (int64_t)row * p.rsc + n0 + c0;
+          if (p.c_vec && n0 + c0 + 32 <= p.N) {  // 16-byte stores: eight per lane cover the chunk's 128 bytes of the row
 #pragma unroll
-          for (int e = 0; e < 32; ++e) {
-            if (n0 + c0 + e < p.N) {
-              float v = __fmul_rn(p.alpha, __uint_as_float(r[e]));
-              if (p.beta != 0.0f) v = __fadd_rn(__fmul_rn(p.beta, cp[e]), v);
-              cp[e] = v;
+            for (int q = 0; q < 8; ++q) {
+              float4 v = make_float4(__fmul_rn(p.alpha, __uint_as_float(r[4 * q])), __fmul_rn(p.alpha, __uint_as_float(r[4 * q + 1])),
+                                     __fmul_rn(p.alpha, __uint_as_float(r[4 * q + 2])), __fmul_rn(p.alpha, __uint_as_float(r[4 * q + 3])));
+              if (p.beta != 0.0f) {
+                const float4 o = *reinterpret_cast<const float4 *>(cp + 4 * q);
+                v.x = __fadd_rn(__fmul_rn(p.beta, o.x), v.x);
+                v.y = __fadd_rn(__fmul_rn(p.beta, o.y), v.y);
+                v.z = __fadd_rn(__fmul_rn(p.beta, o.z), v.z);
+                v.w = __fadd_rn(__fmul_rn(p.beta, o.w), v.w);
+              }
+              *reinterpret_cast<float4 *>(cp + 4 * q) = v;
+            }
+          } else {
+#pragma unroll
+            for (int e = 0; e < 32; ++e) {
+              if (n0 + c0 + e < p.N) {
+                float v = __fmul_rn(p.alpha, __uint_as_float(r[e]));
+                if (p.beta != 0.0f) v = __fadd_rn(__fmul_rn(p.beta, cp[e]), v);
+                cp[e] = v;
+              }
             }
           }
         }
@@ -1976,6 +1993,7 @@ extern "C" int skl_b200_launch_gemm_mxf4(const void *a, int64_t rsa, const void 
   p.beta = beta;
   p.wait_ns = (uint64_t)(wait_limit_ms ? wait_limit_ms : 2000u) * 1000000ull;
   p.status = dev_status;
+  p.c_vec = ((reinterpret_cast<uintptr_t>(c) & 15u) == 0 && (m <= 1 || (rsc & 3) == 0)) ? 1 : 0;
   p.sf_vec = ((reinterpret_cast<uintptr_t>(sa) | reinterpret_cast<uintptr_t>(sb) | (uintptr_t)rssa | (uintptr_t)cssb) & 7u) == 0;
   static bool attr_set[64] = {};
   const int dev = current_device();
