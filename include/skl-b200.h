@@ -275,8 +275,9 @@ SKL_FUNC void skl_gemm_f32rcptex1c_f32rcp1xte_f32rcptexterc_sm100a(
  * per row of k ("[N][K]"): column j starts at b + j*csb bytes, its scales at sb + j*cssb.  k must be a multiple of 32.
  *     C[i, j] = beta * C[i, j] + alpha * sum_k A[i, k] * B[k, j]      (C row-major fp32, row stride rsc elements)
  * with SKL's float-GEMM conventions: products and sum in fp32 (ref/gemm/gemm_bf16rc_bf16rc_f32rc.c:9-24 with the
- * scaled elements as operands).  Both operands are widened exactly to bf16 and run on the bf16 tensor-core kernel; the
- * hardware's block-scaled MMA kinds are not used.  Results are within the forward bound of the reference's GEMM tests. */
+ * scaled elements as operands).  Device operands whose packed rows are 16-byte aligned (base and row strides) run on
+ * the block-scaled tensor-core instruction; others are widened exactly to bf16 and run on the bf16 kernel.  Results
+ * are within the forward bound of the reference's GEMM tests on either path. */
 SKL_FUNC void skl_gemm_mxf4e2m1_mxf4e2m1_f32_sm100a(size_t m, size_t n, size_t k, float alpha, const uint8_t *a,
                                                     size_t rsa, const uint8_t *sa, size_t rssa, const uint8_t *b,
                                                     size_t csb, const uint8_t *sb, size_t cssb, float beta, float *c,
