@@ -1190,8 +1190,9 @@ void skl_cvt_f4e2m1_f8e4m3_sm100a(uint8_t *pDst, const uint8_t *pSrc, size_t n) 
 
 /* ------------------------------------------------------------------ MX-FP4 GEMM (block-scaled E2M1) */
 
-/* Both operands are widened exactly to bf16 (element x 2^(scale - 127)) into workspaces and multiplied by the bf16
- * tensor-core path with fp32 accumulation. */
+/* Device operands with TMA-compatible packed rows run on the block-scaled tensor-core kernel; otherwise both operands
+ * are widened exactly to bf16 (element x 2^(scale - 127)) into workspaces and multiplied by the bf16 tensor-core path
+ * with fp32 accumulation. */
 void skl_gemm_mxf4e2m1_mxf4e2m1_f32_sm100a(size_t m, size_t n, size_t k, float alpha, const uint8_t *a, size_t rsa,
                                            const uint8_t *sa, size_t rssa, const uint8_t *b, size_t csb,
                                            const uint8_t *sb, size_t cssb, float beta, float *c, size_t rsc) {
