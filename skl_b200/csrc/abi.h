@@ -114,9 +114,11 @@ int skl_b200_launch_cvt_f4_to_f8e4m3(void *dst, const void *src, size_t n, void 
 /* MX-FP4 rows (16 bytes + one E8M0 scale per block of 32 elements) -> bf16 rows; ld_* in elements of dst / bytes of src / scale bytes */
 /* MX-FP4 GEMM on the block-scaled tensor-core instruction (device pointers; see gemm_tc.cu) */
 int skl_b200_gemm_mxf4_supported(const void *a, int64_t rsa, const void *b, int64_t csb, int64_t m, int64_t n, int64_t k);
+size_t skl_b200_gemm_mxf4_scale_bytes(int64_t rows, int64_t k); /* workspace for one operand's re-laid scales */
 int skl_b200_launch_gemm_mxf4(const void *a, int64_t rsa, const void *sa, int64_t rssa, const void *b, int64_t csb,
                               const void *sb, int64_t cssb, float *c, int64_t rsc, int64_t m, int64_t n, int64_t k,
-                              float alpha, float beta, uint32_t wait_limit_ms, uint32_t *dev_status, void *stream);
+                              float alpha, float beta, void *ws_sa, void *ws_sb, uint32_t wait_limit_ms,
+                              uint32_t *dev_status, void *stream);
 int skl_b200_launch_cvt_mxf4_to_bf16(void *dst, size_t ld_dst, const void *src, size_t ld_src, const void *scales,
                                      size_t ld_scales, size_t rows, size_t kblocks, void *stream);
 /* Device-side self check: counts inputs in [first, first+count) (fp32 bit patterns) for which the

@@ -1162,32 +1162,64 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
 // ====================================================================== MX-FP4 (block-scaled E2M1) GEMM
 // C[m, n] (fp32, row-major) = beta * C + alpha * sum_k A[m, k] * B[n, k], A and B packed E2M1 (two per byte, k
 // contiguous) with one E8M0 scale per 32 consecutive k, on tcgen05.mma.kind::mxf4.block_scale (K = 64 per instruction,
-// two scales per row and instruction).  One 128 x 128 tile per CTA.  A stage holds 256 elements of k: a 128 x 128-byte
-// box of A and of B (TMA, 128-byte swizzle) and the stage's 8 scales per row of A and of B in the layout the
-// smem -> TMEM scale copy expects (per chunk of 4 scales: row r at (r % 32) * 16 + (r / 32) * 4; tcgen05.cp
-// 32x128b.warpx4 spreads it over the four lane quarters).  Warp 0 issues TMA, warp 1 the scale copies and MMAs,
-// warps 2..5 fetch the scales with plain loads during the main loop and run the epilogue afterwards.  The scale bytes
-// of an instruction are picked by the scale-factor id in the instruction descriptor (0 or 2 inside the 4-byte column).
+// two scales per row and instruction; the scale bytes of an instruction are picked by the scale-factor id in the
+// instruction descriptor: 0 or 2 inside the 4-byte column).
+//
+// Scales.  The smem -> TMEM scale copy (tcgen05.cp 32x128b.warpx4) wants, per 128 rows and 4 k blocks, a 512-byte
+// chunk with row r at (r % 32) * 16 + (r / 32) * 4.  mx_pack_scales_kernel re-lays the caller's row-major scale
+// matrices into [row tile][chunk][512 bytes] once per call (rows and k blocks that do not exist get 127 = 1.0), after
+// which a stage's scales of A and of B are one 1024-byte bulk copy each.
+//
+// Kernel.  Persistent, one CTA per SM, 128 x 256 tiles (n fastest): the tensor core spends 128 clocks on an MMA of 128
+// rows whatever its width, so only 256-column instructions reach its rate (128 x 128 tiles measured 2.6 PFLOP/s with
+// the pipe 30 % busy).  4 stages of 256 elements of k: a 128 x 128-byte box of A, a 256 x 128-byte box of B (TMA,
+// 128-byte swizzle) and three 1 KiB scale pieces.  Warp 0 issues the copies, warp 1 the scale copies into TMEM and the
+// MMAs, warps 2..5 run the epilogue.  The accumulator takes 256 of the 512 TMEM columns and the scales need columns
+// too, so there is one accumulator: the epilogue of a tile is exposed, only the copies of the next tile's first
+// stages run under it.  Every wait is bounded like the main kernel's.
 namespace mx {
-constexpr int BM = 128, BN = 128, STAGE_K_BYTES = 128, STAGES = 3;  // 3 stages: two CTAs fit on an SM
-constexpr int A_BYTES = BM * STAGE_K_BYTES, B_BYTES = BN * STAGE_K_BYTES, SF_BYTES = 2 * 512;
-constexpr int STAGE_BYTES = A_BYTES + B_BYTES + 2 * SF_BYTES;
+constexpr int BM = 128, BN = 256, STAGE_K_BYTES = 128, STAGES = 4;
+constexpr int A_BYTES = BM * STAGE_K_BYTES, B_BYTES = BN * STAGE_K_BYTES, SF_BYTES = 2 * 512;  // SF_BYTES: 128 rows, one stage
+constexpr int STAGE_BYTES = A_BYTES + B_BYTES + 3 * SF_BYTES;  // scales: 128 rows of A, 2 x 128 columns of B
 constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + 256;
 constexpr int THREADS = 192;
-constexpr uint32_t ERR_EMPTY = 0x301, ERR_FULL = 0x302, ERR_DONE = 0x303;
+constexpr uint32_t ERR_EMPTY = 0x301, ERR_FULL = 0x302, ERR_TFULL = 0x303, ERR_TEMPTY = 0x304;
 
 struct Params {
-  const uint8_t *sa, *sb;  // scales, row i at sa + i * rssa
-  int64_t rssa, rssb;
+  const uint8_t *psa, *psb;  // packed scales: [row tile][stage][1024 bytes]
   float *c;
   int64_t rsc;
-  int M, N, kblocks;       // kblocks = K / 32
+  int M, N, kblocks;         // kblocks = K / 32
+  int tiles_m, tiles_n;
   float alpha, beta;
   uint64_t wait_ns;
   uint32_t *status;
-  int sf_vec;              // the scale rows are 8-byte aligned: a stage's 8 scales of a row are one load
-  int c_vec;               // the rows of C are 16-byte aligned
+  int c_vec;                 // the rows of C are 16-byte aligned
 };
+
+// dst[(tile * chunks + chunk) * 512 + (r % 32) * 16 + (r / 32) * 4 + e] = src[(tile * 128 + r) * ld + chunk * 4 + e]
+__global__ void __launch_bounds__(256)
+    mx_pack_scales_kernel(uint32_t *__restrict__ dst, const uint8_t *__restrict__ src, int64_t ld, int rows, int kblocks,
+                          int chunks, int64_t total) {
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+    // i = (tile * chunks + chunk) * 128 + slot, slot = (r % 32) * 4 + r / 32  (one 4-byte word each)
+    const int slot = (int)(i & 127);
+    const int64_t tc = i >> 7;
+    const int chunk = (int)(tc % chunks);
+    const int64_t tile = tc / chunks;
+    const int r = (slot >> 2) + 32 * (slot & 3);
+    const int64_t row = tile * 128 + r;
+    uint32_t w = 0x7F7F7F7Fu;
+    if (row < rows) {
+      const uint8_t *sp = src + row * ld + chunk * 4;
+#pragma unroll
+      for (int e = 0; e < 4; ++e)
+        if (chunk * 4 + e < kblocks) w = (w & ~(0xFFu << (8 * e))) | ((uint32_t)__ldg(sp + e) << (8 * e));
+    }
+    dst[i] = w;
+  }
+}
 
 // no-swizzle k-major descriptor of a 32-row x 16-byte scale chunk: 8-row groups 128 bytes apart
 __device__ __forceinline__ uint64_t sf_desc(uint32_t saddr) {
@@ -1197,33 +1229,39 @@ __device__ __forceinline__ uint64_t sf_desc(uint32_t saddr) {
   d |= 1ull << 46;
   return d;
 }
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(src),
+               "r"(bytes), "r"(bar)
+               : "memory");
+}
 
-__global__ void __launch_bounds__(THREADS, 2)
+__global__ void __launch_bounds__(THREADS, 1)
     gemm_mxf4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const Params p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t tiles = (raw + 1023u) & ~1023u;
   const uint32_t bars = tiles + STAGES * STAGE_BYTES;
-  const uint32_t full_bar = bars, empty_bar = bars + 8 * STAGES, done_bar = bars + 16 * STAGES;
+  const uint32_t full_bar = bars, empty_bar = bars + 8 * STAGES, tfull_bar = bars + 16 * STAGES, tempty_bar = tfull_bar + 16;
   uint8_t *gen = smem_raw + (bars - raw);
-  volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(gen + 16 * STAGES + 16);
+  volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(gen + 16 * STAGES + 32);
   volatile uint32_t *abort_flag = tmem_slot + 1;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int m0 = (int)blockIdx.y * BM, n0 = (int)blockIdx.x * BN;
-  const int num_kb = (p.kblocks + 7) / 8;  // stages of 256 elements
+  const int num_kb = (p.kblocks + 7) / 8;  // stages of 256 elements per tile
+  const int total_tiles = p.tiles_m * p.tiles_n;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
-      mbar_init(full_bar + 8 * s, 1 + 4);  // the TMA thread's expect_tx arrival + one per scale-loading warp
+      mbar_init(full_bar + 8 * s, 1);
       mbar_init(empty_bar + 8 * s, 1);
     }
-    mbar_init(done_bar, 1);
+    mbar_init(tfull_bar, 1);
+    mbar_init(tempty_bar, 128);
     *abort_flag = 0u;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
   if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 256;" ::"r"(
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 512;" ::"r"(
                      smem_u32((const void *)tmem_slot))
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -1235,111 +1273,97 @@ __global__ void __launch_bounds__(THREADS, 2)
 
   if (warp == 0) {
     if (lane == 0) {
-      for (int kb = 0; kb < num_kb; ++kb) {
-        const int stage = kb % STAGES;
-        if (kb >= STAGES &&
-            !mbar_wait(empty_bar + 8 * stage, (uint32_t)(kb / STAGES - 1) & 1u, abort_flag, p.status, ERR_EMPTY, p.wait_ns))
-          break;
-        const uint32_t sa = tiles + stage * STAGE_BYTES, sb = sa + A_BYTES, fb = full_bar + 8 * stage;
-        mbar_expect_tx(fb, A_BYTES + B_BYTES);
-        tma_load_2d(sa, &tmA, fb, kb * STAGE_K_BYTES, m0);
-        tma_load_2d(sb, &tmB, fb, kb * STAGE_K_BYTES, n0);
+      int g = 0;  // stages issued so far, over all tiles
+      bool ok = true;
+      for (int t = (int)blockIdx.x; ok && t < total_tiles; t += (int)gridDim.x) {
+        const int mi = t / p.tiles_n, ni = t - mi * p.tiles_n;
+        const uint8_t *sfa_src = p.psa + (int64_t)mi * num_kb * SF_BYTES, *sfb_src = p.psb + (int64_t)(2 * ni) * num_kb * SF_BYTES;
+        for (int kb = 0; kb < num_kb; ++kb, ++g) {
+          const int stage = g % STAGES;
+          if (g >= STAGES &&
+              !mbar_wait(empty_bar + 8 * stage, (uint32_t)(g / STAGES - 1) & 1u, abort_flag, p.status, ERR_EMPTY, p.wait_ns)) {
+            ok = false;
+            break;
+          }
+          const uint32_t sa = tiles + stage * STAGE_BYTES, sb = sa + A_BYTES, sfa = sb + B_BYTES, sfb = sfa + SF_BYTES;
+          const uint32_t fb = full_bar + 8 * stage;
+          mbar_expect_tx(fb, STAGE_BYTES);
+          tma_load_2d(sa, &tmA, fb, kb * STAGE_K_BYTES, mi * BM);
+          tma_load_2d(sb, &tmB, fb, kb * STAGE_K_BYTES, ni * BN);
+          bulk_load(sfa, sfa_src + (int64_t)kb * SF_BYTES, SF_BYTES, fb);
+          bulk_load(sfb, sfb_src + (int64_t)kb * SF_BYTES, SF_BYTES, fb);                               // columns 0..127
+          bulk_load(sfb + SF_BYTES, sfb_src + (int64_t)(num_kb + kb) * SF_BYTES, SF_BYTES, fb);  // columns 128..255
+        }
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      for (int kb = 0; kb < num_kb; ++kb) {
-        const int stage = kb % STAGES;
-        if (!mbar_wait(full_bar + 8 * stage, (uint32_t)(kb / STAGES) & 1u, abort_flag, p.status, ERR_FULL, p.wait_ns)) break;
+      int g = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int t = (int)blockIdx.x; ok && t < total_tiles; t += (int)gridDim.x) {
+        // one accumulator (256 of the 512 columns; the scales need columns too): the epilogue of the previous tile
+        // must have read it, while the copies of this tile's first stages are already under way
+        if (!mbar_wait(tempty_bar, acc_phase ^ 1u, abort_flag, p.status, ERR_TEMPTY, p.wait_ns)) break;
         tc_fence_after();
-        const uint32_t sa = tiles + stage * STAGE_BYTES, sb = sa + A_BYTES, sfa = sb + B_BYTES, sfb = sfa + SF_BYTES;
-        // scales of this stage -> TMEM columns 128.. (two regions used in turn): A chunks at +0, +4, B chunks at +8, +12
-        const uint32_t tsf = tmem_base + 128u + (uint32_t)(kb & 1) * 16u;
-#pragma unroll
-        for (int c = 0; c < 2; ++c) {
-          asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(tsf + 4u * c), "l"(sf_desc(sfa + 512u * c)) : "memory");
-          asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(tsf + 8u + 4u * c), "l"(sf_desc(sfb + 512u * c)) : "memory");
-        }
-        const uint64_t da = make_smem_desc(sa, 16, 1024), db = make_smem_desc(sb, 16, 1024);
-        const int left = p.kblocks - kb * 8;               // scale blocks left from this stage on
-        const int mmas = left >= 8 ? 4 : (left + 1) / 2;   // 64 elements = 2 scale blocks per instruction
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          if (j < mmas) {
-            const uint32_t sf_id = (uint32_t)(j & 1) * 2u;
-            // E2M1 x E2M1, E8M0 scales, N = 128, M = 128, K = 64
-            const uint32_t idesc = (sf_id << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | (1u << 23) |
-                                   ((uint32_t)(BM >> 4) << 24) | (sf_id << 29);
-            const uint32_t acc = (uint32_t)((kb | j) != 0);
-            asm volatile(
-                "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-                "tcgen05.mma.cta_group::1.kind::mxf4.block_scale.scale_vec::2X [%0], %1, %2, %3, [%5], [%6], p;\n\t}" ::"r"(
-                    tmem_base),
-                "l"(da + (uint64_t)(2 * j)), "l"(db + (uint64_t)(2 * j)), "r"(idesc), "r"(acc),
-                "r"(tsf + 4u * (uint32_t)(j >> 1)), "r"(tsf + 8u + 4u * (uint32_t)(j >> 1))
-                : "memory");
+        const uint32_t d_tmem = tmem_base;
+        for (int kb = 0; kb < num_kb; ++kb, ++g) {
+          const int stage = g % STAGES;
+          if (!mbar_wait(full_bar + 8 * stage, (uint32_t)(g / STAGES) & 1u, abort_flag, p.status, ERR_FULL, p.wait_ns)) {
+            ok = false;
+            break;
           }
+          tc_fence_after();
+          const uint32_t sa = tiles + stage * STAGE_BYTES, sb = sa + A_BYTES, sfa = sb + B_BYTES, sfb = sfa + SF_BYTES;
+          // scales of this stage -> TMEM columns 256.. (two regions used in turn): A chunks at +0, +4; B chunk c at
+          // +8 + 8 c (columns 0..127 of the tile) and +12 + 8 c (columns 128..255)
+          const uint32_t tsf = tmem_base + 256u + (uint32_t)(g & 1) * 32u;
+#pragma unroll
+          for (int c = 0; c < 2; ++c) {
+            asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(tsf + 4u * c), "l"(sf_desc(sfa + 512u * c)) : "memory");
+            asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(tsf + 8u + 8u * c), "l"(sf_desc(sfb + 512u * c)) : "memory");
+            asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(tsf + 12u + 8u * c), "l"(sf_desc(sfb + SF_BYTES + 512u * c)) : "memory");
+          }
+          const uint64_t da = make_smem_desc(sa, 16, 1024), db = make_smem_desc(sb, 16, 1024);
+          const int left = p.kblocks - kb * 8;               // scale blocks left from this stage on
+          const int mmas = left >= 8 ? 4 : (left + 1) / 2;   // 64 elements = 2 scale blocks per instruction
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            if (j < mmas) {
+              const uint32_t sf_id = (uint32_t)(j & 1) * 2u;
+              // E2M1 x E2M1, E8M0 scales, N = 256, M = 128, K = 64
+              const uint32_t idesc = (sf_id << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | (1u << 23) |
+                                     ((uint32_t)(BM >> 4) << 24) | (sf_id << 29);
+              const uint32_t accum = (uint32_t)((kb | j) != 0);
+              asm volatile(
+                  "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                  "tcgen05.mma.cta_group::1.kind::mxf4.block_scale.scale_vec::2X [%0], %1, %2, %3, [%5], [%6], p;\n\t}" ::"r"(
+                      d_tmem),
+                  "l"(da + (uint64_t)(2 * j)), "l"(db + (uint64_t)(2 * j)), "r"(idesc), "r"(accum),
+                  "r"(tsf + 4u * (uint32_t)(j >> 1)), "r"(tsf + 8u + 8u * (uint32_t)(j >> 1))
+                  : "memory");
+            }
+          }
+          umma_commit(empty_bar + 8 * stage);
         }
-        umma_commit(empty_bar + 8 * stage);
+        if (!ok) break;
+        umma_commit(tfull_bar);
+        acc_phase ^= 1u;
       }
-      umma_commit(done_bar);
     }
   } else {
-    // ---- scale loaders, then epilogue.  Thread t of the 128 = row t of the tile (A) and column t (B).
-    const int quad = warp & 3, t = quad * 32 + lane;
-    const int row = m0 + t, col = n0 + t;
-    const uint32_t off = (uint32_t)((t & 31) * 16 + (t >> 5) * 4);
-    bool ok = true;
-    // the 8 scales of this thread's row of A and column of B for stage kb (1.0 where there is no row / no k)
-    auto fetch = [&](int kb, uint32_t (&wa)[2], uint32_t (&wb)[2]) {
-      wa[0] = wa[1] = wb[0] = wb[1] = 0x7F7F7F7Fu;
-      if (p.sf_vec && kb * 8 + 8 <= p.kblocks) {
-        if (row < p.M) {
-          const uint2 v = __ldg(reinterpret_cast<const uint2 *>(p.sa + (int64_t)row * p.rssa + kb * 8));
-          wa[0] = v.x;
-          wa[1] = v.y;
-        }
-        if (col < p.N) {
-          const uint2 v = __ldg(reinterpret_cast<const uint2 *>(p.sb + (int64_t)col * p.rssb + kb * 8));
-          wb[0] = v.x;
-          wb[1] = v.y;
-        }
-      } else {
-#pragma unroll
-        for (int e = 0; e < 8; ++e) {
-          const int blk = kb * 8 + e;
-          if (blk < p.kblocks) {
-            const uint32_t sh = 8u * (uint32_t)(e & 3);
-            if (row < p.M) wa[e >> 2] = (wa[e >> 2] & ~(0xFFu << sh)) | ((uint32_t)__ldg(p.sa + (int64_t)row * p.rssa + blk) << sh);
-            if (col < p.N) wb[e >> 2] = (wb[e >> 2] & ~(0xFFu << sh)) | ((uint32_t)__ldg(p.sb + (int64_t)col * p.rssb + blk) << sh);
-          }
-        }
-      }
-    };
-    uint32_t wa[2], wb[2], na[2], nb[2];
-    if (num_kb > 0) fetch(0, wa, wb);
-    for (int kb = 0; kb < num_kb && ok; ++kb) {
-      const int stage = kb % STAGES;
-      if (kb + 1 < num_kb) fetch(kb + 1, na, nb);  // in flight while this stage's buffer is waited for
-      if (kb >= STAGES)
-        ok = mbar_wait(empty_bar + 8 * stage, (uint32_t)(kb / STAGES - 1) & 1u, abort_flag, p.status, ERR_EMPTY, p.wait_ns);
-      if (!ok) break;
-      const uint32_t sfa = tiles + stage * STAGE_BYTES + A_BYTES + B_BYTES, sfb = sfa + SF_BYTES;
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        asm volatile("st.shared.u32 [%0], %1;" ::"r"(sfa + 512u * c + off), "r"(wa[c]) : "memory");
-        asm volatile("st.shared.u32 [%0], %1;" ::"r"(sfb + 512u * c + off), "r"(wb[c]) : "memory");
-      }
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-      __syncwarp();
-      if (lane == 0) mbar_arrive(full_bar + 8 * stage);
-      wa[0] = na[0]; wa[1] = na[1]; wb[0] = nb[0]; wb[1] = nb[1];
-    }
-    if (ok && mbar_wait(done_bar, 0u, abort_flag, p.status, ERR_DONE, p.wait_ns)) {
+    // ---- epilogue: warp quarter q reads lanes 32 q .. of the tile's accumulator, lane = row
+    const int quad = warp & 3;
+    uint32_t acc_phase = 0;
+    for (int t = (int)blockIdx.x; t < total_tiles; t += (int)gridDim.x) {
+      const int mi = t / p.tiles_n, ni = t - mi * p.tiles_n;
+      const int row = mi * BM + quad * 32 + lane, n0 = ni * BN;
+      if (!mbar_wait(tfull_bar, acc_phase, abort_flag, p.status, ERR_TFULL, p.wait_ns)) break;
       tc_fence_after();
       const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16);
 #pragma unroll 1
       for (int c0 = 0; c0 < BN; c0 += 32) {
+        if (n0 + c0 >= p.N) break;  // uniform across the warp
         uint32_t r[32];
         tmem_ld32(taddr + c0, r);
         if (row < p.M) {
@@ -1370,13 +1394,16 @@ __global__ void __launch_bounds__(THREADS, 2)
           }
         }
       }
+      tc_fence_before();
+      mbar_arrive(tempty_bar);
+      acc_phase ^= 1u;
     }
   }
   tc_fence_before();
   __syncthreads();
   if (warp == 1) {
     tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 256;" ::"r"(tmem_base) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;" ::"r"(tmem_base) : "memory");
   }
 }
 }  // namespace mx
@@ -1960,16 +1987,22 @@ extern "C" int skl_b200_gemm_mxf4_supported(const void *a, int64_t rsa, const vo
   return encode_fn() != nullptr;
 }
 
+extern "C" size_t skl_b200_gemm_mxf4_scale_bytes(int64_t rows, int64_t k) {
+  return (size_t)(2 * ((rows + 255) / 256)) * (size_t)((k + 255) / 256) * mx::SF_BYTES;  // row tiles of 128, an even number
+}
+
+// ws_sa / ws_sb: device buffers of skl_b200_gemm_mxf4_scale_bytes(m, k) / (n, k) bytes for the re-laid scales
 extern "C" int skl_b200_launch_gemm_mxf4(const void *a, int64_t rsa, const void *sa, int64_t rssa, const void *b,
                                          int64_t csb, const void *sb, int64_t cssb, float *c, int64_t rsc, int64_t m,
-                                         int64_t n, int64_t k, float alpha, float beta, uint32_t wait_limit_ms,
-                                         uint32_t *dev_status, void *stream) {
+                                         int64_t n, int64_t k, float alpha, float beta, void *ws_sa, void *ws_sb,
+                                         uint32_t wait_limit_ms, uint32_t *dev_status, void *stream) {
   EncodeTiledFn enc = encode_fn();
   if (!enc) return (int)cudaErrorNotSupported;
   CUtensorMap tmA, tmB;
-  const cuuint32_t box[2] = {(cuuint32_t)mx::STAGE_K_BYTES, (cuuint32_t)mx::BM}, estr[2] = {1, 1};
+  cuuint32_t box[2] = {(cuuint32_t)mx::STAGE_K_BYTES, 0}, estr[2] = {1, 1};
   for (int which = 0; which < 2; ++which) {
     const cuuint64_t rows = (cuuint64_t)(which ? n : m);
+    box[1] = (cuuint32_t)(which ? mx::BN : mx::BM);
     cuuint64_t dims[2] = {(cuuint64_t)(k / 2), rows}, strides[1];
     int64_t ld = which ? csb : rsa;
     if (rows <= 1) ld = (k / 2 + 15) / 16 * 16;  // stride unused; keep it legal
@@ -1979,22 +2012,32 @@ extern "C" int skl_b200_launch_gemm_mxf4(const void *a, int64_t rsa, const void 
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
       return (int)cudaErrorInvalidValue;
   }
+  const int kblocks = (int)(k / 32), chunks = 2 * ((kblocks + 7) / 8);
+  for (int which = 0; which < 2; ++which) {
+    const int64_t rows = which ? n : m;
+    const int64_t tiles = which ? 2 * ((rows + mx::BN - 1) / mx::BN) : (rows + mx::BM - 1) / mx::BM, total = tiles * chunks * 128;
+    int grid = (int)((total + 255) / 256);
+    if (grid > 8 * sm_count()) grid = 8 * sm_count();
+    mx::mx_pack_scales_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>((uint32_t *)(which ? ws_sb : ws_sa),
+                                                                      (const uint8_t *)(which ? sb : sa), which ? cssb : rssa,
+                                                                      (int)rows, kblocks, chunks, total);
+    SKLB_COUNT_LAUNCH();
+  }
   mx::Params p;
-  p.sa = (const uint8_t *)sa;
-  p.sb = (const uint8_t *)sb;
-  p.rssa = rssa;
-  p.rssb = cssb;
+  p.psa = (const uint8_t *)ws_sa;
+  p.psb = (const uint8_t *)ws_sb;
   p.c = c;
   p.rsc = rsc;
   p.M = (int)m;
   p.N = (int)n;
-  p.kblocks = (int)(k / 32);
+  p.kblocks = kblocks;
+  p.tiles_m = (int)((m + mx::BM - 1) / mx::BM);
+  p.tiles_n = (int)((n + mx::BN - 1) / mx::BN);
   p.alpha = alpha;
   p.beta = beta;
   p.wait_ns = (uint64_t)(wait_limit_ms ? wait_limit_ms : 2000u) * 1000000ull;
   p.status = dev_status;
   p.c_vec = ((reinterpret_cast<uintptr_t>(c) & 15u) == 0 && (m <= 1 || (rsc & 3) == 0)) ? 1 : 0;
-  p.sf_vec = ((reinterpret_cast<uintptr_t>(sa) | reinterpret_cast<uintptr_t>(sb) | (uintptr_t)rssa | (uintptr_t)cssb) & 7u) == 0;
   static bool attr_set[64] = {};
   const int dev = current_device();
   if (!attr_set[dev]) {
@@ -2002,8 +2045,9 @@ extern "C" int skl_b200_launch_gemm_mxf4(const void *a, int64_t rsa, const void 
     if (e != cudaSuccess) return (int)e;
     attr_set[dev] = true;
   }
-  const dim3 grid((unsigned)((n + mx::BN - 1) / mx::BN), (unsigned)((m + mx::BM - 1) / mx::BM));
-  mx::gemm_mxf4_kernel<<<grid, mx::THREADS, mx::SMEM_BYTES, (cudaStream_t)stream>>>(tmA, tmB, p);
+  int64_t grid = (int64_t)p.tiles_m * p.tiles_n;
+  if (grid > sm_count()) grid = sm_count();
+  mx::gemm_mxf4_kernel<<<(unsigned)grid, mx::THREADS, mx::SMEM_BYTES, (cudaStream_t)stream>>>(tmA, tmB, p);
   SKLB_COUNT_LAUNCH();
   return (int)cudaGetLastError();
 }

@@ -1221,9 +1221,12 @@ void skl_gemm_mxf4e2m1_mxf4e2m1_f32_sm100a(size_t m, size_t n, size_t k, float a
         if (native) {
           uint32_t *st = device_status_words();
           if (!st) break;
+          void *psa = workspace(WS_PLAIN_A, skl_b200_gemm_mxf4_scale_bytes((int64_t)m, (int64_t)k));
+          void *psb = psa ? workspace(WS_PLAIN_B, skl_b200_gemm_mxf4_scale_bytes((int64_t)n, (int64_t)k)) : 0;
+          if (!psb) break;
           if (cuda_ok((cudaError_t)skl_b200_launch_gemm_mxf4(da, (int64_t)rsa, dsa, (int64_t)rssa, db, (int64_t)csb, dsb,
                                                               (int64_t)cssb, c, (int64_t)rsc, (int64_t)m, (int64_t)n,
-                                                              (int64_t)k, alpha, beta, g_ctx.wait_limit_ms, st,
+                                                              (int64_t)k, alpha, beta, psa, psb, g_ctx.wait_limit_ms, st,
                                                               g_ctx.stream))) {
             g_ctx.last_path = SKL_B200_PATH_TCGEN05;
             finish(!on_device(a) || !on_device(b) || !on_device(sa) || !on_device(sb));
