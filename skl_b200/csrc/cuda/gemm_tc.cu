@@ -1174,15 +1174,15 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
 // rows whatever its width, so only 256-column instructions reach its rate (128 x 128 tiles measured 2.6 PFLOP/s with
 // the pipe 30 % busy).  4 stages of 256 elements of k: a 128 x 128-byte box of A, a 256 x 128-byte box of B (TMA,
 // 128-byte swizzle) and three 1 KiB scale pieces.  Warp 0 issues the copies, warp 1 the scale copies into TMEM and the
-// MMAs, warps 2..5 run the epilogue.  The accumulator takes 256 of the 512 TMEM columns and the scales need columns
-// too, so there is one accumulator: the epilogue of a tile is exposed, only the copies of the next tile's first
-// stages run under it.  Every wait is bounded like the main kernel's.
+// MMAs, warps 2..9 run the epilogue.  The accumulator takes 256 of the 512 TMEM columns and the scales need columns
+// too, so there is one accumulator: the epilogue warps copy it into registers at once (128 columns per thread) and
+// hand it back, so that only those loads, not the stores, keep the tensor core waiting.  Every wait is bounded like the main kernel's.
 namespace mx {
 constexpr int BM = 128, BN = 256, STAGE_K_BYTES = 128, STAGES = 4;
 constexpr int A_BYTES = BM * STAGE_K_BYTES, B_BYTES = BN * STAGE_K_BYTES, SF_BYTES = 2 * 512;  // SF_BYTES: 128 rows, one stage
 constexpr int STAGE_BYTES = A_BYTES + B_BYTES + 3 * SF_BYTES;  // scales: 128 rows of A, 2 x 128 columns of B
 constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + 256;
-constexpr int THREADS = 192;
+constexpr int THREADS = 320;  // producer, MMA issuer, 8 epilogue warps
 constexpr uint32_t ERR_EMPTY = 0x301, ERR_FULL = 0x302, ERR_TFULL = 0x303, ERR_TEMPTY = 0x304;
 
 struct Params {
@@ -1235,6 +1235,20 @@ __device__ __forceinline__ void bulk_load(uint32_t dst, const void *src, uint32_
                : "memory");
 }
 
+// 32 accumulator columns of this thread's lane, without waiting for the load
+__device__ __forceinline__ void tmem_ld32_async(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]),
+        "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]),
+        "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]),
+        "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+}
+
 __global__ void __launch_bounds__(THREADS, 1)
     gemm_mxf4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const Params p) {
   extern __shared__ uint8_t smem_raw[];
@@ -1255,7 +1269,7 @@ __global__ void __launch_bounds__(THREADS, 1)
       mbar_init(empty_bar + 8 * s, 1);
     }
     mbar_init(tfull_bar, 1);
-    mbar_init(tempty_bar, 128);
+    mbar_init(tempty_bar, 256);
     *abort_flag = 0u;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -1352,27 +1366,35 @@ __global__ void __launch_bounds__(THREADS, 1)
       }
     }
   } else {
-    // ---- epilogue: warp quarter q reads lanes 32 q .. of the tile's accumulator, lane = row
-    const int quad = warp & 3;
+    // ---- epilogue.  There is one accumulator, so the tensor core waits while it is read: 8 warps (quarter q = warp % 4
+    // reads lanes 32 q .., lane = row; warps 2..5 take columns 0..127, warps 6..9 columns 128..255) pull their 128
+    // columns into registers at once and hand the accumulator back before they scale and store.
+    const int quad = warp & 3, half = warp >= 6 ? 1 : 0;
     uint32_t acc_phase = 0;
     for (int t = (int)blockIdx.x; t < total_tiles; t += (int)gridDim.x) {
       const int mi = t / p.tiles_n, ni = t - mi * p.tiles_n;
-      const int row = mi * BM + quad * 32 + lane, n0 = ni * BN;
+      const int row = mi * BM + quad * 32 + lane, n0 = ni * BN + half * (BN / 2);
       if (!mbar_wait(tfull_bar, acc_phase, abort_flag, p.status, ERR_TFULL, p.wait_ns)) break;
       tc_fence_after();
-      const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16);
-#pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 32) {
-        if (n0 + c0 >= p.N) break;  // uniform across the warp
-        uint32_t r[32];
-        tmem_ld32(taddr + c0, r);
-        if (row < p.M) {
+      const uint32_t taddr = tmem_base + (uint32_t)(half * (BN / 2)) + ((uint32_t)(quad * 32) << 16);
+      uint32_t r[4][32];
+#pragma unroll
+      for (int ch = 0; ch < 4; ++ch) tmem_ld32_async(taddr + 32 * ch, r[ch]);
+      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+      tc_fence_before();
+      mbar_arrive(tempty_bar);
+      acc_phase ^= 1u;
+      if (row < p.M) {
+#pragma unroll
+        for (int ch = 0; ch < 4; ++ch) {
+          const int c0 = 32 * ch;
+          if (n0 + c0 >= p.N) break;
           float *cp = p.c + (int64_t)row * p.rsc + n0 + c0;
           if (p.c_vec && n0 + c0 + 32 <= p.N) {  // 16-byte stores: eight per lane cover the chunk's 128 bytes of the row
 #pragma unroll
             for (int q = 0; q < 8; ++q) {
-              float4 v = make_float4(__fmul_rn(p.alpha, __uint_as_float(r[4 * q])), __fmul_rn(p.alpha, __uint_as_float(r[4 * q + 1])),
-                                     __fmul_rn(p.alpha, __uint_as_float(r[4 * q + 2])), __fmul_rn(p.alpha, __uint_as_float(r[4 * q + 3])));
+              float4 v = make_float4(__fmul_rn(p.alpha, __uint_as_float(r[ch][4 * q])), __fmul_rn(p.alpha, __uint_as_float(r[ch][4 * q + 1])),
+                                     __fmul_rn(p.alpha, __uint_as_float(r[ch][4 * q + 2])), __fmul_rn(p.alpha, __uint_as_float(r[ch][4 * q + 3])));
               if (p.beta != 0.0f) {
                 const float4 o = *reinterpret_cast<const float4 *>(cp + 4 * q);
                 v.x = __fadd_rn(__fmul_rn(p.beta, o.x), v.x);
@@ -1386,7 +1408,7 @@ __global__ void __launch_bounds__(THREADS, 1)
 #pragma unroll
             for (int e = 0; e < 32; ++e) {
               if (n0 + c0 + e < p.N) {
-                float v = __fmul_rn(p.alpha, __uint_as_float(r[e]));
+                float v = __fmul_rn(p.alpha, __uint_as_float(r[ch][e]));
                 if (p.beta != 0.0f) v = __fadd_rn(__fmul_rn(p.beta, cp[e]), v);
                 cp[e] = v;
               }
@@ -1394,9 +1416,6 @@ __global__ void __launch_bounds__(THREADS, 1)
           }
         }
       }
-      tc_fence_before();
-      mbar_arrive(tempty_bar);
-      acc_phase ^= 1u;
     }
   }
   tc_fence_before();
