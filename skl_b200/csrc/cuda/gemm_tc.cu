@@ -1167,7 +1167,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
 //
 // Scales.  The smem -> TMEM scale copy (tcgen05.cp 32x128b.warpx4) wants, per 128 rows and 4 k blocks, a 512-byte
 // chunk with row r at (r % 32) * 16 + (r / 32) * 4.  mx_pack_scales_kernel re-lays the caller's row-major scale
-// matrices into [row tile][chunk][512 bytes] once per call (rows and k blocks that do not exist get 127 = 1.0), after
+// matrices into [row tile][chunk][512 bytes] once per call (one launch for both operands) (rows and k blocks that do not exist get 127 = 1.0), after
 // which a stage's scales of A and of B are one 1024-byte bulk copy each.
 //
 // Kernel.  Persistent, one CTA per SM, 128 x 256 tiles (n fastest): the tensor core spends 128 clocks on an MMA of 128
@@ -1197,12 +1197,19 @@ struct Params {
   int c_vec;                 // the rows of C are 16-byte aligned
 };
 
-// dst[(tile * chunks + chunk) * 512 + (r % 32) * 16 + (r / 32) * 4 + e] = src[(tile * 128 + r) * ld + chunk * 4 + e]
+// dst[(tile * chunks + chunk) * 512 + (r % 32) * 16 + (r / 32) * 4 + e] = src[(tile * 128 + r) * ld + chunk * 4 + e],
+// for the scales of A (the first total_a words) and of B (the rest) in one launch
 __global__ void __launch_bounds__(256)
-    mx_pack_scales_kernel(uint32_t *__restrict__ dst, const uint8_t *__restrict__ src, int64_t ld, int rows, int kblocks,
-                          int chunks, int64_t total) {
+    mx_pack_scales_kernel(uint32_t *__restrict__ dst_a, const uint8_t *__restrict__ src_a, int64_t ld_a, int rows_a,
+                          int64_t total_a, uint32_t *__restrict__ dst_b, const uint8_t *__restrict__ src_b, int64_t ld_b,
+                          int rows_b, int64_t total_b, int kblocks, int chunks) {
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
-  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+  for (int64_t j = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; j < total_a + total_b; j += stride) {
+    const bool second = j >= total_a;
+    const int64_t i = second ? j - total_a : j;
+    const uint8_t *src = second ? src_b : src_a;
+    const int64_t ld = second ? ld_b : ld_a;
+    const int rows = second ? rows_b : rows_a;
     // i = (tile * chunks + chunk) * 128 + slot, slot = (r % 32) * 4 + r / 32  (one 4-byte word each)
     const int slot = (int)(i & 127);
     const int64_t tc = i >> 7;
@@ -1217,7 +1224,7 @@ __global__ void __launch_bounds__(256)
       for (int e = 0; e < 4; ++e)
         if (chunk * 4 + e < kblocks) w = (w & ~(0xFFu << (8 * e))) | ((uint32_t)__ldg(sp + e) << (8 * e));
     }
-    dst[i] = w;
+    (second ? dst_b : dst_a)[i] = w;
   }
 }
 
@@ -2032,14 +2039,13 @@ extern "C" int skl_b200_launch_gemm_mxf4(const void *a, int64_t rsa, const void 
       return (int)cudaErrorInvalidValue;
   }
   const int kblocks = (int)(k / 32), chunks = 2 * ((kblocks + 7) / 8);
-  for (int which = 0; which < 2; ++which) {
-    const int64_t rows = which ? n : m;
-    const int64_t tiles = which ? 2 * ((rows + mx::BN - 1) / mx::BN) : (rows + mx::BM - 1) / mx::BM, total = tiles * chunks * 128;
-    int grid = (int)((total + 255) / 256);
+  {
+    const int64_t total_a = ((m + mx::BM - 1) / mx::BM) * chunks * 128, total_b = 2 * ((n + mx::BN - 1) / mx::BN) * chunks * 128;
+    int64_t grid = (total_a + total_b + 255) / 256;
     if (grid > 8 * sm_count()) grid = 8 * sm_count();
-    mx::mx_pack_scales_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>((uint32_t *)(which ? ws_sb : ws_sa),
-                                                                      (const uint8_t *)(which ? sb : sa), which ? cssb : rssa,
-                                                                      (int)rows, kblocks, chunks, total);
+    mx::mx_pack_scales_kernel<<<(unsigned)grid, 256, 0, (cudaStream_t)stream>>>(
+        (uint32_t *)ws_sa, (const uint8_t *)sa, rssa, (int)m, total_a, (uint32_t *)ws_sb, (const uint8_t *)sb, cssb, (int)n,
+        total_b, kblocks, chunks);
     SKLB_COUNT_LAUNCH();
   }
   mx::Params p;

@@ -65,12 +65,16 @@ def test_mxf4_gemm_within_the_forward_bound(skl, where, native, monkeypatch):
     or SKL_B200_MXF4_NATIVE=0 take the exact widening to bf16 followed by the bf16 kernel."""
     monkeypatch.setenv("SKL_B200_MXF4_NATIVE", native)
     for i, (m, n, k, alpha, beta, pad) in enumerate([(256, 512, 1024, 1.0, 0.0, 0), (100, 300, 64, 0.5, 2.0, 3),
-                                                      (1, 7, 32, 1.0, 1.0, 1), (130, 129, 4096, 2.0, 0.0, 0)]):
+                                                      (1, 7, 32, 1.0, 1.0, 1), (130, 129, 4096, 2.0, 0.0, 0),
+                                                      # k that ends inside a stage of 256 / inside an instruction of 64,
+                                                      # ragged row and column counts, a single k block
+                                                      (200, 260, 96, 1.0, 0.5, 0), (64, 40, 32, 1.0, 0.0, 0),
+                                                      (300, 520, 352, -1.5, 1.0, 0), (129, 257, 288, 1.0, 0.0, 0)]):
         case(skl, m, n, k, alpha, beta, where, 10 * i + (where == "host"), pad)
-        # pad = 0 keeps the packed rows 16-byte aligned: the block-scaled kernel after two launches that re-lay the
-        # scales; otherwise two widening launches and the bf16 GEMM (3 launches either way: the path is told by name)
+        # pad = 0 keeps the packed rows 16-byte aligned: one launch that re-lays the scales + the block-scaled kernel;
+        # otherwise two widening launches and the bf16 GEMM
         native_here = where == "device" and native == "1" and pad == 0
-        assert skl.skl_b200_last_launch_count() == 3, (m, n, k, where, native, native_here)
+        assert skl.skl_b200_last_launch_count() == (2 if native_here else 3), (m, n, k, where, native)
     assert skl.skl_b200_last_path() in (S.PATH_TCGEN05, S.PATH_GENERIC)
 
 
@@ -106,6 +110,7 @@ def test_mxf4_native_scale_placement(skl):
         fn(m, n, k, 1.0, da.ptr(0), k // 2, dsa.ptr(0), k // 32, db.ptr(0), k // 2, dsb.ptr(0), k // 32, 0.0,
            dc.data_ptr(), n)
         S.check()
+        assert skl.skl_b200_last_launch_count() == 2  # the block-scaled kernel, not the widening route
         got = dc.cpu().numpy()
         assert np.array_equal(got, want), (ri, kbi, cj, kbj, np.argwhere(got != want)[:4])
 
