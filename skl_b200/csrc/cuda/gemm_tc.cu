@@ -1174,7 +1174,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
 // rows whatever its width, so only 256-column instructions reach its rate (128 x 128 tiles measured 2.6 PFLOP/s with
 // the pipe 30 % busy).  4 stages of 256 elements of k: a 128 x 128-byte box of A, a 256 x 128-byte box of B (TMA,
 // 128-byte swizzle) and three 1 KiB scale pieces.  Warp 0 issues the copies, warp 1 the scale copies into TMEM and the
-// MMAs, warps 2..9 run the epilogue.  The accumulator takes 256 of the 512 TMEM columns and the scales need columns
+// MMAs (the scale copies come from warp 10), warps 2..9 run the epilogue.  The accumulator takes 256 of the 512 TMEM columns and the scales need columns
 // too, so there is one accumulator: the epilogue warps copy it into registers at once (128 columns per thread) and
 // hand it back, so that only those loads, not the stores, keep the tensor core waiting.  Every wait is bounded like the main kernel's.
 namespace mx {
@@ -1182,8 +1182,8 @@ constexpr int BM = 128, BN = 256, STAGE_K_BYTES = 128, STAGES = 4;
 constexpr int A_BYTES = BM * STAGE_K_BYTES, B_BYTES = BN * STAGE_K_BYTES, SF_BYTES = 2 * 512;  // SF_BYTES: 128 rows, one stage
 constexpr int STAGE_BYTES = A_BYTES + B_BYTES + 3 * SF_BYTES;  // scales: 128 rows of A, 2 x 128 columns of B
 constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + 256;
-constexpr int THREADS = 320;  // producer, MMA issuer, 8 epilogue warps
-constexpr uint32_t ERR_EMPTY = 0x301, ERR_FULL = 0x302, ERR_TFULL = 0x303, ERR_TEMPTY = 0x304;
+constexpr int THREADS = 352;  // producer, MMA issuer, 8 epilogue warps, scale copier
+constexpr uint32_t ERR_EMPTY = 0x301, ERR_FULL = 0x302, ERR_TFULL = 0x303, ERR_TEMPTY = 0x304, ERR_SF = 0x305;
 
 struct Params {
   const uint8_t *psa, *psb;  // packed scales: [row tile][stage][1024 bytes]
@@ -1263,8 +1263,9 @@ __global__ void __launch_bounds__(THREADS, 1)
   const uint32_t tiles = (raw + 1023u) & ~1023u;
   const uint32_t bars = tiles + STAGES * STAGE_BYTES;
   const uint32_t full_bar = bars, empty_bar = bars + 8 * STAGES, tfull_bar = bars + 16 * STAGES, tempty_bar = tfull_bar + 16;
+  const uint32_t sf_bar = tfull_bar + 32;  // [2]: the scales of a stage are in their TMEM region
   uint8_t *gen = smem_raw + (bars - raw);
-  volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(gen + 16 * STAGES + 32);
+  volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(gen + 16 * STAGES + 64);
   volatile uint32_t *abort_flag = tmem_slot + 1;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int num_kb = (p.kblocks + 7) / 8;  // stages of 256 elements per tile
@@ -1277,6 +1278,8 @@ __global__ void __launch_bounds__(THREADS, 1)
     }
     mbar_init(tfull_bar, 1);
     mbar_init(tempty_bar, 256);
+    mbar_init(sf_bar, 1);
+    mbar_init(sf_bar + 8, 1);
     *abort_flag = 0u;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -1335,16 +1338,15 @@ __global__ void __launch_bounds__(THREADS, 1)
             break;
           }
           tc_fence_after();
-          const uint32_t sa = tiles + stage * STAGE_BYTES, sb = sa + A_BYTES, sfa = sb + B_BYTES, sfb = sfa + SF_BYTES;
-          // scales of this stage -> TMEM columns 256.. (two regions used in turn): A chunks at +0, +4; B chunk c at
-          // +8 + 8 c (columns 0..127 of the tile) and +12 + 8 c (columns 128..255)
+          const uint32_t sa = tiles + stage * STAGE_BYTES, sb = sa + A_BYTES;
+          // the scale copier (warp 10) has put this stage's scales into TMEM region g % 2 (columns 256 + 32 (g % 2)):
+          // A chunks at +0, +4; B chunk c at +8 + 8 c (columns 0..127 of the tile) and +12 + 8 c (columns 128..255)
           const uint32_t tsf = tmem_base + 256u + (uint32_t)(g & 1) * 32u;
-#pragma unroll
-          for (int c = 0; c < 2; ++c) {
-            asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(tsf + 4u * c), "l"(sf_desc(sfa + 512u * c)) : "memory");
-            asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(tsf + 8u + 8u * c), "l"(sf_desc(sfb + 512u * c)) : "memory");
-            asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(tsf + 12u + 8u * c), "l"(sf_desc(sfb + SF_BYTES + 512u * c)) : "memory");
+          if (!mbar_wait(sf_bar + 8 * (g & 1), (uint32_t)(g >> 1) & 1u, abort_flag, p.status, ERR_SF, p.wait_ns)) {
+            ok = false;
+            break;
           }
+          tc_fence_after();
           const uint64_t da = make_smem_desc(sa, 16, 1024), db = make_smem_desc(sb, 16, 1024);
           const int left = p.kblocks - kb * 8;               // scale blocks left from this stage on
           const int mmas = left >= 8 ? 4 : (left + 1) / 2;   // 64 elements = 2 scale blocks per instruction
@@ -1370,6 +1372,40 @@ __global__ void __launch_bounds__(THREADS, 1)
         if (!ok) break;
         umma_commit(tfull_bar);
         acc_phase ^= 1u;
+      }
+    }
+  } else if (warp == 10) {
+    // ---- scale copier: smem -> TMEM copies of a stage's scales, issued from a thread of its own so that they do not
+    // queue between the MMAs of the issuing thread.  Stage g's copies may overwrite region g % 2 once the MMAs of stage
+    // g - 2 are done, which is when that stage's buffer was handed back.
+    if (lane == 0) {
+      int g = 0;
+      bool ok = true;
+      for (int t = (int)blockIdx.x; ok && t < total_tiles; t += (int)gridDim.x) {
+        for (int kb = 0; kb < num_kb; ++kb, ++g) {
+          const int stage = g % STAGES;
+          if (!mbar_wait(full_bar + 8 * stage, (uint32_t)(g / STAGES) & 1u, abort_flag, p.status, ERR_FULL, p.wait_ns)) {
+            ok = false;
+            break;
+          }
+          if (g >= 2) {
+            const int g2 = g - 2;
+            if (!mbar_wait(empty_bar + 8 * (g2 % STAGES), (uint32_t)(g2 / STAGES) & 1u, abort_flag, p.status, ERR_EMPTY, p.wait_ns)) {
+              ok = false;
+              break;
+            }
+          }
+          tc_fence_after();
+          const uint32_t sfa = tiles + stage * STAGE_BYTES + A_BYTES + B_BYTES, sfb = sfa + SF_BYTES;
+          const uint32_t tsf = tmem_base + 256u + (uint32_t)(g & 1) * 32u;
+#pragma unroll
+          for (int c = 0; c < 2; ++c) {
+            asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(tsf + 4u * c), "l"(sf_desc(sfa + 512u * c)) : "memory");
+            asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(tsf + 8u + 8u * c), "l"(sf_desc(sfb + 512u * c)) : "memory");
+            asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(tsf + 12u + 8u * c), "l"(sf_desc(sfb + SF_BYTES + 512u * c)) : "memory");
+          }
+          umma_commit(sf_bar + 8 * (g & 1));
+        }
       }
     }
   } else {
