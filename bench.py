@@ -37,7 +37,7 @@ if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
 M_C5, K_C5, N_C5 = 16384, 4096, 14336
-C5_DRAM_BYTES_PER_LAUNCH_1GPU = 625.3e6 + 456.4e6  # dram__bytes_read + dram__bytes_write, one launch of this build
+C5_DRAM_BYTES_PER_LAUNCH_1GPU = 804.4e6 + 453.8e6  # dram__bytes_read + dram__bytes_write, one launch of this build
 
 
 def measured_peaks():
@@ -792,7 +792,7 @@ def main() -> None:
     region_s = ms_total * 1e-3
     peak_kind = "sustained" if region_s >= 2.0 else "burst"
     peak = peaks["bf16_sustained"] if peak_kind == "sustained" else peaks["bf16_burst"]
-    roofline = {"bound": "tensor", "kernel": "gemm_tc_kernel<256, f16> (bf16 x bf16 -> fp32 in TMEM -> bf16)",
+    roofline = {"bound": "tensor", "kernel": "gemm_tc2_kernel<256, f16> (CTA pair; bf16 x bf16 -> fp32 in TMEM -> bf16)",
                 "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": (achieved / peak if achieved else None),
                 "peak_kind": f"{peak_kind}, of {peaks['source']}", "kernel_ms": kern_ms,
                 # dram__bytes_read + dram__bytes_write of one launch at the 1-GPU shape, from a profiler capture of

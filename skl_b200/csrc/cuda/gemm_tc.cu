@@ -1791,17 +1791,22 @@ int pair_mode() {
 
 // Is the two-CTA kernel usable / worthwhile for this problem?  Measured on B200 against the one-CTA kernel at
 // equal data: it moves a third less data from L2 to the SMs and runs at a higher clock under the power cap;
-// the net effect is +2-7 % for int8, +2 % for fp8 and under 1 % for bf16.  It has no tail strips, so it is
+// the net effect is +2-7 % for int8, +2 % for fp8 and +2-4 % for bf16 on large problems.  It has no tail strips, so it is
 // chosen for the 8-bit kinds only and only when its last round of 256 x 256 tiles is nearly full.
 bool use_pair_kernel(int kind, int64_t M, int64_t N, const OperandView &vb) {
   const int mode = pair_mode();
   if (mode == 0) return false;
   (void)vb;
   if (mode == 2) return N > 16;
-  if (kind == KIND_F16 || M <= 128) return false;
+  if (M <= 128) return false;
   const int64_t tiles = ((M + 255) / 256) * ((N + 255) / 256), pairs = sm_count() / 2;
   if (tiles < pairs) return false;
   const int64_t rounds = (tiles + pairs - 1) / pairs;
+  // 16-bit operands: the pair wins from about five rounds of tiles on (measured on bf16: +2.3 ... +3.6 % on
+  // 16384 x 4096 x {14336, 7168, 3584, 1792}, -1.7 % on 4096^3 with its 3.5 rounds).  The one-CTA kernel's column strips
+  // for a short last round do not decide this: a 128-row MMA takes 128 clocks at any width, so strips shorten only
+  // the loads and the epilogue (the 1792-column problem measures the same with and without them).
+  if (kind == KIND_F16) return rounds >= 5;
   const double fill = (double)tiles / (double)(rounds * pairs);
   return kind == KIND_I8 ? fill >= 0.85 : fill >= 0.95;
 }
