@@ -28,7 +28,9 @@
 //     these m (15.3 us against 17.4 us on 14336 x 4096 at m = 4); this variant serves callers that force the skinny
 //     path.  Other designs measured on that size and dropped: tcgen05.mma on 128-row tiles filled by plain loads and
 //     st.shared (20-25 us), the same filled by cp.async in three 72 KiB stages (16.7 us: the tensor core's reads of a
-//     tile and the fills of the next did not overlap), fragments re-read from a warp-private shared-memory tile (22-30 us).
+//     tile and the fills of the next did not overlap), fragments re-read from a warp-private shared-memory tile (22-30 us),
+//     the activations as the 64-row operand of tcgen05.mma against 97-row TMA boxes of weights (0.375 us per 128 bytes of k
+//     on every SM, i.e. slower than the 128-row form's 0.28 us, plus a 16-lane epilogue: 25 us).
 //
 // Launch overlap.  The kernels let their successor on the stream start early (griddepcontrol) and are themselves
 // launched as such dependents; they wait for their predecessor before their first global read, having asked the L2
